@@ -1,0 +1,125 @@
+"""Pins the CPU oracle against results produced by the reference's own Python code
+(tests/golden/make_golden.py says how each fixture was made)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import woq_oracle as O
+
+QUANT_CASES = [
+    "int4_g128_asym",
+    "int4_g64_asym",
+    "int4_g32_sym",
+    "int4_g128_rem",
+    "int4_pc_asym",
+    "int8_pc_sym",
+    "int8_g128_asym",
+]
+
+
+@pytest.fixture(scope="module")
+def qcases(golden_dir):
+    return np.load(os.path.join(golden_dir, "quantizer_cases.npz"))
+
+
+@pytest.mark.parametrize("name", QUANT_CASES)
+def test_quantizer_bit_exact(qcases, name):
+    N, K, dt, G, sym = (int(v) for v in qcases[name + ".meta"])
+    w = qcases[name + ".w"]
+    if G > 0:
+        qw, s, z = O.quantize_per_block(w, dt, G, bool(sym))
+    else:
+        qw, s, z = O.quantize_per_channel(w, dt, bool(sym))
+    ref_qw = qcases[name + ".qw"]
+    assert qw.dtype == ref_qw.dtype and qw.shape == ref_qw.shape
+    np.testing.assert_array_equal(qw, ref_qw)
+    np.testing.assert_array_equal(s.view(np.uint32), qcases[name + ".scales"].view(np.uint32))
+    if sym:
+        assert z is None and (name + ".zps") not in qcases
+    else:
+        np.testing.assert_array_equal(z, qcases[name + ".zps"])
+
+
+@pytest.mark.parametrize("name", QUANT_CASES)
+def test_dequantizer_matches_reference_fp32(qcases, name):
+    """scale_rounding='none' without output rounding is the reference's fp32 dequantiser."""
+    N, K, dt, G, sym = (int(v) for v in qcases[name + ".meta"])
+    zps = None if sym else qcases[name + ".zps"]
+    dq = O.dequantize_weight(
+        qcases[name + ".qw"], qcases[name + ".scales"], zps, dt, K, G,
+        scale_rounding="none", round_output=False,
+    )
+    np.testing.assert_array_equal(dq.view(np.uint32), qcases[name + ".dq"].view(np.uint32))
+
+
+def test_canonical_dequant_is_bf16_of_bf16_scale(qcases):
+    name = "int4_g128_asym"
+    N, K, dt, G, sym = (int(v) for v in qcases[name + ".meta"])
+    dq = O.dequantize_weight(qcases[name + ".qw"], qcases[name + ".scales"].astype(np.float16),
+                             qcases[name + ".zps"], dt, K, G)
+    q = O.unpack_nibbles(qcases[name + ".qw"]).astype(np.float32)
+    s = O.rne_bf16(qcases[name + ".scales"].astype(np.float16).astype(np.float32))
+    z = qcases[name + ".zps"]
+    expect = O.rne_bf16((q - np.repeat(z, G, 1)) * np.repeat(s, G, 1))
+    np.testing.assert_array_equal(dq.view(np.uint32), expect.view(np.uint32))
+    assert np.all((dq.view(np.uint32) & 0xFFFF) == 0)
+
+
+def test_rne_bf16_against_torch():
+    import torch
+
+    rng = np.random.default_rng(0)
+    x = np.concatenate([
+        rng.standard_normal(20000).astype(np.float32) * 3,
+        np.array([0.0, -0.0, 1.00390625, 1.01171875, 3.3895314e38, 1e-40, np.inf, -np.inf],
+                 dtype=np.float32),
+    ])
+    ours = O.rne_bf16(x)
+    ref = torch.from_numpy(x).bfloat16().float().numpy()
+    np.testing.assert_array_equal(ours.view(np.uint32), ref.view(np.uint32))
+
+
+def test_awq_fixture(golden_dir):
+    """The reference's AWQ known-answer tensors: integer codes and zero points must come
+    out exactly, the dequantised weight and the output within the reference test's own
+    tolerance (tests/cpu/test_ipex_llm_quantization.py:151 uses prec=0.1)."""
+    f = np.load(os.path.join(golden_dir, "awq_fixture.npz"))
+    G = int(f["group_size"])
+    scales = O.from_bf16_bits(f["scales_bf16"])  # [K/G, N]
+    qw, s, z = O.awq_to_plain(f["qweight"], f["qzeros"], scales)
+    K = f["qweight"].shape[0]
+    N = f["qweight"].shape[1] * 8
+    assert qw.shape == (N, K // 2) and s.shape == (N, K // G) and z.shape == (N, K // G)
+    w_ref = O.from_bf16_bits(f["w_ref_bf16"])  # rows w_ref_rows of [N, K]
+    rows = f["w_ref_rows"]
+    # the reference test computes q*s - bf16(z*s) in bf16; ours is (q-z)*s rounded once:
+    # equal up to bf16 rounding of numbers of size |q*s|.
+    w = O.dequantize_weight(qw, s, z, O.WOQ_DTYPE_INT4, K, G)[rows]
+    tol = np.abs(w_ref).max() * 2.0 ** -7
+    assert np.abs(w - w_ref).max() <= tol
+    # exact check of the integer part: recover q - z from the reference weight
+    sfull = np.repeat(s[rows], G, axis=1)
+    qz = O.unpack_nibbles(qw)[rows].astype(np.float32) - np.repeat(z[rows], G, axis=1)
+    assert np.abs(np.rint(w_ref / sfull) - qz).max() <= 1.0
+    assert (np.rint(w_ref / sfull) == qz).mean() > 0.98
+    x = O.from_bf16_bits(f["act_bf16"])
+    bias = O.from_bf16_bits(f["bias_bf16"])
+    y = O.woq_linear_bf16(x, qw, s, z, bias, O.WOQ_DTYPE_INT4, G)
+    y_ref = O.from_bf16_bits(f["y_ref_bf16"])
+    assert np.abs(y - y_ref).max() <= 0.1
+    mx, mr = O.parity_metrics(y, y_ref)
+    assert mx < 2e-2 and mr < 1e-2
+
+
+def test_act_quant_against_reference_fakequant(golden_dir):
+    """Codes * scale must reproduce the reference test's per-token symmetric fake-quant
+    (tests/cpu/test_quantization_default_recipe.py:915-979, mode 6)."""
+    f = np.load(os.path.join(golden_dir, "act_quant_cases.npz"))
+    for i in range(3):
+        x = O.from_bf16_bits(f[f"c{i}.x_bf16"])
+        fq_ref = f[f"c{i}.fq_f32"]
+        q, s, _ = O.dynamic_quant_per_token(x, sym=True)
+        fq = q.astype(np.float32) * s[:, None]
+        np.testing.assert_array_equal(fq, fq_ref)  # value equality (-0.0 == 0.0)
+        assert q.min() >= -128 and q.max() <= 127 and np.abs(q).max() == 127
