@@ -1,0 +1,194 @@
+/*
+ * woq_b200.h -- C ABI of libwoq_b200.so: weight-only-quantised (WOQ) linear for NVIDIA B200
+ * (sm_100a).
+ *
+ * The library replaces the kernel layer of intel-extension-for-pytorch's WOQ linear.  Every
+ * entry point names the reference interface it stands in for (paths are relative to the
+ * reference project).  All pointers are plain device pointers unless stated otherwise; no
+ * framework types cross this boundary.  Calls are asynchronous on the CUDA stream passed in
+ * (a `cudaStream_t` carried as `void*`), never throw and never abort: they return one of the
+ * WOQ_B200_* status codes, and `woq_b200_last_error()` gives a message for the calling thread.
+ *
+ * Numeric contract (same as the reference's bf16 / int8 compute modes):
+ *   INT4/INT8 weights, lowp BF16:  y = bf16( sum_k x[m,k] * W[n,k] + bias[n] ), then post-op,
+ *       W[n,k] = (q[n,k] - zp[n,g]) * bf16(scale[n,g]), fp32 accumulation.
+ *   INT8 weights, lowp INT8:       per-token symmetric int8 activations, int32 accumulation,
+ *       y = bf16( float(acc) * scale_a[m] * scale_w[n] + bias[n] ), then post-op.
+ */
+#ifndef WOQ_B200_H_
+#define WOQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------- */
+#define WOQ_B200_OK 0
+#define WOQ_B200_ERR_INVALID_ARG 1   /* null pointer, bad size, misaligned buffer          */
+#define WOQ_B200_ERR_UNSUPPORTED 2   /* a valid reference configuration this build lacks   */
+#define WOQ_B200_ERR_CUDA 3          /* a CUDA runtime call failed                         */
+#define WOQ_B200_ERR_WORKSPACE 4     /* workspace smaller than woq_b200_workspace_bytes()  */
+#define WOQ_B200_ERR_BAD_HANDLE 5    /* context pointer does not carry the magic word      */
+#define WOQ_B200_ERR_DEVICE_WAIT 6   /* a bounded in-kernel wait ran out (status word set) */
+
+/* ---- enumerations shared with the reference (csrc/cpu/aten/utils/woq_defines.h:6-50) -- */
+#define WOQ_B200_DTYPE_INT8 1
+#define WOQ_B200_DTYPE_INT4 2
+#define WOQ_B200_DTYPE_NF4 3
+#define WOQ_B200_DTYPE_FP8 4
+
+#define WOQ_B200_LOWP_NONE 0
+#define WOQ_B200_LOWP_FP16 1
+#define WOQ_B200_LOWP_BF16 2
+#define WOQ_B200_LOWP_INT8 3
+
+#define WOQ_B200_ACT_NONE (-1)
+#define WOQ_B200_ACT_PER_M 2
+#define WOQ_B200_ACT_PER_M_SYM 6
+
+#define WOQ_B200_FMT_PLAIN 0 /* INT4: [N, K/2] u8, even k in the low nibble; INT8: [N, K] s8 */
+#define WOQ_B200_FMT_GPTQ 1  /* [K/8, N] int32                                             */
+#define WOQ_B200_FMT_AWQ 2   /* [K, N/8] int32, nibble order 0,2,4,6,1,3,5,7               */
+
+/* post-op codes (woq_defines.h:27-38) */
+#define WOQ_B200_FUSE_NONE 0x0
+#define WOQ_B200_FUSE_GELU_ERF 0x1
+#define WOQ_B200_FUSE_GELU_TANH 0x2
+#define WOQ_B200_FUSE_RELU 0x3
+#define WOQ_B200_FUSE_SILU 0x4
+#define WOQ_B200_FUSE_ADD 0x10
+#define WOQ_B200_FUSE_ADD_ADD 0x20
+#define WOQ_B200_FUSE_MUL 0x30
+/* Not in the reference: y[M,N/2] = bf16(up * silu(gate)) for a weight that stacks gate rows
+ * [0,N/2) over up rows [N/2,N).  Equals woq_linear_silu followed by woq_linear_mul
+ * (intel_extension_for_pytorch/transformers/models/cpu/fusions/linear_fusion.py:482-490).
+ * Needs a context created with WOQ_B200_LAYOUT_GATE_UP. */
+#define WOQ_B200_FUSE_SILU_MUL 0x100
+/* Not in the reference as a post-op: out[row_idx[i], :] = bf16(out + y[i,:] * row_w[i]), the
+ * scatter step of mixtral_moe_woq (csrc/cpu/aten/kernels/MoEKrnl.cpp:67-120). */
+#define WOQ_B200_FUSE_SCALED_SCATTER_ADD 0x200
+
+/* element types of the tensors handed to woq_b200_ctx_create */
+#define WOQ_B200_T_NONE 0
+#define WOQ_B200_T_F32 1
+#define WOQ_B200_T_F16 2
+#define WOQ_B200_T_BF16 3
+#define WOQ_B200_T_U8 4
+#define WOQ_B200_T_S8 5
+#define WOQ_B200_T_I32 6 /* packed 4-bit zero points of GPTQ/AWQ checkpoints */
+
+#define WOQ_B200_LAYOUT_GATE_UP 0x1
+
+/* kernel selection for INT4 weights (the results of the two kernels agree within the output
+ * tolerance; the tensor-core kernel reproduces the bf16-rounded dequantised weights exactly) */
+#define WOQ_B200_HINT_AUTO 0
+#define WOQ_B200_HINT_TENSOR_CORE 1 /* tcgen05 kernel for every M                         */
+#define WOQ_B200_HINT_STREAM 2      /* register-dequant streaming kernel, 16 tokens a pass */
+
+/* Description of one quantised linear layer: the arguments of
+ * ipex_prepack::weight_only_qlinear_prepack
+ * (csrc/cpu/jit/cpu/kernels/RegisterOpContextClass.cpp:192-205). */
+typedef struct woq_b200_desc {
+  int64_t n;              /* out features                                                   */
+  int64_t k;              /* in features                                                    */
+  int32_t weight_dtype;   /* WOQ_B200_DTYPE_*                                               */
+  int32_t group_size;     /* > 0, or -1 for one group per output channel                   */
+  int32_t lowp_mode;      /* WOQ_B200_LOWP_*                                                */
+  int32_t act_quant_mode; /* WOQ_B200_ACT_*; only read when lowp_mode is INT8               */
+  int32_t weight_format;  /* WOQ_B200_FMT_*                                                 */
+  int32_t scale_dtype;    /* F32, F16 or BF16; scales are [N, ceil(K/G)] ([K/G, N] for AWQ/GPTQ) */
+  int32_t zp_dtype;       /* NONE (symmetric: 8 for INT4, 0 for INT8), F32, U8, or packed
+                             int32 words (same packing as the weight) for GPTQ/AWQ         */
+  int32_t bias_dtype;     /* NONE, F32 or BF16; bias is [N]                                 */
+  int32_t layout_flags;   /* WOQ_B200_LAYOUT_*                                              */
+  int32_t kernel_hint;    /* WOQ_B200_HINT_*: 0 lets the library choose per call              */
+} woq_b200_desc;
+
+typedef struct woq_b200_ctx woq_b200_ctx; /* opaque; host memory owning device buffers */
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int woq_b200_version(void);
+
+/* Message for the last non-OK status returned to the calling host thread. */
+const char* woq_b200_last_error(void);
+
+/* Number of kernels this library has launched in this process (all threads). */
+int64_t woq_b200_kernel_launches(void);
+
+/* Repack a plain quantised weight into the tiled device layout and keep bf16 scales,
+ * zero points and fp32 bias beside it.  Replaces woq_linear_pack_weight + qlinear_woq_pack
+ * (csrc/cpu/aten/Linear.cpp:379-438, csrc/cpu/aten/kernels/WoqUtilKrnl.cpp:32-249) and the
+ * scale/zero-point re-layout of ContextLinearWoq (csrc/cpu/jit/cpu/kernels/ContextLinearWoq.h:36-128).
+ * Allocates the packed buffers with cudaMalloc on the current device; inputs may be freed
+ * once the stream has passed this call.  Synchronises the stream once to validate the zero
+ * points. */
+int woq_b200_ctx_create(const woq_b200_desc* desc, const void* qweight, const void* scales,
+                        const void* zero_points, const void* bias, void* stream,
+                        woq_b200_ctx** out);
+
+/* Frees the packed buffers.  Counterpart of the op-context destructor
+ * (csrc/cpu/jit/cpu/kernels/OpContext.h:363-405). */
+int woq_b200_ctx_destroy(woq_b200_ctx* ctx);
+
+/* Copy of the descriptor a context was created with. */
+int woq_b200_ctx_desc(const woq_b200_ctx* ctx, woq_b200_desc* out);
+
+/* Bytes of the packed weight + scale buffers held on the device. */
+size_t woq_b200_ctx_device_bytes(const woq_b200_ctx* ctx);
+
+/* Bit-exact inverse of the repack: writes the plain [N, K/2] u8 (INT4) or [N, K] s8 (INT8)
+ * weight.  Replaces qlinear_woq_unpack (csrc/cpu/aten/kernels/WoqUtilKrnl.cpp:251-324). */
+int woq_b200_ctx_unpack(const woq_b200_ctx* ctx, void* qweight_plain, void* stream);
+
+/* Scratch bytes woq_b200_linear needs for M tokens.  The first woq_b200_workspace_header_bytes()
+ * bytes must be zero before the first use of a workspace (cudaMemsetAsync once); every call
+ * leaves them zero again, so one workspace can be reused by any number of stream-ordered
+ * calls.  Calls that overlap on the device need separate workspaces. */
+size_t woq_b200_workspace_bytes(const woq_b200_ctx* ctx, int64_t m);
+size_t woq_b200_workspace_header_bytes(void);
+
+/* y[M, N_out] (bf16) = post_op( x[M, K] (bf16) * W^T + bias ).  Replaces the kernel reached
+ * from torch_ipex::ipex_woq_linear / woq_linear_{gelu,new_gelu,relu,silu,add,add_add,mul}
+ * (csrc/cpu/aten/Linear.cpp:499-811 -> qlinear_woq_affine,
+ * csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:56-165).  `others` is a HOST array of n_others
+ * device pointers to [M, N] bf16 tensors (ADD: 1, ADD_ADD: 2, MUL: 1).  x rows are ldx
+ * elements apart, y rows ldy (pass K and N_out for dense tensors).  N_out = N, or N/2 for
+ * WOQ_B200_FUSE_SILU_MUL. */
+int woq_b200_linear(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx, int32_t fusion,
+                    const void* const* others, int32_t n_others, void* y, int64_t ldy,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* One expert of a mixture-of-experts layer on gathered tokens:
+ * out[row_idx[i], :] = bf16(out[row_idx[i], :] + y[i, :] * row_weight[i]) with
+ * y = x[row_idx_in ? row_idx_in[i] : i, :] * W^T.  Replaces fuse_index_unsqueeze /
+ * fuse_index_mul_index_add around the WOQ linears of mixtral_moe_woq
+ * (csrc/cpu/aten/kernels/MoEKrnl.cpp:67-160,254-285).  row_weight is bf16 [m]. */
+int woq_b200_linear_scatter(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
+                            const int32_t* row_idx, const void* row_weight, void* out,
+                            int64_t ld_out, void* workspace, size_t workspace_bytes,
+                            void* stream);
+
+/* Parity hooks -------------------------------------------------------------------------
+ * Dequantised weight [N, K] bf16 produced by the same device routine the tensor-core kernel
+ * uses for its tiles (the reference's Dequantize<bfloat16>, csrc/cpu/aten/utils/woq.h:1501-1581). */
+int woq_b200_dump_dequant(const woq_b200_ctx* ctx, void* w_bf16, void* stream);
+
+/* INT8-lowp internals for M tokens: quantised activations qa[M, K] s8, their scales sa[M] f32
+ * (dynamic_quantize_per_block, csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750) and the
+ * int32 accumulators acc[M, N] summed over the whole K (woq.h:2231-2354).  Any of the three
+ * outputs may be null. */
+int woq_b200_int8_internals(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
+                            int8_t* qa, float* sa, int32_t* acc, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* Reads the status word of a workspace (synchronises the stream).  WOQ_B200_OK, or
+ * WOQ_B200_ERR_DEVICE_WAIT when a bounded wait inside a kernel gave up; the word is cleared. */
+int woq_b200_workspace_status(void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WOQ_B200_H_ */

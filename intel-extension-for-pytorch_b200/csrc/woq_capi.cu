@@ -1,0 +1,548 @@
+// C ABI of libwoq_b200.so (declared in include/woq_b200.h): contexts, argument checks and
+// kernel selection.  No kernel code lives here.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "../../include/woq_b200.h"
+#include "woq_kernels.h"
+
+namespace woq {
+static std::atomic<int64_t> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+}  // namespace woq
+
+namespace {
+
+constexpr uint64_t kMagic = 0x574f5142323030ull;  // "WOQB200"
+constexpr size_t kWsHeaderBytes = 64 * 1024;      // status word + per-tile arrival counters
+constexpr int kMaxCounterTiles = (kWsHeaderBytes - 256) / 4;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t e__ = (expr);                                                              \
+    if (e__ != cudaSuccess)                                                                \
+      return fail(WOQ_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));     \
+  } while (0)
+
+}  // namespace
+
+struct woq_b200_ctx {
+  uint64_t magic;
+  woq_b200_desc desc;
+  int device;
+  int num_sms;
+  // derived
+  int tiles;         // ceil(N / 64) (gate/up layout: N / 64)
+  int kb_per_tile;   // K / 64
+  int kb_per_group;  // group size / 64 (per-channel: kb_per_tile)
+  int groups;        // groups along K
+  int gate_up;
+  // device buffers
+  uint8_t* wq;       // INT4: tiled nibbles; INT8: plain [n_pad][k]
+  uint32_t* sz;      // INT4 group scales + zero points
+  uint8_t* wq_tc;    // INT4: 128-row layout for the tensor-core kernel
+  uint32_t* sz_tc;
+  int tiles_tc, kbpg_shift;
+  size_t wq_tc_bytes, sz_tc_bytes;
+  float* scale_f32;  // INT8: per-channel fp32 scales [n_pad]
+  float* bias;       // fp32 [n] or null
+  size_t wq_bytes, sz_bytes;
+};
+
+namespace {
+
+int check_ctx(const woq_b200_ctx* c) {
+  if (!c) return fail(WOQ_B200_ERR_INVALID_ARG, "context is null");
+  if (c->magic != kMagic) return fail(WOQ_B200_ERR_BAD_HANDLE, "context magic mismatch");
+  return WOQ_B200_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+__global__ void convert_bias_kernel(const void* src, float* dst, int n, int dtype) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  dst[i] = dtype == WOQ_B200_T_F32 ? reinterpret_cast<const float*>(src)[i]
+                                   : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int woq_b200_version(void) { return 100; }
+
+const char* woq_b200_last_error(void) { return g_err; }
+
+int64_t woq_b200_kernel_launches(void) { return woq::g_launches.load(); }
+
+size_t woq_b200_workspace_header_bytes(void) { return kWsHeaderBytes; }
+
+int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void* scales,
+                        const void* zero_points, const void* bias, void* stream_,
+                        woq_b200_ctx** out) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!d || !qweight || !scales || !out)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "desc, qweight, scales and out must be non-null");
+  *out = nullptr;
+  if (d->n <= 0 || d->k <= 0 || d->n > (1 << 24) || d->k > (1 << 24))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "bad shape N=%lld K=%lld", (long long)d->n, (long long)d->k);
+  if (d->weight_dtype == WOQ_B200_DTYPE_NF4 || d->weight_dtype == WOQ_B200_DTYPE_FP8)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "NF4 / FP8 weights are not built yet");
+  if (d->weight_dtype != WOQ_B200_DTYPE_INT4 && d->weight_dtype != WOQ_B200_DTYPE_INT8)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "unknown weight dtype %d", d->weight_dtype);
+  if (d->group_size == 0 || d->group_size < -1)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "group_size must be -1 or positive, got %d", d->group_size);
+  if ((zero_points == nullptr) != (d->zp_dtype == WOQ_B200_T_NONE))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "zero_points pointer and zp_dtype disagree");
+  if ((bias == nullptr) != (d->bias_dtype == WOQ_B200_T_NONE))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "bias pointer and bias_dtype disagree");
+  if (d->bias_dtype != WOQ_B200_T_NONE && d->bias_dtype != WOQ_B200_T_F32 &&
+      d->bias_dtype != WOQ_B200_T_BF16)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "bias must be fp32 or bf16");
+  if (d->scale_dtype != WOQ_B200_T_F32 && d->scale_dtype != WOQ_B200_T_F16 &&
+      d->scale_dtype != WOQ_B200_T_BF16)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "scales must be fp32, fp16 or bf16");
+
+  if (d->weight_dtype == WOQ_B200_DTYPE_INT8)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 weights are not built yet");
+  // ---- INT4 ----
+  if (d->lowp_mode == WOQ_B200_LOWP_INT8)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 weights with INT8 compute are not built yet");
+  if (d->k % 64 != 0)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 path needs K %% 64 == 0 (K=%lld)", (long long)d->k);
+  const int64_t g_eff = d->group_size > 0 ? d->group_size : d->k;
+  if (g_eff % 64 != 0 || (g_eff < d->k && (g_eff & (g_eff - 1)) != 0))
+    return fail(WOQ_B200_ERR_UNSUPPORTED,
+                "INT4 path needs a power-of-two group size >= 64 or per-channel (got %d)",
+                d->group_size);
+  const int gate_up = (d->layout_flags & WOQ_B200_LAYOUT_GATE_UP) ? 1 : 0;
+  if (gate_up && (d->n % 128 != 0))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "gate/up layout needs N %% 128 == 0");
+  if (d->weight_format != WOQ_B200_FMT_PLAIN && (d->n % 8 != 0))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "GPTQ/AWQ formats need N %% 8 == 0");
+
+  woq_b200_ctx* c = new (std::nothrow) woq_b200_ctx();
+  if (!c) return fail(WOQ_B200_ERR_CUDA, "out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->desc = *d;
+  c->gate_up = gate_up;
+  CUDA_TRY(cudaGetDevice(&c->device));
+  CUDA_TRY(cudaDeviceGetAttribute(&c->num_sms, cudaDevAttrMultiProcessorCount, c->device));
+  c->tiles = static_cast<int>((d->n + 63) / 64);
+  c->kb_per_tile = static_cast<int>(d->k / 64);
+  c->kb_per_group = static_cast<int>(g_eff >= d->k ? c->kb_per_tile : g_eff / 64);
+  c->groups = static_cast<int>((d->k + g_eff - 1) / g_eff);
+  c->wq_bytes = static_cast<size_t>(c->tiles) * c->kb_per_tile * woq::kBlockBytes;
+  c->sz_bytes = static_cast<size_t>(c->tiles) * c->groups * 64 * 4;
+  c->tiles_tc = static_cast<int>((d->n + 127) / 128);
+  c->kbpg_shift = 30;  // per-channel: every k-block maps to group 0
+  if (g_eff < d->k) {
+    c->kbpg_shift = 0;
+    while ((1 << c->kbpg_shift) < c->kb_per_group) ++c->kbpg_shift;
+  }
+  c->wq_tc_bytes = static_cast<size_t>(c->tiles_tc) * c->kb_per_tile * woq::kTcBlockBytes;
+  c->sz_tc_bytes = static_cast<size_t>(c->tiles_tc) * c->groups * 128 * 4;
+
+  int* d_flag = nullptr;
+  uint8_t* tmp_plain = nullptr;
+  uint8_t* tmp_zp = nullptr;
+  auto cleanup = [&](int rc) {
+    if (d_flag) cudaFree(d_flag);
+    if (tmp_plain) cudaFree(tmp_plain);
+    if (tmp_zp) cudaFree(tmp_zp);
+    if (rc != WOQ_B200_OK) {
+      if (c->wq) cudaFree(c->wq);
+      if (c->sz) cudaFree(c->sz);
+      if (c->wq_tc) cudaFree(c->wq_tc);
+      if (c->sz_tc) cudaFree(c->sz_tc);
+      if (c->bias) cudaFree(c->bias);
+      delete c;
+    }
+    return rc;
+  };
+#define CUDA_TRY_C(expr)                                                                       \
+  do {                                                                                         \
+    cudaError_t e__ = (expr);                                                                  \
+    if (e__ != cudaSuccess)                                                                    \
+      return cleanup(fail(WOQ_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__))); \
+  } while (0)
+
+  CUDA_TRY_C(cudaMalloc(&c->wq, c->wq_bytes));
+  CUDA_TRY_C(cudaMalloc(&c->sz, c->sz_bytes));
+  CUDA_TRY_C(cudaMalloc(&c->wq_tc, c->wq_tc_bytes));
+  CUDA_TRY_C(cudaMalloc(&c->sz_tc, c->sz_tc_bytes));
+  CUDA_TRY_C(cudaMalloc(&d_flag, sizeof(int)));
+  CUDA_TRY_C(cudaMemsetAsync(d_flag, 0, sizeof(int), stream));
+
+  const uint8_t* plain = static_cast<const uint8_t*>(qweight);
+  const void* zps = zero_points;
+  int zp_dtype = d->zp_dtype;
+  int transposed = 0;
+  if (d->weight_format != WOQ_B200_FMT_PLAIN) {
+    // int32 checkpoint layouts: scales / zero points are [groups][N]
+    CUDA_TRY_C(cudaMalloc(&tmp_plain, static_cast<size_t>(d->n) * (d->k / 2)));
+    if (d->weight_format == WOQ_B200_FMT_AWQ)
+      CUDA_TRY_C(woq::launch_awq_to_plain(static_cast<const int32_t*>(qweight), tmp_plain,
+                                          (int)d->n, (int)d->k, stream));
+    else
+      CUDA_TRY_C(woq::launch_gptq_to_plain(static_cast<const int32_t*>(qweight), tmp_plain,
+                                           (int)d->n, (int)d->k, stream));
+    plain = tmp_plain;
+    transposed = 1;
+    if (zero_points && d->zp_dtype != WOQ_B200_T_F32 && d->zp_dtype != WOQ_B200_T_U8) {
+      // packed int32 zero points [groups][N/8]
+      CUDA_TRY_C(cudaMalloc(&tmp_zp, static_cast<size_t>(d->n) * c->groups));
+      CUDA_TRY_C(woq::launch_unpack_qzeros(static_cast<const int32_t*>(zero_points), tmp_zp,
+                                           (int)d->n, c->groups,
+                                           d->weight_format == WOQ_B200_FMT_AWQ, 0, stream));
+      zps = tmp_zp;
+      zp_dtype = WOQ_B200_T_U8;
+      // tmp_zp is [N][groups]; scales stay transposed -> handled by two passes below
+    }
+  }
+  woq::PackInt4Args pa{plain, c->wq, (int)d->n, (int)d->k, c->tiles, c->kb_per_tile, gate_up, 0};
+  CUDA_TRY_C(woq::launch_pack_int4(pa, stream));
+  woq::PackInt4Args pt{plain, c->wq_tc, (int)d->n, (int)d->k, c->tiles_tc, c->kb_per_tile, gate_up, 1};
+  CUDA_TRY_C(woq::launch_pack_int4(pt, stream));
+
+  woq::PackScaleArgs sa{};
+  sa.scales = scales;
+  sa.zps = zps;
+  sa.sz = c->sz;
+  sa.bad_zp = d_flag;
+  sa.n = (int)d->n;
+  sa.tiles = c->tiles;
+  sa.groups = c->groups;
+  sa.gate_up = gate_up;
+  sa.transposed = transposed;
+  sa.zp_transposed = (tmp_zp != nullptr) ? 0 : transposed;
+  sa.scale_dtype = d->scale_dtype;
+  sa.zp_dtype = zp_dtype;
+  sa.default_zp = 8;  // symmetric INT4 is stored as q + 8
+  sa.tc = 0;
+  CUDA_TRY_C(woq::launch_pack_scales(sa, stream));
+  sa.sz = c->sz_tc;
+  sa.tiles = c->tiles_tc;
+  sa.tc = 1;
+  CUDA_TRY_C(woq::launch_pack_scales(sa, stream));
+
+  if (bias) {
+    CUDA_TRY_C(cudaMalloc(&c->bias, static_cast<size_t>(d->n) * sizeof(float)));
+    convert_bias_kernel<<<(unsigned)((d->n + 255) / 256), 256, 0, stream>>>(bias, c->bias, (int)d->n,
+                                                                          d->bias_dtype);
+    woq::count_launch();
+    CUDA_TRY_C(cudaGetLastError());
+  }
+  int h_flag = 0;
+  CUDA_TRY_C(cudaMemcpyAsync(&h_flag, d_flag, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY_C(cudaStreamSynchronize(stream));
+  if (h_flag)
+    return cleanup(fail(WOQ_B200_ERR_INVALID_ARG, "zero points must be integers in [0, 127]"));
+#undef CUDA_TRY_C
+  c->magic = kMagic;
+  *out = c;
+  return cleanup(WOQ_B200_OK);
+}
+
+int woq_b200_ctx_destroy(woq_b200_ctx* c) {
+  if (int rc = check_ctx(c)) return rc;
+  c->magic = 0;
+  cudaFree(c->wq);
+  cudaFree(c->sz);
+  cudaFree(c->wq_tc);
+  cudaFree(c->sz_tc);
+  cudaFree(c->scale_f32);
+  cudaFree(c->bias);
+  delete c;
+  return WOQ_B200_OK;
+}
+
+int woq_b200_ctx_desc(const woq_b200_ctx* c, woq_b200_desc* out) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!out) return fail(WOQ_B200_ERR_INVALID_ARG, "out is null");
+  *out = c->desc;
+  return WOQ_B200_OK;
+}
+
+size_t woq_b200_ctx_device_bytes(const woq_b200_ctx* c) {
+  if (check_ctx(c)) return 0;
+  return c->wq_bytes + c->sz_bytes + c->wq_tc_bytes + c->sz_tc_bytes;
+}
+
+int woq_b200_ctx_unpack(const woq_b200_ctx* c, void* qweight_plain, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!qweight_plain) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  CUDA_TRY(woq::launch_unpack_int4(c->wq, static_cast<uint8_t*>(qweight_plain), (int)c->desc.n,
+                                   (int)c->desc.k, c->tiles, c->kb_per_tile, c->gate_up, stream));
+  return WOQ_B200_OK;
+}
+
+size_t woq_b200_workspace_bytes(const woq_b200_ctx* c, int64_t m) {
+  if (check_ctx(c)) return 0;
+  // header + one pair of partial tiles per CTA of the largest grid
+  size_t decode = woq::decode_int4_partial_bytes(2 * c->num_sms);
+  int n_tok = static_cast<int>(m < 256 ? m : 256);
+  n_tok = (n_tok + 15) / 16 * 16;
+  if (n_tok < 16) n_tok = 16;
+  size_t tc = woq::tc_partial_bytes(c->num_sms, n_tok);
+  return kWsHeaderBytes + (decode > tc ? decode : tc);
+}
+
+static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
+                      const void* o0, const void* o1, const int32_t* row_idx, const void* row_w,
+                      void* y, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (ws_bytes < woq_b200_workspace_bytes(c, m))
+    return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", ws_bytes,
+                woq_b200_workspace_bytes(c, m));
+  if (c->tiles > kMaxCounterTiles)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the workspace header");
+  woq::DecodeParams p{};
+  p.wq = c->wq;
+  p.sz = c->sz;
+  p.bias = c->bias;
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.other0 = static_cast<const __nv_bfloat16*>(o0);
+  p.other1 = static_cast<const __nv_bfloat16*>(o1);
+  p.row_idx = row_idx;
+  p.row_w = static_cast<const __nv_bfloat16*>(row_w);
+  uint8_t* w8 = static_cast<uint8_t*>(ws);
+  p.status = reinterpret_cast<int*>(w8);
+  p.counters = reinterpret_cast<uint32_t*>(w8 + 256);
+  p.partials = reinterpret_cast<float*>(w8 + kWsHeaderBytes);
+  p.ldx = ldx;
+  p.ldy = ldy;
+  p.m = (int)m;
+  p.n = (int)c->desc.n;
+  p.n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? (int)(c->desc.n / 2) : (int)c->desc.n;
+  p.k = (int)c->desc.k;
+  p.tiles = c->tiles;
+  p.kb_per_tile = c->kb_per_tile;
+  p.kb_per_group = c->kb_per_group;
+  p.groups = c->groups;
+  p.gps = c->kb_per_group >= 8 ? 1 : 8 / c->kb_per_group;
+  p.fusion = fusion;
+  p.gate_up = c->gate_up;
+  woq::DecodeShape shape{(int)m, c->tiles, c->kb_per_tile};
+  const int grid = woq::decode_int4_pick_grid(shape, c->num_sms);
+  CUDA_TRY(woq::launch_decode_int4(p, grid, stream));
+  woq::count_launch();
+  return WOQ_B200_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// K-major tile map over a row-major [rows][ld] matrix of `elt_bytes`-byte elements:
+// box = 128 bytes along K x `box_rows` rows, 128-byte swizzle, zero fill outside.
+static int make_kmajor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols,
+                           int64_t ld, int elt_bytes, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(WOQ_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elt_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elt_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elt_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(WOQ_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return WOQ_B200_OK;
+}
+
+static int run_tc(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
+                  const void* o0, const void* o1, const int32_t* row_idx, const void* row_w,
+                  void* y, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  if (ws_bytes < woq_b200_workspace_bytes(c, m))
+    return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", ws_bytes,
+                woq_b200_workspace_bytes(c, m));
+  if (c->tiles_tc > kMaxCounterTiles)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the workspace header");
+  CUtensorMap xmap;
+  const int64_t mt = m < 256 ? m : 256;
+  int n_tok = static_cast<int>((mt + 15) / 16 * 16);
+  if (int rc = make_kmajor_map(&xmap, x, m, c->desc.k, ldx, 2, n_tok)) return rc;
+  uint8_t* w8 = static_cast<uint8_t*>(ws);
+  const bool scatter = fusion == WOQ_B200_FUSE_SCALED_SCATTER_ADD;
+  for (int64_t m0 = 0; m0 < m; m0 += 256) {
+    const int64_t mm = m - m0 < 256 ? m - m0 : 256;
+    woq::TcParams p{};
+    p.wq = c->wq_tc;
+    p.sz = c->sz_tc;
+    p.bias = c->bias;
+    p.y = scatter ? static_cast<__nv_bfloat16*>(y) : static_cast<__nv_bfloat16*>(y) + m0 * ldy;
+    p.other0 = o0 ? static_cast<const __nv_bfloat16*>(o0) + m0 * ldy : nullptr;
+    p.other1 = o1 ? static_cast<const __nv_bfloat16*>(o1) + m0 * ldy : nullptr;
+    p.row_idx = row_idx ? row_idx + m0 : nullptr;
+    p.row_w = row_w ? static_cast<const __nv_bfloat16*>(row_w) + m0 : nullptr;
+    p.status = reinterpret_cast<int*>(w8);
+    p.counters = reinterpret_cast<uint32_t*>(w8 + 256);
+    p.partials = reinterpret_cast<float*>(w8 + kWsHeaderBytes);
+    p.ldy = ldy;
+    p.m = (int)mm;
+    p.n = (int)c->desc.n;
+    p.n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? (int)(c->desc.n / 2) : (int)c->desc.n;
+    p.k = (int)c->desc.k;
+    p.m0 = (int)m0;
+    p.n_tok = n_tok;
+    p.tiles = c->tiles_tc;
+    p.kb_per_tile = c->kb_per_tile;
+    p.kbpg_shift = c->kbpg_shift;
+    p.groups = c->groups;
+    p.fusion = fusion;
+    p.gate_up = c->gate_up;
+    const int grid = woq::tc_pick_grid(c->tiles_tc, c->kb_per_tile, c->num_sms);
+    CUDA_TRY(woq::launch_int4_tc(p, xmap, grid, stream));
+    woq::count_launch();
+  }
+  return WOQ_B200_OK;
+}
+
+static bool use_tc_path(const woq_b200_ctx* c, int64_t m) {
+  static int env = -1;
+  if (env < 0) {
+    const char* e = getenv("WOQ_B200_KERNEL_HINT");
+    env = e ? atoi(e) : 0;
+  }
+  const int hint = c->desc.kernel_hint ? c->desc.kernel_hint : env;
+  if (hint == WOQ_B200_HINT_TENSOR_CORE) return true;
+  if (hint == WOQ_B200_HINT_STREAM) return false;
+  return m > 16;
+}
+
+int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
+                    const void* const* others, int32_t n_others, void* y, int64_t ldy,
+                    void* workspace, size_t workspace_bytes, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (m == 0) return WOQ_B200_OK;
+  if (!x || !y || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "x, y and workspace must be non-null");
+  if (m < 0) return fail(WOQ_B200_ERR_INVALID_ARG, "negative M");
+  if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
+  int need = 0;
+  switch (fusion) {
+    case WOQ_B200_FUSE_NONE: case WOQ_B200_FUSE_GELU_ERF: case WOQ_B200_FUSE_GELU_TANH:
+    case WOQ_B200_FUSE_RELU: case WOQ_B200_FUSE_SILU: need = 0; break;
+    case WOQ_B200_FUSE_ADD: case WOQ_B200_FUSE_MUL: need = 1; break;
+    case WOQ_B200_FUSE_ADD_ADD: need = 2; break;
+    case WOQ_B200_FUSE_SILU_MUL:
+      if (!c->gate_up)
+        return fail(WOQ_B200_ERR_INVALID_ARG, "silu_mul needs a context created with the gate/up layout");
+      need = 0;
+      break;
+    default: return fail(WOQ_B200_ERR_INVALID_ARG, "unexpected fusion type %#x", fusion);
+  }
+  if (n_others != need || (need > 0 && !others))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "fusion %#x takes %d extra tensors, got %d", fusion, need, n_others);
+  const void* o0 = need > 0 ? others[0] : nullptr;
+  const void* o1 = need > 1 ? others[1] : nullptr;
+  if ((need > 0 && !o0) || (need > 1 && !o1)) return fail(WOQ_B200_ERR_INVALID_ARG, "null extra tensor");
+  const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? c->desc.n / 2 : c->desc.n;
+  if (ldy < n_out) return fail(WOQ_B200_ERR_INVALID_ARG, "ldy smaller than the output width");
+  if (use_tc_path(c, m))
+    return run_tc(c, x, m, ldx, fusion, o0, o1, nullptr, nullptr, y, ldy, workspace, workspace_bytes,
+                  stream);
+  // tokens in slabs of 16 through the decode kernel
+  for (int64_t m0 = 0; m0 < m; m0 += 16) {
+    const int64_t mm = m - m0 < 16 ? m - m0 : 16;
+    const __nv_bfloat16* xs = static_cast<const __nv_bfloat16*>(x) + m0 * ldx;
+    __nv_bfloat16* ys = static_cast<__nv_bfloat16*>(y) + m0 * ldy;
+    const void* s0 = o0 ? static_cast<const __nv_bfloat16*>(o0) + m0 * ldy : nullptr;
+    const void* s1 = o1 ? static_cast<const __nv_bfloat16*>(o1) + m0 * ldy : nullptr;
+    if (int rc = run_decode(c, xs, mm, ldx, fusion, s0, s1, nullptr, nullptr, ys, ldy, workspace,
+                            workspace_bytes, stream))
+      return rc;
+  }
+  return WOQ_B200_OK;
+}
+
+int woq_b200_linear_scatter(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx,
+                            const int32_t* row_idx, const void* row_weight, void* out,
+                            int64_t ld_out, void* workspace, size_t workspace_bytes,
+                            void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (m == 0) return WOQ_B200_OK;
+  if (!x || !out || !workspace || !row_idx || !row_weight)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "null argument");
+  if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
+  if (ld_out < c->desc.n) return fail(WOQ_B200_ERR_INVALID_ARG, "ld_out smaller than N");
+  if (use_tc_path(c, m))
+    return run_tc(c, x, m, ldx, WOQ_B200_FUSE_SCALED_SCATTER_ADD, nullptr, nullptr, row_idx, row_weight,
+                  out, ld_out, workspace, workspace_bytes, stream);
+  for (int64_t m0 = 0; m0 < m; m0 += 16) {
+    const int64_t mm = m - m0 < 16 ? m - m0 : 16;
+    const __nv_bfloat16* xs = static_cast<const __nv_bfloat16*>(x) + m0 * ldx;
+    if (int rc = run_decode(c, xs, mm, ldx, WOQ_B200_FUSE_SCALED_SCATTER_ADD, nullptr, nullptr,
+                            row_idx + m0, static_cast<const __nv_bfloat16*>(row_weight) + m0, out,
+                            ld_out, workspace, workspace_bytes, stream))
+      return rc;
+  }
+  return WOQ_B200_OK;
+}
+
+int woq_b200_dump_dequant(const woq_b200_ctx* c, void* w_bf16, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!w_bf16) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  CUDA_TRY(woq::launch_dump_dequant_int4(c->wq, c->sz, static_cast<__nv_bfloat16*>(w_bf16),
+                                         (int)c->desc.n, (int)c->desc.k, c->tiles, c->kb_per_tile,
+                                         c->kb_per_group, c->groups, c->gate_up, stream));
+  return WOQ_B200_OK;
+}
+
+int woq_b200_int8_internals(const woq_b200_ctx* c, const void*, int64_t, int64_t, int8_t*, float*,
+                            int32_t*, void*, size_t, void*) {
+  if (int rc = check_ctx(c)) return rc;
+  return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 compute is not built yet");
+}
+
+int woq_b200_workspace_status(void* workspace, void* stream_) {
+  if (!workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "workspace is null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int h = 0;
+  CUDA_TRY(cudaMemcpyAsync(&h, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  if (h != 0) {
+    CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), stream));
+    return fail(WOQ_B200_ERR_DEVICE_WAIT, "a bounded in-kernel wait gave up (code %d)", h);
+  }
+  return WOQ_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,128 @@
+// Internal interface between the C ABI (woq_capi.cu) and the kernel translation units.
+#pragma once
+#include <cuda.h>
+
+#include "woq_common.cuh"
+
+namespace woq {
+
+// ---- INT4 decode (M <= 16) -----------------------------------------------------------
+struct DecodeParams {
+  const uint8_t* wq;       // tiled nibbles [tiles][kb_per_tile][2048]
+  const uint32_t* sz;      // [tiles][groups][64] {bf16 scale, bf16 128+zp}
+  const float* bias;       // [n] or null
+  const __nv_bfloat16* x;  // [m][ldx]
+  __nv_bfloat16* y;        // [m][ldy]  (scatter: [*][ldy])
+  const __nv_bfloat16* other0;
+  const __nv_bfloat16* other1;
+  const int32_t* row_idx;       // scatter epilogue
+  const __nv_bfloat16* row_w;   // scatter epilogue
+  float* partials;         // [2 * grid][16][64]
+  uint32_t* counters;      // [tiles], zero between calls
+  int* status;             // 0, or the code of the wait that gave up
+  int64_t ldx, ldy;
+  int m, n, n_out, k;
+  int tiles, kb_per_tile, kb_per_group, groups, gps;  // gps = max(1, 8 / kb_per_group)
+  int fusion, gate_up, stages;
+  int debug;  // experiment switches: 1 skip math, 2 skip x copies, 4 skip scale copies
+};
+
+struct DecodeShape {
+  int m, tiles, kb_per_tile;
+};
+
+__device__ __forceinline__ int decode_row_to_n(const DecodeParams& p, int tile, int row) {
+  if (p.gate_up) return row < 32 ? tile * 32 + row : p.n / 2 + tile * 32 + (row - 32);
+  return tile * kTileN + row;
+}
+
+int decode_int4_pick_grid(const DecodeShape& s, int num_sms);
+size_t decode_int4_partial_bytes(int grid);
+cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream);
+
+// ---- INT4 tensor-core path (any M up to 256 per launch) --------------------------------
+// Row layout: tiles of 128 output rows x 64 k, 4096 bytes each, [tile][k-block][half][row][16 B].
+// Word j' = 4 * half + j of a row holds k = 8 j' + 2 s in nibble s (bits 4s..4s+3) and
+// k = 8 j' + 2 s + 1 in nibble s + 4, so (w >> 4s) & 0x000f000f is the bf16x2 pair (k, k+1).
+// Scales: [tile][group][128] words, same {bf16 scale, bf16 128 + zp} format.
+constexpr int kTcTileN = 128;
+constexpr int kTcBlockBytes = kTcTileN * kBlockK / 2;  // 4096
+
+struct TcParams {
+  const uint8_t* wq;
+  const uint32_t* sz;
+  const float* bias;
+  __nv_bfloat16* y;
+  const __nv_bfloat16* other0;
+  const __nv_bfloat16* other1;
+  const int32_t* row_idx;
+  const __nv_bfloat16* row_w;
+  float* partials;     // [2 * grid][n_tok][128]
+  uint32_t* counters;  // [tiles]
+  int* status;
+  int64_t ldy;
+  int m, n, n_out, k;
+  int m0;              // first token row of this launch inside the x tensor map
+  int n_tok;           // token columns of the MMA (multiple of 16, <= 256)
+  int tiles, kb_per_tile, kbpg_shift, groups;
+  int kbs, stages;
+  int fusion, gate_up;
+};
+
+int tc_pick_grid(int tiles, int kb_per_tile, int num_sms);
+size_t tc_partial_bytes(int grid, int n_tok);
+cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream);
+
+__host__ __device__ inline int tc_tile_row_to_n(int n_total, int gate_up, int tile, int row) {
+  if (gate_up) return row < 64 ? tile * 64 + row : n_total / 2 + tile * 64 + (row - 64);
+  return tile * kTcTileN + row;
+}
+
+// ---- pack / unpack / dump ------------------------------------------------------------
+struct PackInt4Args {
+  const uint8_t* plain;  // [n][ceil(k/2)]
+  uint8_t* tiled;
+  int n, k, tiles, kb_per_tile, gate_up;
+  int tc;  // 0: 64-row fragment layout, 1: 128-row row layout
+};
+cudaError_t launch_pack_int4(const PackInt4Args& a, cudaStream_t stream);
+cudaError_t launch_unpack_int4(const uint8_t* tiled, uint8_t* plain, int n, int k, int tiles,
+                               int kb_per_tile, int gate_up, cudaStream_t stream);
+
+struct PackScaleArgs {
+  const void* scales;  // [n][groups] (or transposed [groups][n])
+  const void* zps;     // same shape or null
+  uint32_t* sz;        // [tiles][groups][64]
+  int* bad_zp;         // set to 1 if a zero point is not an integer in 0..127
+  int n, tiles, groups, gate_up;
+  int transposed;     // scales are [groups][n]
+  int zp_transposed;  // zero points are [groups][n]
+  int scale_dtype, zp_dtype, default_zp;
+  int tc;  // 0: [tiles64][groups][64] fragment order, 1: [tiles128][groups][128] row order
+};
+cudaError_t launch_pack_scales(const PackScaleArgs& a, cudaStream_t stream);
+
+cudaError_t launch_dump_dequant_int4(const uint8_t* tiled, const uint32_t* sz, __nv_bfloat16* w,
+                                     int n, int k, int tiles, int kb_per_tile, int kb_per_group,
+                                     int groups, int gate_up, cudaStream_t stream);
+cudaError_t launch_dump_dequant_int4_tc(const uint8_t* tiled, const uint32_t* sz, __nv_bfloat16* w,
+                                        int n, int k, int tiles, int kb_per_tile, int kbpg_shift,
+                                        int groups, int gate_up, cudaStream_t stream);
+
+// AWQ / GPTQ int32 checkpoints -> plain nibble layout [n][k/2]
+cudaError_t launch_awq_to_plain(const int32_t* qweight_kn8, uint8_t* plain, int n, int k,
+                                cudaStream_t stream);
+cudaError_t launch_gptq_to_plain(const int32_t* qweight_k8n, uint8_t* plain, int n, int k,
+                                 cudaStream_t stream);
+// packed int32 zero points [groups][n/8] -> u8 [n][groups]; gptq_plus_one adds 1 (GPTQ v1)
+cudaError_t launch_unpack_qzeros(const int32_t* qzeros, uint8_t* zps, int n, int groups, int awq,
+                                 int plus_one, cudaStream_t stream);
+
+__host__ __device__ inline int tile_row_to_n(int n_total, int gate_up, int tile, int row) {
+  if (gate_up) return row < 32 ? tile * 32 + row : n_total / 2 + tile * 32 + (row - 32);
+  return tile * kTileN + row;
+}
+
+void count_launch();
+
+}  // namespace woq

@@ -1,0 +1,292 @@
+"""ctypes binding of libwoq_b200.so (include/woq_b200.h) for torch CUDA tensors.
+
+This is the thin host layer the tests, the benchmark and the Python modules share.  There is
+no fallback: if the shared library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libwoq_b200.so")
+
+# constants of include/woq_b200.h
+DTYPE_INT8, DTYPE_INT4, DTYPE_NF4, DTYPE_FP8 = 1, 2, 3, 4
+LOWP_NONE, LOWP_FP16, LOWP_BF16, LOWP_INT8 = 0, 1, 2, 3
+ACT_NONE, ACT_PER_M, ACT_PER_M_SYM = -1, 2, 6
+FMT_PLAIN, FMT_GPTQ, FMT_AWQ = 0, 1, 2
+FUSE_NONE, FUSE_GELU_ERF, FUSE_GELU_TANH, FUSE_RELU, FUSE_SILU = 0, 1, 2, 3, 4
+FUSE_ADD, FUSE_ADD_ADD, FUSE_MUL, FUSE_SILU_MUL = 0x10, 0x20, 0x30, 0x100
+T_NONE, T_F32, T_F16, T_BF16, T_U8, T_S8, T_I32 = 0, 1, 2, 3, 4, 5, 6
+LAYOUT_GATE_UP = 1
+HINT_AUTO, HINT_TENSOR_CORE, HINT_STREAM = 0, 1, 2
+
+EXPORTS = [
+    "woq_b200_version",
+    "woq_b200_last_error",
+    "woq_b200_kernel_launches",
+    "woq_b200_ctx_create",
+    "woq_b200_ctx_destroy",
+    "woq_b200_ctx_desc",
+    "woq_b200_ctx_device_bytes",
+    "woq_b200_ctx_unpack",
+    "woq_b200_workspace_bytes",
+    "woq_b200_workspace_header_bytes",
+    "woq_b200_linear",
+    "woq_b200_linear_scatter",
+    "woq_b200_dump_dequant",
+    "woq_b200_int8_internals",
+    "woq_b200_workspace_status",
+]
+
+
+class Desc(ctypes.Structure):
+    _fields_ = [
+        ("n", ctypes.c_int64),
+        ("k", ctypes.c_int64),
+        ("weight_dtype", ctypes.c_int32),
+        ("group_size", ctypes.c_int32),
+        ("lowp_mode", ctypes.c_int32),
+        ("act_quant_mode", ctypes.c_int32),
+        ("weight_format", ctypes.c_int32),
+        ("scale_dtype", ctypes.c_int32),
+        ("zp_dtype", ctypes.c_int32),
+        ("bias_dtype", ctypes.c_int32),
+        ("layout_flags", ctypes.c_int32),
+        ("kernel_hint", ctypes.c_int32),
+    ]
+
+
+class WoqError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"libwoq_b200 status {code}: {msg}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the shared library once.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with "
+            "`python intel-extension-for-pytorch_b200/build_native.py` (no CPU fallback exists)"
+        )
+    L = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+    L.woq_b200_version.restype = ctypes.c_int
+    L.woq_b200_last_error.restype = ctypes.c_char_p
+    L.woq_b200_kernel_launches.restype = i64
+    L.woq_b200_ctx_create.argtypes = [ctypes.POINTER(Desc), vp, vp, vp, vp, vp, ctypes.POINTER(vp)]
+    L.woq_b200_ctx_destroy.argtypes = [vp]
+    L.woq_b200_ctx_desc.argtypes = [vp, ctypes.POINTER(Desc)]
+    L.woq_b200_ctx_device_bytes.argtypes = [vp]
+    L.woq_b200_ctx_device_bytes.restype = sz
+    L.woq_b200_ctx_unpack.argtypes = [vp, vp, vp]
+    L.woq_b200_workspace_bytes.argtypes = [vp, i64]
+    L.woq_b200_workspace_bytes.restype = sz
+    L.woq_b200_workspace_header_bytes.restype = sz
+    L.woq_b200_linear.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
+    L.woq_b200_linear_scatter.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
+    L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
+    L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
+    L.woq_b200_workspace_status.argtypes = [vp, vp]
+    _lib = L
+    return L
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise WoqError(rc, lib().woq_b200_last_error().decode())
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_TORCH_T = {
+    torch.float32: T_F32,
+    torch.float16: T_F16,
+    torch.bfloat16: T_BF16,
+    torch.uint8: T_U8,
+    torch.int8: T_S8,
+    torch.int32: T_I32,
+}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class Workspace:
+    """Scratch buffer shared by stream-ordered calls; zeroed once at creation."""
+
+    def __init__(self, nbytes: int, device):
+        self.buf = torch.zeros(max(int(nbytes), 1), dtype=torch.uint8, device=device)
+
+    @property
+    def nbytes(self) -> int:
+        return self.buf.numel()
+
+    def status(self) -> None:
+        _check(lib().woq_b200_workspace_status(self.buf.data_ptr(), _stream()))
+
+
+class WoqContext:
+    """Owns one packed layer (woq_b200_ctx)."""
+
+    def __init__(
+        self,
+        qweight: torch.Tensor,
+        scales: torch.Tensor,
+        zero_points: Optional[torch.Tensor],
+        bias: Optional[torch.Tensor],
+        n: int,
+        k: int,
+        weight_dtype: int = DTYPE_INT4,
+        group_size: int = -1,
+        lowp_mode: int = LOWP_BF16,
+        act_quant_mode: int = ACT_NONE,
+        weight_format: int = FMT_PLAIN,
+        layout_flags: int = 0,
+        kernel_hint: int = 0,
+    ):
+        for t in (qweight, scales, zero_points, bias):
+            if t is not None and (not t.is_cuda or not t.is_contiguous()):
+                raise ValueError("WoqContext wants contiguous CUDA tensors")
+        d = Desc(
+            n=n, k=k, weight_dtype=weight_dtype, group_size=group_size, lowp_mode=lowp_mode,
+            act_quant_mode=act_quant_mode, weight_format=weight_format,
+            scale_dtype=_TORCH_T[scales.dtype],
+            zp_dtype=T_NONE if zero_points is None else _TORCH_T[zero_points.dtype],
+            bias_dtype=T_NONE if bias is None else _TORCH_T[bias.dtype],
+            layout_flags=layout_flags, kernel_hint=kernel_hint,
+        )
+        self.n, self.k = n, k
+        self.device = qweight.device
+        self.layout_flags = layout_flags
+        self.weight_dtype = weight_dtype
+        self._h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _check(
+                lib().woq_b200_ctx_create(
+                    ctypes.byref(d), _ptr(qweight), _ptr(scales), _ptr(zero_points), _ptr(bias),
+                    _stream(), ctypes.byref(self._h),
+                )
+            )
+        self._ws: Optional[Workspace] = None
+
+    # -- lifetime ---------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().woq_b200_ctx_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def handle(self) -> int:
+        return self._h.value
+
+    def device_bytes(self) -> int:
+        return lib().woq_b200_ctx_device_bytes(self._h)
+
+    def workspace_bytes(self, m: int) -> int:
+        return lib().woq_b200_workspace_bytes(self._h, m)
+
+    def workspace(self, m: int) -> Workspace:
+        need = self.workspace_bytes(m)
+        if self._ws is None or self._ws.nbytes < need:
+            self._ws = Workspace(need, self.device)
+        return self._ws
+
+    # -- compute ------------------------------------------------------------------------
+    def linear(
+        self,
+        x: torch.Tensor,
+        fusion: int = FUSE_NONE,
+        others: Sequence[torch.Tensor] = (),
+        out: Optional[torch.Tensor] = None,
+        workspace: Optional[Workspace] = None,
+    ) -> torch.Tensor:
+        if x.dtype != torch.bfloat16 or not x.is_cuda:
+            raise ValueError("x must be a bf16 CUDA tensor")
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        n_out = self.n // 2 if fusion == FUSE_SILU_MUL else self.n
+        if out is None:
+            out = torch.empty((m, n_out), dtype=torch.bfloat16, device=x.device)
+        ws = workspace or self.workspace(m)
+        oth = [o.reshape(m, n_out).contiguous() for o in others]
+        arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
+        with torch.cuda.device(self.device):
+            _check(
+                lib().woq_b200_linear(
+                    self._h, x2.data_ptr(), m, x2.stride(0), fusion, arr, len(oth),
+                    out.data_ptr(), out.stride(0), ws.buf.data_ptr(), ws.nbytes, _stream(),
+                )
+            )
+        return out.reshape(*x.shape[:-1], n_out)
+
+    def linear_scatter(self, x, row_idx, row_weight, out, workspace=None):
+        x2 = x.reshape(-1, x.shape[-1])
+        m = x2.shape[0]
+        ws = workspace or self.workspace(m)
+        with torch.cuda.device(self.device):
+            _check(
+                lib().woq_b200_linear_scatter(
+                    self._h, x2.data_ptr(), m, x2.stride(0), row_idx.data_ptr(),
+                    row_weight.data_ptr(), out.data_ptr(), out.stride(0), ws.buf.data_ptr(),
+                    ws.nbytes, _stream(),
+                )
+            )
+        return out
+
+    def unpack(self) -> torch.Tensor:
+        if self.weight_dtype == DTYPE_INT4:
+            out = torch.empty((self.n, (self.k + 1) // 2), dtype=torch.uint8, device=self.device)
+        else:
+            out = torch.empty((self.n, self.k), dtype=torch.int8, device=self.device)
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_ctx_unpack(self._h, out.data_ptr(), _stream()))
+        return out
+
+    def dump_dequant(self) -> torch.Tensor:
+        out = torch.empty((self.n, self.k), dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_dump_dequant(self._h, out.data_ptr(), _stream()))
+        return out
+
+    def int8_internals(self, x: torch.Tensor):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        m = x2.shape[0]
+        qa = torch.empty((m, self.k), dtype=torch.int8, device=self.device)
+        sa = torch.empty((m,), dtype=torch.float32, device=self.device)
+        acc = torch.empty((m, self.n), dtype=torch.int32, device=self.device)
+        ws = self.workspace(m)
+        with torch.cuda.device(self.device):
+            _check(
+                lib().woq_b200_int8_internals(
+                    self._h, x2.data_ptr(), m, x2.stride(0), qa.data_ptr(), sa.data_ptr(),
+                    acc.data_ptr(), ws.buf.data_ptr(), ws.nbytes, _stream(),
+                )
+            )
+        return qa, sa, acc
+
+
+def kernel_launches() -> int:
+    return int(lib().woq_b200_kernel_launches())

@@ -1,0 +1,68 @@
+"""CPU-only: the C-ABI library builds, loads, and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "woq_b200.h")
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location(
+        "build_native", os.path.join(ROOT, "intel-extension-for-pytorch_b200", "build_native.py")
+    )
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build()
+
+
+def declared_symbols():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(woq_b200_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_header_declares_entry_points():
+    syms = declared_symbols()
+    for must in ("woq_b200_ctx_create", "woq_b200_linear", "woq_b200_ctx_unpack",
+                 "woq_b200_dump_dequant", "woq_b200_int8_internals"):
+        assert must in syms
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    lib = ctypes.CDLL(built_lib)
+    for s in declared_symbols():
+        assert hasattr(lib, s), f"{s} declared in include/woq_b200.h but not exported"
+    lib.woq_b200_version.restype = ctypes.c_int
+    assert lib.woq_b200_version() >= 100
+
+
+def test_python_binding_lists_the_same_symbols(built_lib):
+    from ipex_b200 import _capi
+
+    assert sorted(_capi.EXPORTS) == declared_symbols()
+    _capi.lib()
+
+
+def test_bad_arguments_are_rejected_without_a_gpu(built_lib):
+    """Argument checks run on the host before any CUDA call."""
+    from ipex_b200 import _capi
+
+    L = _capi.lib()
+    h = ctypes.c_void_p()
+    d = _capi.Desc(n=64, k=64, weight_dtype=_capi.DTYPE_INT4, group_size=0)
+    rc = L.woq_b200_ctx_create(ctypes.byref(d), 16, 16, None, None, None, ctypes.byref(h))
+    assert rc == 1 and b"group_size" in L.woq_b200_last_error()
+    d = _capi.Desc(n=64, k=64, weight_dtype=_capi.DTYPE_NF4, group_size=64,
+                   scale_dtype=_capi.T_F32)
+    rc = L.woq_b200_ctx_create(ctypes.byref(d), 16, 16, None, None, None, ctypes.byref(h))
+    assert rc == 2
+    assert L.woq_b200_ctx_destroy(None) == 1
+    assert L.woq_b200_linear(None, None, 1, 64, 0, None, 0, None, 64, None, 0, None) == 1
+    fake = (ctypes.c_uint64 * 64)()
+    assert L.woq_b200_ctx_destroy(ctypes.cast(fake, ctypes.c_void_p)) == 5
