@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the INT4 weight-only-quantised linear hot path.
+
+Workload (synthetic, seeded): the linears of a Llama-3-70B-architecture decoder, INT4
+asymmetric group-128, 80 layers x {QKV 10240x8192, o_proj 8192x8192, gate_up 57344x8192 with
+the silu*mul epilogue, down_proj 8192x28672}, decode batch M tokens (default 1).  A step is one
+token step through all 320 linears.  With N GPUs the layers are tensor-parallel: QKV / gate_up
+sharded along N with an all-gather, o_proj / down_proj sharded along K with an all-reduce (NCCL).
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nproc-per-node 8 ... bench.py --gpus 8 --steps 20 --warmup 3
+    python bench.py --impl reference          # the CPU restatement of the reference kernel
+
+Prints ONE JSON line (rank 0).  `value` = weight bytes streamed per second over all GPUs
+(inputs resident in HBM); `e2e` = the same through the public module API with the step's
+activations copied from pinned host memory and the result copied back every step.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG_DIR = os.path.join(ROOT, "intel-extension-for-pytorch_b200")
+for _p in (ROOT, PKG_DIR):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+HIDDEN, QKV_N, FFN, LAYERS, GROUP = 8192, 10240, 28672, 80, 128
+METRIC = "int4_woq_linear_weight_GBps_decode"
+UNIT = "GB/s"
+
+
+def weight_bytes(n, k, g=GROUP):
+    """Algorithmic weight bytes of one INT4 linear: nibbles + fp16 scale + u8 zero point."""
+    return n * k // 2 + 3 * n * (k // g)
+
+
+def layer_shapes(p):
+    """(name, N_local, K_local, parallel kind) for one rank of a p-way tensor-parallel layer."""
+    return [
+        ("qkv", QKV_N // p, HIDDEN, "col"),
+        ("o_proj", HIDDEN, HIDDEN // p, "row"),
+        ("gate_up", 2 * FFN // p, HIDDEN, "col"),
+        ("down_proj", HIDDEN, FFN // p, "row"),
+    ]
+
+
+def full_layer_weight_bytes():
+    return sum(weight_bytes(n, k) for _, n, k, _ in layer_shapes(1))
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6),
+                              ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the CPU restatement of the reference's WOQ kernel on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_baseline(m, passes=3):
+    """Times oracle/woq_oracle_c.c (OpenMP, all host threads) on one of the 80 layers."""
+    import numpy as np
+
+    from oracle import woq_oracle_c as OC
+
+    rng = np.random.default_rng(0)
+    layers = []
+    for name, n, k, _ in layer_shapes(1):
+        qw = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+        s = (rng.random((n, k // GROUP), dtype=np.float32) * 0.01 + 0.001).astype(np.float16).astype(np.float32)
+        z = rng.integers(0, 16, (n, k // GROUP)).astype(np.float32)
+        layers.append((name, OC.Layer(qw, n, k, s, z, None, GROUP), n, k))
+    xs = {k: (rng.standard_normal((m, k)).astype(np.float32)) for k in (HIDDEN, FFN)}
+    for _, L, n, k in layers:  # warm-up pass
+        L.linear_bf16(xs[k], 0x100 if n == 2 * FFN else 0)
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        for _, L, n, k in layers:
+            L.linear_bf16(xs[k], 0x100 if n == 2 * FFN else 0)
+    dt = (time.perf_counter() - t0) / passes
+    gbps = full_layer_weight_bytes() / dt / 1e9
+    return {"value": gbps, "unit": UNIT, "cores": OC.max_threads(), "kind": "port",
+            "sample": f"1 of {LAYERS} layers (4 linears, {full_layer_weight_bytes() / 1e6:.0f} MB of "
+                      f"weights), M={m}, {passes} passes after 1 warm-up, blocked-layout C port of "
+                      "the reference kernel with OpenMP"}, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), args.warmup
+    passes = max(1, min(steps, 5))
+    cb, dt = cpu_baseline(args.m, passes=passes)
+    line = {
+        "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": dt * 1e3 * LAYERS, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "reference",
+        "config": {"workload": "llama3-70b linears, INT4 asym g128, decode", "m": args.m,
+                   "layers": LAYERS, "note": "each step = a bounded sample (1 layer) of the workload; "
+                   "ms_per_step extrapolates to 80 layers"},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def build_layers(torch, capi, quant, p, rank, n_layers, device):
+    """Random-init N(0, 0.02) weights, quantised on the GPU, packed into contexts."""
+    layers = []
+    for l in range(n_layers):
+        row = {}
+        for name, n, k, kind in layer_shapes(p):
+            g = torch.Generator(device=device).manual_seed(1000 * l + 17 * rank + len(row))
+            w = torch.randn((n, k), device=device, generator=g) * 0.02
+            qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
+            del w
+            flags = capi.LAYOUT_STREAM_ONLY | (capi.LAYOUT_GATE_UP if name == "gate_up" else 0)
+            row[name] = capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP,
+                                        capi.LOWP_BF16, layout_flags=flags)
+            del qw, s, z
+        layers.append(row)
+    torch.cuda.synchronize()
+    return layers
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from ipex_b200 import _capi as capi
+    from ipex_b200 import quantization as quant
+
+    p = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert p == args.gpus or p == 1, f"--gpus {args.gpus} but WORLD_SIZE={p}"
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if p > 1:
+        dist.init_process_group("nccl", device_id=device)
+    capi.lib()
+    m = args.m
+    n_layers = args.layers
+    layers = build_layers(torch, capi, quant, p, rank, n_layers, device)
+    ws = capi.Workspace(layers[0]["qkv"].workspace_bytes(m), device)
+
+    bf = dict(dtype=torch.bfloat16, device=device)
+    hidden = torch.randn((m, HIDDEN), **bf)
+    resid = torch.randn((m, HIDDEN), **bf)
+    attn_in = torch.randn((m, HIDDEN), **bf)            # what attention would hand to o_proj
+    qkv_local = torch.empty((m, QKV_N // p), **bf)
+    qkv_full = torch.empty((p, m, QKV_N // p), **bf) if p > 1 else None
+    act_local = torch.empty((m, FFN // p), **bf)
+    act_full = torch.empty((p, m, FFN // p), **bf) if p > 1 else None
+    o_out = torch.empty((m, HIDDEN), **bf)
+    d_out = torch.empty((m, HIDDEN), **bf)
+    attn_slice = attn_in[:, rank * (HIDDEN // p):(rank + 1) * (HIDDEN // p)]
+
+    launches_per_step = [0]
+
+    def step(x):
+        n_launch = 0
+        for L in layers:
+            L["qkv"].linear(x, out=qkv_local, workspace=ws)
+            if p > 1:
+                dist.all_gather_into_tensor(qkv_full, qkv_local)
+            if p == 1:
+                L["o_proj"].linear(attn_slice, capi.FUSE_ADD, [resid], out=o_out, workspace=ws)
+            else:
+                L["o_proj"].linear(attn_slice, out=o_out, workspace=ws)
+                dist.all_reduce(o_out)
+                o_out.add_(resid)
+            L["gate_up"].linear(o_out, capi.FUSE_SILU_MUL, out=act_local, workspace=ws)
+            if p > 1:
+                dist.all_gather_into_tensor(act_full, act_local)
+            if p == 1:
+                L["down_proj"].linear(act_local, capi.FUSE_ADD, [resid], out=d_out, workspace=ws)
+            else:
+                L["down_proj"].linear(act_local, out=d_out, workspace=ws)
+                dist.all_reduce(d_out)
+                d_out.add_(resid)
+            n_launch += 4
+        launches_per_step[0] = n_launch
+        return d_out
+
+    # eager warm-up (also initialises NCCL), then capture one step in a CUDA graph
+    step(hidden)
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream(device=device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step(hidden)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step(hidden)
+        except Exception as e:  # pragma: no cover - depends on the NCCL build
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); running eagerly",
+                      file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step(hidden)
+
+    def barrier():
+        if p > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        run_step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    if p > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    total_w = full_layer_weight_bytes() * n_layers  # all ranks together stream the whole model
+    value = total_w / (ms_per_step * 1e-3) / 1e9
+    ws.status()
+
+    # ---- kernel-only timing for the roofline (linears alone, no collectives) --------------
+    def linears_only():
+        for L in layers:
+            L["qkv"].linear(hidden, out=qkv_local, workspace=ws)
+            L["o_proj"].linear(attn_slice, capi.FUSE_ADD if p == 1 else 0, [resid] if p == 1 else [],
+                               out=o_out, workspace=ws)
+            L["gate_up"].linear(o_out, capi.FUSE_SILU_MUL, out=act_local, workspace=ws)
+            L["down_proj"].linear(act_local, capi.FUSE_ADD if p == 1 else 0, [resid] if p == 1 else [],
+                                  out=d_out, workspace=ws)
+
+    kgraph = torch.cuda.CUDAGraph()
+    linears_only()
+    torch.cuda.synchronize()
+    with torch.cuda.graph(kgraph):
+        linears_only()
+    for _ in range(3):
+        kgraph.replay()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(3, min(args.steps, 10))
+    k0.record()
+    for _ in range(reps):
+        kgraph.replay()
+    k1.record()
+    torch.cuda.synchronize()
+    n_launch = launches_per_step[0]
+    kernel_ms = k0.elapsed_time(k1) / reps / n_launch
+    local_bytes = sum(weight_bytes(n, k) + 2 * m * k + 2 * m * (n // 2 if name == "gate_up" else n)
+                      + (2 * m * n if (p == 1 and kind == "row") else 0)
+                      for name, n, k, kind in layer_shapes(p)) * n_layers
+    hbm_peak, _, peak_src = peaks()
+    achieved = local_bytes / n_launch / (kernel_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                "frac": achieved / hbm_peak, "traffic": args.traffic,
+                "kernel": "woq_int4_decode_kernel", "peak_source": peak_src,
+                "avg_launch_us": kernel_ms * 1e3,
+                "algorithmic_bytes_per_launch": local_bytes / n_launch}
+
+    # ---- end to end: host activations in, host result out, through the module API ---------
+    x_host = torch.randn((m, HIDDEN)).bfloat16().pin_memory()
+    y_host = torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        hidden.copy_(x_host, non_blocking=True)
+        run_step()
+        y_host.copy_(d_out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    if p > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": total_w / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": m * HIDDEN * 2,
+           "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": e2e_s * 1e3}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": p, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama3-70b linears (QKV 10240x8192, o 8192x8192, gate_up 57344x8192 "
+                                   "silu_mul, down 8192x28672), INT4 asym g128, lowp BF16, decode",
+                       "m": m, "layers": n_layers, "parallelism": f"tp{p}",
+                       "l2": "weights (35.8 GB per step over all ranks) exceed L2; no flush needed",
+                       "cuda_graph": graph is not None},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": n_launch * args.steps,
+            "clocks": clocks,
+        }
+        if p == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = cpu_baseline(m)
+        print(json.dumps(line))
+    if p > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="decode batch (tokens per step)")
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per launch from an ncu capture (profiles/)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -81,12 +81,21 @@ extern "C" {
 #define WOQ_B200_T_I32 6 /* packed 4-bit zero points of GPTQ/AWQ checkpoints */
 
 #define WOQ_B200_LAYOUT_GATE_UP 0x1
+/* An INT4 context normally keeps the weight in two tilings (streaming kernel / tensor-core
+ * kernel).  These flags keep only one, halving device memory; calls then always use the
+ * kernel whose tiling exists (the streaming kernel takes large M in 16-token passes). */
+#define WOQ_B200_LAYOUT_STREAM_ONLY 0x2
+#define WOQ_B200_LAYOUT_TC_ONLY 0x4
 
-/* kernel selection for INT4 weights (the results of the two kernels agree within the output
- * tolerance; the tensor-core kernel reproduces the bf16-rounded dequantised weights exactly) */
-#define WOQ_B200_HINT_AUTO 0
-#define WOQ_B200_HINT_TENSOR_CORE 1 /* tcgen05 kernel for every M                         */
-#define WOQ_B200_HINT_STREAM 2      /* register-dequant streaming kernel, 16 tokens a pass */
+/* kernel selection for INT4 weights.  AUTO, TENSOR_CORE and STREAM all multiply by the
+ * bf16-rounded dequantised weights bf16((q - zp) * bf16(scale)) and differ only in summation
+ * order.  STREAM_FAST applies scale and zero point after the per-block sum (what the
+ * reference's small-M kernel does, csrc/cpu/aten/utils/woq.h:784-951): cheaper, within the
+ * output tolerance, but not the same rounding as the tile dequantiser. */
+#define WOQ_B200_HINT_AUTO 0        /* streaming kernel for M <= 16, tcgen05 kernel above      */
+#define WOQ_B200_HINT_TENSOR_CORE 1 /* tcgen05 kernel for every M                              */
+#define WOQ_B200_HINT_STREAM 2      /* register-dequant streaming kernel, 16 tokens a pass     */
+#define WOQ_B200_HINT_STREAM_FAST 3 /* streaming kernel, scale applied after the k-block sum   */
 
 /* Description of one quantised linear layer: the arguments of
  * ipex_prepack::weight_only_qlinear_prepack

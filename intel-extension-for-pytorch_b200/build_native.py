@@ -43,7 +43,7 @@ def _digest():
         if os.path.isfile(p) and n.endswith((".cu", ".cuh", ".h")):
             h.update(n.encode())
             h.update(open(p, "rb").read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + os.environ.get("WOQ_NVCC_EXTRA", "").split()).encode())
     return h.hexdigest()
 
 
@@ -54,7 +54,8 @@ def build(force=False, verbose=False):
         if open(STAMP).read().strip() == digest:
             return LIB
     os.makedirs(OUT_DIR, exist_ok=True)
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else [])
+    extra = os.environ.get("WOQ_NVCC_EXTRA", "").split()
+    cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else [])
     cmd += [os.path.join(CSRC, s) for s in CUDA_SOURCES] + ["-o", LIB]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:

@@ -182,10 +182,18 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
       return cleanup(fail(WOQ_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__))); \
   } while (0)
 
-  CUDA_TRY_C(cudaMalloc(&c->wq, c->wq_bytes));
-  CUDA_TRY_C(cudaMalloc(&c->sz, c->sz_bytes));
-  CUDA_TRY_C(cudaMalloc(&c->wq_tc, c->wq_tc_bytes));
-  CUDA_TRY_C(cudaMalloc(&c->sz_tc, c->sz_tc_bytes));
+  const bool want_stream = !(d->layout_flags & WOQ_B200_LAYOUT_TC_ONLY);
+  const bool want_tc = !(d->layout_flags & WOQ_B200_LAYOUT_STREAM_ONLY);
+  if (!want_stream) c->wq_bytes = c->sz_bytes = 0;
+  if (!want_tc) c->wq_tc_bytes = c->sz_tc_bytes = 0;
+  if (want_stream) {
+    CUDA_TRY_C(cudaMalloc(&c->wq, c->wq_bytes));
+    CUDA_TRY_C(cudaMalloc(&c->sz, c->sz_bytes));
+  }
+  if (want_tc) {
+    CUDA_TRY_C(cudaMalloc(&c->wq_tc, c->wq_tc_bytes));
+    CUDA_TRY_C(cudaMalloc(&c->sz_tc, c->sz_tc_bytes));
+  }
   CUDA_TRY_C(cudaMalloc(&d_flag, sizeof(int)));
   CUDA_TRY_C(cudaMemsetAsync(d_flag, 0, sizeof(int), stream));
 
@@ -215,10 +223,14 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
       // tmp_zp is [N][groups]; scales stay transposed -> handled by two passes below
     }
   }
-  woq::PackInt4Args pa{plain, c->wq, (int)d->n, (int)d->k, c->tiles, c->kb_per_tile, gate_up, 0};
-  CUDA_TRY_C(woq::launch_pack_int4(pa, stream));
-  woq::PackInt4Args pt{plain, c->wq_tc, (int)d->n, (int)d->k, c->tiles_tc, c->kb_per_tile, gate_up, 1};
-  CUDA_TRY_C(woq::launch_pack_int4(pt, stream));
+  if (want_stream) {
+    woq::PackInt4Args pa{plain, c->wq, (int)d->n, (int)d->k, c->tiles, c->kb_per_tile, gate_up, 0};
+    CUDA_TRY_C(woq::launch_pack_int4(pa, stream));
+  }
+  if (want_tc) {
+    woq::PackInt4Args pt{plain, c->wq_tc, (int)d->n, (int)d->k, c->tiles_tc, c->kb_per_tile, gate_up, 1};
+    CUDA_TRY_C(woq::launch_pack_int4(pt, stream));
+  }
 
   woq::PackScaleArgs sa{};
   sa.scales = scales;
@@ -235,11 +247,11 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
   sa.zp_dtype = zp_dtype;
   sa.default_zp = 8;  // symmetric INT4 is stored as q + 8
   sa.tc = 0;
-  CUDA_TRY_C(woq::launch_pack_scales(sa, stream));
+  if (want_stream) CUDA_TRY_C(woq::launch_pack_scales(sa, stream));
   sa.sz = c->sz_tc;
   sa.tiles = c->tiles_tc;
   sa.tc = 1;
-  CUDA_TRY_C(woq::launch_pack_scales(sa, stream));
+  if (want_tc) CUDA_TRY_C(woq::launch_pack_scales(sa, stream));
 
   if (bias) {
     CUDA_TRY_C(cudaMalloc(&c->bias, static_cast<size_t>(d->n) * sizeof(float)));
@@ -288,6 +300,8 @@ int woq_b200_ctx_unpack(const woq_b200_ctx* c, void* qweight_plain, void* stream
   if (int rc = check_ctx(c)) return rc;
   if (!qweight_plain) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!c->wq)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "unpack needs the streaming layout (context was packed tensor-core only)");
   CUDA_TRY(woq::launch_unpack_int4(c->wq, static_cast<uint8_t*>(qweight_plain), (int)c->desc.n,
                                    (int)c->desc.k, c->tiles, c->kb_per_tile, c->gate_up, stream));
   return WOQ_B200_OK;
@@ -334,11 +348,12 @@ static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t l
   p.k = (int)c->desc.k;
   p.tiles = c->tiles;
   p.kb_per_tile = c->kb_per_tile;
-  p.kb_per_group = c->kb_per_group;
+  p.kbpg_shift = c->kbpg_shift;
   p.groups = c->groups;
   p.gps = c->kb_per_group >= 8 ? 1 : 8 / c->kb_per_group;
   p.fusion = fusion;
   p.gate_up = c->gate_up;
+  p.exact = c->desc.kernel_hint == WOQ_B200_HINT_STREAM_FAST ? 0 : 1;
   woq::DecodeShape shape{(int)m, c->tiles, c->kb_per_tile};
   const int grid = woq::decode_int4_pick_grid(shape, c->num_sms);
   CUDA_TRY(woq::launch_decode_int4(p, grid, stream));
@@ -437,9 +452,11 @@ static bool use_tc_path(const woq_b200_ctx* c, int64_t m) {
     const char* e = getenv("WOQ_B200_KERNEL_HINT");
     env = e ? atoi(e) : 0;
   }
+  if (!c->wq_tc) return false;  // context packed for the streaming kernel only
+  if (!c->wq) return true;      // context packed for the tensor-core kernel only
   const int hint = c->desc.kernel_hint ? c->desc.kernel_hint : env;
   if (hint == WOQ_B200_HINT_TENSOR_CORE) return true;
-  if (hint == WOQ_B200_HINT_STREAM) return false;
+  if (hint == WOQ_B200_HINT_STREAM || hint == WOQ_B200_HINT_STREAM_FAST) return false;
   return m > 16;
 }
 
@@ -520,9 +537,17 @@ int woq_b200_dump_dequant(const woq_b200_ctx* c, void* w_bf16, void* stream_) {
   if (int rc = check_ctx(c)) return rc;
   if (!w_bf16) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  CUDA_TRY(woq::launch_dump_dequant_int4(c->wq, c->sz, static_cast<__nv_bfloat16*>(w_bf16),
-                                         (int)c->desc.n, (int)c->desc.k, c->tiles, c->kb_per_tile,
-                                         c->kb_per_group, c->groups, c->gate_up, stream));
+  if (c->wq_tc) {
+    // the routine the tensor-core kernel uses for its tiles
+    CUDA_TRY(woq::launch_dump_dequant_int4_tc(c->wq_tc, c->sz_tc, static_cast<__nv_bfloat16*>(w_bf16),
+                                              (int)c->desc.n, (int)c->desc.k, c->tiles_tc,
+                                              c->kb_per_tile, c->kbpg_shift, c->groups, c->gate_up,
+                                              stream));
+  } else {
+    CUDA_TRY(woq::launch_dump_dequant_int4(c->wq, c->sz, static_cast<__nv_bfloat16*>(w_bf16),
+                                           (int)c->desc.n, (int)c->desc.k, c->tiles, c->kb_per_tile,
+                                           c->kb_per_group, c->groups, c->gate_up, stream));
+  }
   return WOQ_B200_OK;
 }
 

@@ -108,7 +108,11 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef WOQ_USE_TEST_WAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -124,18 +128,22 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Upper bound for any in-kernel wait.  A wait that runs out records `code` in *status,
 // raises the block-wide abort flag, and returns false; from then on every wait in the
 // block returns immediately so that all threads still reach the end of the kernel.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// Time is taken from the SM cycle counter and only looked at every 1024 polls: the common
+// case (the barrier flips within a few polls) costs nothing beyond the polls themselves.
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_test(bar, parity)) return true;
-  if (*abort_flag) return false;
-  const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (!mbar_test(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
+    if ((++spins & 1023u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

@@ -5,16 +5,16 @@
 // activations are the B operand (N = tokens, 16..256), so one CTA tile is y^T[128 rows x
 // tokens] accumulated in fp32 in TMEM over the whole K of its share.
 //
-//   warp 8      producer: bulk copies of packed nibbles + group scales, TMA tile loads of x
+//   warp 16     producer: bulk copies of packed nibbles + group scales, TMA tile loads of x
 //               (128-byte swizzled K-major rows) - all completing on mbarriers;
-//   warps 0-7   dequantise: thread = output row.  Two 128-bit shared loads give the row's 64
+//   warps 0-15  dequantise: thread = output row.  Two 128-bit shared loads give the row's 64
 //               nibbles of a k-block; each becomes bf16((q - zp) * bf16(scale)) exactly (the
 //               reference's tile dequantiser) and the 32 packed registers go straight to
 //               TMEM with one tcgen05.st - the dequantised tile never touches shared memory.
-//               Even / odd k-blocks alternate between the two warpgroups;
-//   warp 9      one thread issues tcgen05.mma (A from TMEM, B from shared memory) and
+//               Consecutive k-blocks go round-robin to the four warpgroups;
+//   warp 17     one thread issues tcgen05.mma (A from TMEM, B from shared memory) and
 //               releases A slots / x stages / the accumulator with tcgen05.commit;
-//   warps 0-7   epilogue at the end of a tile segment: tcgen05.ld the accumulators, then
+//   warps 0-15  epilogue at the end of a tile segment: tcgen05.ld the accumulators, then
 //               either the fused post-op and store, or - when the CTA saw only part of K -
 //               a partial tile in the workspace that the last contributor sums in a fixed
 //               order.
@@ -28,11 +28,14 @@ namespace woq {
 
 namespace {
 
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 16;
+constexpr int kWarpGroups = kDequantWarps / 4;
 constexpr int kTcThreads = (kDequantWarps + 2) * 32;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1;
 constexpr int kASlots = 8;           // 32 TMEM columns each (one k-block of bf16 A)
 constexpr int kDCol0 = 0;            // accumulator columns [0, 256)
+constexpr int kDCols = 256;
+constexpr int kMaxAcc = 8;           // independent accumulators for small token counts
 constexpr int kACol0 = 256;          // A slots in columns [256, 512)
 constexpr int kTmemCols = 512;
 constexpr int kMaxTcStages = 8;
@@ -82,6 +85,13 @@ __device__ __forceinline__ void tc_store(const TcParams& p, int tile, int row, i
   p.y[o] = __float2bfloat16_rn(r);
 }
 
+// Timeline probe for experiments (debug bit 64): CTA 0 writes cycle stamps of its first 64
+// stages into the partial-tile area, [role][stage][4].
+__device__ __forceinline__ void tc_stamp(const TcParams& p, int role, int stage, int k) {
+  if ((p.debug & 64) && blockIdx.x == 0 && stage < 64)
+    reinterpret_cast<long long*>(p.partials)[(role * 64 + stage) * 4 + k] = clock64();
+}
+
 __global__ void __launch_bounds__(kTcThreads, 1)
     woq_int4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -90,7 +100,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   const int w_stage_bytes = p.kbs * kTcBlockBytes + (p.kbs + 1) * 512;
   uint8_t* x_stages = smem + kTcHeaderBytes;
   uint8_t* w_stages = x_stages + static_cast<size_t>(p.stages) * x_stage_bytes;
-  float* fin = reinterpret_cast<float*>(w_stages + static_cast<size_t>(p.stages) * w_stage_bytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (smem_u32(smem) & 1023u) {  // swizzled tiles need a 1024-byte aligned base
@@ -109,7 +118,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       mbar_init(&hdr->x_empty[s], 1);
     }
     for (int s = 0; s < kASlots; ++s) {
-      mbar_init(&hdr->a_full[s], 4);
+      mbar_init(&hdr->a_full[s], kDequantWarps);
       mbar_init(&hdr->a_empty[s], 1);
     }
     mbar_init(&hdr->d_full, 1);
@@ -128,10 +137,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   const uint32_t tmem_base = hdr->tmem_base;
   volatile int* abort_flag = &hdr->abort_flag;
 
-  // every role walks the same sequence of stages
+  // every role walks the same sequence of stages; a stage is up to `kbs` k-blocks of one tile.
+  // Stage `it` uses pipeline slot it % stages and A group it % a_groups (kbs * 32 TMEM columns).
   int tile = static_cast<int>(b_begin / p.kb_per_tile);
   int kb0 = static_cast<int>(b_begin % p.kb_per_tile);
   int64_t b = b_begin;
+  int slot = 0;
+  uint32_t phase = 0;       // parity of the current use of `slot`
+  int agrp = 0;
+  uint32_t aphase = 0;      // parity of the current use of `agrp`
+  const int a_groups = kASlots / p.kbs;  // 2, 4 or 8
   auto stage_len = [&]() {
     int nkb = p.kb_per_tile - kb0;
     if (nkb > p.kbs) nkb = p.kbs;
@@ -145,19 +160,28 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       kb0 = 0;
       ++tile;
     }
+    if (++slot == p.stages) {
+      slot = 0;
+      phase ^= 1;
+    }
+    if (++agrp == a_groups) {
+      agrp = 0;
+      aphase ^= 1;
+    }
   };
 
   if (warp == kProducerWarp) {
     if (lane == 0) {
-      for (int it = 0; b < b_end; ++it) {
+      int pst = 0;
+      while (b < b_end) {
         const int nkb = stage_len();
-        const int slot = it % p.stages;
-        const uint32_t phase = (it / p.stages) & 1;
         uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
         uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
         const int g0 = kb0 >> p.kbpg_shift;
         const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
+        tc_stamp(p, 0, pst, 0);
         mbar_wait(&hdr->w_empty[slot], phase ^ 1, abort_flag, p.status, 11);
+        tc_stamp(p, 0, pst, 1);
         mbar_arrive_expect_tx(&hdr->w_full[slot], nkb * kTcBlockBytes + ng * 512);
         bulk_g2s(ws, p.wq + (static_cast<size_t>(tile) * p.kb_per_tile + kb0) * kTcBlockBytes,
                  nkb * kTcBlockBytes, &hdr->w_full[slot]);
@@ -165,44 +189,68 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                  p.sz + (static_cast<size_t>(tile) * p.groups + g0) * kTcTileN, ng * 512,
                  &hdr->w_full[slot]);
         mbar_wait(&hdr->x_empty[slot], phase ^ 1, abort_flag, p.status, 12);
-        mbar_arrive_expect_tx(&hdr->x_full[slot], nkb * p.n_tok * 128);
-        for (int j = 0; j < nkb; ++j)
-          tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->x_full[slot]);
+        tc_stamp(p, 0, pst, 2);
+        if (p.debug & 8) {
+          mbar_arrive(&hdr->x_full[slot]);
+        } else {
+          mbar_arrive_expect_tx(&hdr->x_full[slot], nkb * p.n_tok * 128);
+          for (int j = 0; j < nkb; ++j)
+            tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->x_full[slot]);
+        }
+        tc_stamp(p, 0, pst, 3);
+        ++pst;
         advance(nkb);
       }
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
+      // One thread issues every MMA of the CTA, so this loop is kept free of divisions and
+      // address recomputation: descriptors advance by constants.
       const uint32_t idesc = umma_idesc(p.n_tok, /*bf16*/ 1, /*f32*/ 1);
-      int kbc = 0, seg = 0;
-      bool seg_start = true;
-      for (int it = 0; b < b_end; ++it) {
+      const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
+      const uint32_t x_base_lo = (smem_u32(x_stages) & 0x3FFFFu) >> 4;
+      const uint32_t x_stage_lo = static_cast<uint32_t>(x_stage_bytes) >> 4;
+      const uint32_t x_blk_lo = static_cast<uint32_t>(p.n_tok * 128) >> 4;
+      const uint32_t d_addr = tmem_base + kDCol0;
+      uint32_t seg = 0;
+      uint32_t accumulate = 0;
+      int mst = 0;
+      while (b < b_end) {
         const int nkb = stage_len();
-        const int slot = it % p.stages;
-        const uint32_t phase = (it / p.stages) & 1;
-        const uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
         const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
+        tc_stamp(p, 1, mst, 0);
         mbar_wait(&hdr->x_full[slot], phase, abort_flag, p.status, 13);
+        tc_stamp(p, 1, mst, 1);
+        if (!(p.debug & 32)) mbar_wait(&hdr->a_full[agrp], aphase, abort_flag, p.status, 14);
+        tc_stamp(p, 1, mst, 2);
+        if (!accumulate) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 15);
+        tc_fence_after_sync();
+        uint32_t a_addr = tmem_base + kACol0 + agrp * (p.kbs * 32);
+        uint32_t b_lo = x_base_lo + slot * x_stage_lo;
         for (int j = 0; j < nkb; ++j) {
-          const int i = kbc + j, aslot = i % kASlots;
-          mbar_wait(&hdr->a_full[aslot], (i / kASlots) & 1, abort_flag, p.status, 14);
-          if (seg_start && j == 0)
-            mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 15);
-          tc_fence_after_sync();
-          const uint64_t bdesc = umma_desc_k128(smem_u32(xs + j * p.n_tok * 128));
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ts(tmem_base + kDCol0, tmem_base + kACol0 + aslot * 32 + ks * 8,
-                        bdesc + ks * 2, idesc, (seg_start && j == 0 && ks == 0) ? 0u : 1u);
-          tc_commit(&hdr->a_empty[aslot]);
+          for (int ks = 0; ks < 4; ++ks) {
+            if (!(p.debug & 2))
+              umma_f16_ts(d_addr, a_addr + ks * 8, desc_hi | (b_lo + ks * 2), idesc, accumulate);
+            accumulate = 1;
+          }
+          a_addr += 32;
+          b_lo += x_blk_lo;
         }
-        tc_commit(&hdr->x_empty[slot]);
+        if (p.debug & 16) {
+          if (!(p.debug & 32)) mbar_arrive(&hdr->a_empty[agrp]);
+          mbar_arrive(&hdr->x_empty[slot]);
+        } else {
+          tc_commit(&hdr->a_empty[agrp]);
+          tc_commit(&hdr->x_empty[slot]);
+        }
         if (seg_end) {
           tc_commit(&hdr->d_full);
           ++seg;
+          accumulate = 0;
         }
-        seg_start = seg_end;
-        kbc += nkb;
+        tc_stamp(p, 1, mst, 3);
+        ++mst;
         advance(nkb);
       }
     }
@@ -211,22 +259,77 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int wg = warp >> 2, q = warp & 3;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    int kbc = 0, seg = 0, seg_kb0 = kb0;
+    const int n_chunks = p.n_tok / 8;  // 8-token column chunks, dealt round-robin to warpgroups
+    // accumulators of this segment summed in a fixed order
+    auto load_acc = [&](int ch, int n_used, float (&v)[8]) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+      for (int a = 0; a < n_used; ++a) {
+        uint32_t t[8];
+        tmem_ld_x8(lane_addr + kDCol0 + a * p.n_tok + ch * 8, t);
+        tc_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += __uint_as_float(t[e]);
+      }
+    };
+    int seg = 0, seg_kb0 = kb0;
     bool first_segment = true;
-    for (int it = 0; b < b_end; ++it) {
+    // a first segment that is partial is reduced at the very end if this CTA turns out to be
+    // the last contributor; `pend_old` (thread 0) is the arrival count the atomic returned
+    int pend_tile = -1;
+    unsigned pend_old = 0;
+
+    // sum the contributors' partial tiles of `t` in CTA order and run the epilogue
+    auto reduce_and_store = [&](int t, bool whole, int own_slot) {
+      const int64_t tb0 = static_cast<int64_t>(t) * p.kb_per_tile;
+      const int c_first = tc_owner_of(tb0, total, gridDim.x);
+      const int c_last = tc_owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
+      for (int ch = wg; ch < n_chunks; ch += kWarpGroups) {
+        for (int e = 0; e < 8; ++e) {
+          const int tok = ch * 8 + e;
+          if (tok >= p.m) break;
+          float v = 0.f, v_up = 0.f;
+          for (int cc = c_first; cc <= c_last; ++cc) {
+            const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
+            const int slot2 = whole ? own_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
+            const float* src = p.partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
+                               static_cast<size_t>(tok) * kTcTileN;
+            v += __ldcg(src + row);
+            if (p.fusion == FUSE_SILU_MUL && row < 64) v_up += __ldcg(src + row + 64);
+          }
+          if (p.fusion == FUSE_SILU_MUL) {
+            if (row < 64) {
+              const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
+              if (p.bias) {
+                v += p.bias[n_gate];
+                v_up += p.bias[n_up];
+              }
+              const float gate = bf16_round(v), up = bf16_round(v_up);
+              if (n_gate < p.n_out)
+                p.y[static_cast<size_t>(tok) * p.ldy + n_gate] =
+                    __float2bfloat16_rn(up * silu_bf16(gate));
+            }
+          } else {
+            tc_store(p, t, row, tok, v);
+          }
+        }
+      }
+    };
+
+    int stage_no = 0;
+    while (b < b_end) {
       const int nkb = stage_len();
-      const int slot = it % p.stages;
-      const uint32_t phase = (it / p.stages) & 1;
       const uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
       const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
+      if (tid == 0) tc_stamp(p, 2, stage_no, 0);
       mbar_wait(&hdr->w_full[slot], phase, abort_flag, p.status, 16);
-      const int g0 = kb0 >> p.kbpg_shift;
-      for (int j = 0; j < nkb; ++j) {
-        const int i = kbc + j;
-        if ((i & 1) != wg) continue;
-        const int aslot = i % kASlots;
+      if (tid == 0) tc_stamp(p, 2, stage_no, 1);
+      // k-block j of this stage belongs to warpgroup (stage_no * kbs + j) % 4
+      const int j = (wg - stage_no * p.kbs) & (kWarpGroups - 1);
+      if (j < nkb) {
         const uint4* wp = reinterpret_cast<const uint4*>(ws + j * kTcBlockBytes);
         const uint4 v0 = wp[row], v1 = wp[kTcTileN + row];
+        const int g0 = kb0 >> p.kbpg_shift;
         const uint32_t szw = reinterpret_cast<const uint32_t*>(
             ws + p.kbs * kTcBlockBytes)[(((kb0 + j) >> p.kbpg_shift) - g0) * kTcTileN + row];
         const uint32_t z2 = __byte_perm(szw, 0, 0x1010), s2 = __byte_perm(szw, 0, 0x3232);
@@ -239,107 +342,104 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             r[jj * 4 + s] = bf16x2_mul(
                 bf16x2_sub(lop3_and_or(words[jj] >> (4 * s), 0x000f000fu, kBf16Magic), z2), s2);
         }
-        mbar_wait(&hdr->a_empty[aslot], ((i / kASlots) & 1) ^ 1, abort_flag, p.status, 17);
+        mbar_wait(&hdr->a_empty[agrp], aphase ^ 1, abort_flag, p.status, 17);
         tc_fence_after_sync();
-        tmem_st_x32(lane_addr + kACol0 + aslot * 32, r);
-        tc_wait_st();
+        if (!(p.debug & 4)) {
+          tmem_st_x32(lane_addr + kACol0 + agrp * (p.kbs * 32) + j * 32, r);
+          tc_wait_st();
+        } else if (r[3] == 0x12345u) {
+          p.status[1] = 1;
+        }
         tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&hdr->a_full[aslot]);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&hdr->w_empty[slot]);
-      kbc += nkb;
+      if (lane == 0) {
+        if (!(p.debug & 32)) mbar_arrive(&hdr->a_full[agrp]);
+        mbar_arrive(&hdr->w_empty[slot]);
+      }
+      ++stage_no;
 
       if (seg_end) {
-        const int seg_kb1 = kb0 + nkb;
-        const bool whole = (seg_kb0 == 0 && seg_kb1 == p.kb_per_tile);
-        const int half_tok = p.n_tok / 2;  // this warpgroup's token columns
-        const int tok0 = wg * half_tok;
+        const bool whole = (seg_kb0 == 0 && kb0 + nkb == p.kb_per_tile);
+        const int n_used = 1;
         mbar_wait(&hdr->d_full, seg & 1, abort_flag, p.status, 18);
         tc_fence_after_sync();
         if (whole && p.fusion != FUSE_SILU_MUL) {
-          for (int c = 0; c < half_tok; c += 8) {
-            uint32_t v[8];
-            tmem_ld_x8(lane_addr + kDCol0 + tok0 + c, v);
-            tc_wait_ld();
+          for (int ch = wg; ch < n_chunks; ch += kWarpGroups) {
+            float v[8];
+            load_acc(ch, n_used, v);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) tc_store(p, tile, row, tok0 + c + e, __uint_as_float(v[e]));
+            for (int e = 0; e < 8; ++e) tc_store(p, tile, row, ch * 8 + e, v[e]);
           }
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&hdr->d_empty);
         } else {
-          // park this CTA's contribution in the workspace (also used to pair gate/up rows)
+          // park this CTA's contribution in the workspace (also pairs gate / up rows)
           const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
           float* dst = p.partials + static_cast<size_t>(my_slot) * p.n_tok * kTcTileN;
-          for (int c = 0; c < half_tok; c += 8) {
-            uint32_t v[8];
-            tmem_ld_x8(lane_addr + kDCol0 + tok0 + c, v);
-            tc_wait_ld();
+          for (int ch = wg; ch < n_chunks; ch += kWarpGroups) {
+            float v[8];
+            load_acc(ch, n_used, v);
 #pragma unroll
             for (int e = 0; e < 8; ++e)
-              if (tok0 + c + e < p.m)
-                __stcg(dst + static_cast<size_t>(tok0 + c + e) * kTcTileN + row, __uint_as_float(v[e]));
+              if (ch * 8 + e < p.m)
+                __stcg(dst + static_cast<size_t>(ch * 8 + e) * kTcTileN + row, v[e]);
           }
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&hdr->d_empty);
-          const int64_t tb0 = static_cast<int64_t>(tile) * p.kb_per_tile;
-          const int c_first = tc_owner_of(tb0, total, gridDim.x);
-          const int c_last = tc_owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
-          __threadfence();
           named_bar_sync(1, kDequantWarps * 32);
-          if (tid == 0) {
-            int last = 1;
-            if (!whole) {
-              const unsigned old = atomicAdd(p.counters + tile, 1u);
-              last = (old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
+          const bool defer = !whole && first_segment && (b + nkb < b_end);
+          if (defer) {
+            // more tiles follow: count the arrival now, look at the answer when all work is done
+            if (tid == 0) {
+              __threadfence();
+              pend_old = atomicAdd(p.counters + tile, 1u);
             }
-            hdr->is_last = last;
-          }
-          named_bar_sync(1, kDequantWarps * 32);
-          if (hdr->is_last) {
-            __threadfence();
-            for (int c = 0; c < half_tok; ++c) {
-              const int tok = tok0 + c;
-              if (tok >= p.m) break;
-              float v = 0.f;
-              float v_up = 0.f;
-              for (int cc = c_first; cc <= c_last; ++cc) {
-                const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
-                const int slot2 = whole ? my_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
-                const float* src = p.partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
-                                   static_cast<size_t>(tok) * kTcTileN;
-                v += __ldcg(src + row);
-                if (p.fusion == FUSE_SILU_MUL && row < 64) v_up += __ldcg(src + row + 64);
+            pend_tile = tile;
+          } else {
+            if (tid == 0) {
+              int last = 1;
+              if (!whole) {
+                const int64_t tb0 = static_cast<int64_t>(tile) * p.kb_per_tile;
+                const int c_first = tc_owner_of(tb0, total, gridDim.x);
+                const int c_last = tc_owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
+                __threadfence();
+                const unsigned old = atomicAdd(p.counters + tile, 1u);
+                last = (old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
+                if (last) p.counters[tile] = 0;
               }
-              if (p.fusion == FUSE_SILU_MUL) {
-                if (row < 64) {
-                  const int ng_ = tile * 64 + row;       // gate row
-                  const int nu_ = p.n / 2 + ng_;         // matching up row
-                  if (p.bias) {
-                    v += p.bias[ng_];
-                    v_up += p.bias[nu_];
-                  }
-                  const float gate = bf16_round(v), up = bf16_round(v_up);
-                  if (ng_ < p.n_out)
-                    p.y[static_cast<size_t>(tok) * p.ldy + ng_] =
-                        __float2bfloat16_rn(up * silu_bf16(gate));
-                }
-              } else {
-                tc_store(p, tile, row, tok, v);
-              }
+              hdr->is_last = last;
             }
-            if (tid == 0 && !whole) p.counters[tile] = 0;
+            named_bar_sync(1, kDequantWarps * 32);
+            if (hdr->is_last) {
+              __threadfence();
+              reduce_and_store(tile, whole, my_slot);
+            }
+            named_bar_sync(1, kDequantWarps * 32);
           }
-          named_bar_sync(1, kDequantWarps * 32);
         }
         ++seg;
         first_segment = false;
       }
       advance(nkb);
       if (seg_end) seg_kb0 = kb0;
+    }
+    if (pend_tile >= 0) {
+      if (tid == 0) {
+        const int64_t tb0 = static_cast<int64_t>(pend_tile) * p.kb_per_tile;
+        const int c_first = tc_owner_of(tb0, total, gridDim.x);
+        const int c_last = tc_owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
+        const int last = (pend_old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
+        if (last) p.counters[pend_tile] = 0;
+        hdr->is_last = last;
+      }
+      named_bar_sync(1, kDequantWarps * 32);
+      if (hdr->is_last) {
+        __threadfence();
+        reduce_and_store(pend_tile, false, 0);
+      }
     }
   }
 
@@ -349,7 +449,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  (void)fin;
 }
 
 }  // namespace
@@ -379,6 +478,7 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
   }
   if (stages < 2) return cudaErrorInvalidConfiguration;
   p.stages = stages;
+  if (const char* e = getenv("WOQ_B200_DEBUG")) p.debug = atoi(e);
   const size_t smem = kTcHeaderBytes + static_cast<size_t>(stages) * (x_stage + w_stage);
   cudaError_t e = cudaFuncSetAttribute(woq_int4_tc_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,

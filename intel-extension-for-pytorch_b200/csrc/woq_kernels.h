@@ -22,8 +22,10 @@ struct DecodeParams {
   int* status;             // 0, or the code of the wait that gave up
   int64_t ldx, ldy;
   int m, n, n_out, k;
-  int tiles, kb_per_tile, kb_per_group, groups, gps;  // gps = max(1, 8 / kb_per_group)
+  int tiles, kb_per_tile, kbpg_shift, groups, gps;  // gps = groups a full stage can touch
   int fusion, gate_up, stages;
+  int exact;            // 1: per-weight bf16 rounding (tile dequantiser); 0: scale after the sum
+  int x_rows, red_tok;  // shared-memory rows for x per stage / tokens in the reduction buffer
   int debug;  // experiment switches: 1 skip math, 2 skip x copies, 4 skip scale copies
 };
 
@@ -67,6 +69,7 @@ struct TcParams {
   int tiles, kb_per_tile, kbpg_shift, groups;
   int kbs, stages;
   int fusion, gate_up;
+  int debug;  // experiment switches: 1 skip dequant math, 2 skip MMA issue, 4 skip TMEM stores
 };
 
 int tc_pick_grid(int tiles, int kb_per_tile, int num_sms);

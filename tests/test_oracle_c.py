@@ -1,0 +1,61 @@
+"""The C restatement (timed CPU baseline) must agree with the numpy oracle, which is the
+one pinned by the golden fixtures."""
+import numpy as np
+import pytest
+
+from oracle import woq_oracle as O
+from oracle import woq_oracle_c as OC
+from tests.helpers import make_acts, make_int4_layer
+
+
+@pytest.mark.parametrize("n,k,g,m", [(96, 256, 128, 3), (500, 512, 64, 33), (64, 1024, -1, 5),
+                                     (256, 384, 128, 70)])
+def test_int4_bf16_linear_matches_numpy_oracle(n, k, g, m):
+    layer = make_int4_layer(n, k, g, seed=n + m, bias=True)
+    x = make_acts(m, k, seed=m)
+    s32 = layer["s16"].astype(np.float32)
+    L = OC.Layer(layer["qw"], n, k, s32, layer["z"], layer["bias"], g)
+    y = L.linear_bf16(x)
+    y_ref = O.woq_linear_bf16(x, layer["qw"], layer["s16"], layer["z"], layer["bias"],
+                              O.WOQ_DTYPE_INT4, g)
+    mx, mr = O.parity_metrics(y, y_ref)
+    # same bf16 weights, fp32 accumulation in a different order
+    assert mx < 4e-3 and mr < 3e-4, (mx, mr)
+    assert (y == y_ref).mean() > 0.97
+
+
+@pytest.mark.parametrize("fusion,n_others", [(O.FUSE_SILU, 0), (O.FUSE_GELU_ERF, 0), (O.FUSE_ADD, 1),
+                                             (O.FUSE_ADD_ADD, 2), (O.FUSE_MUL, 1), (O.FUSE_SILU_MUL, 0)])
+def test_post_ops_match(fusion, n_others):
+    n, k, g, m = 256, 512, 128, 9
+    layer = make_int4_layer(n, k, g, seed=fusion, std=0.05)
+    x = make_acts(m, k, seed=1)
+    others = [make_acts(m, n, seed=10 + i) for i in range(n_others)]
+    L = OC.Layer(layer["qw"], n, k, layer["s16"].astype(np.float32), layer["z"], None, g)
+    y = L.linear_bf16(x, fusion, others)
+    y_ref = O.woq_linear_bf16(x, layer["qw"], layer["s16"], layer["z"], None, O.WOQ_DTYPE_INT4, g,
+                              fusion, others)
+    mx, mr = O.parity_metrics(y, y_ref)
+    assert mx < 8e-3 and mr < 6e-4, (mx, mr)
+
+
+def test_act_quant_bit_exact():
+    x = make_acts(7, 512, seed=3)
+    x[2] = 0.0
+    qa, sa = OC.quant_act_sym(x)
+    qa_ref, sa_ref, _ = O.dynamic_quant_per_token(x, sym=True)
+    np.testing.assert_array_equal(qa, qa_ref)
+    np.testing.assert_array_equal(sa, sa_ref)
+
+
+@pytest.mark.parametrize("n,k,m", [(96, 256, 3), (320, 1024, 40)])
+def test_int8_linear_accumulators_exact_and_outputs_close(n, k, m):
+    rng = np.random.default_rng(n)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    qw, s, _ = O.quantize_per_channel(w, O.WOQ_DTYPE_INT8, sym=True)
+    x = make_acts(m, k, seed=m)
+    L = OC.Layer(qw, n, k, s, None, None, -1, is_int8=True, int8_compute=True)
+    y, acc = L.linear_int8(x, want_acc=True)
+    y_ref, acc_ref, _, _ = O.woq_linear_int8(x, qw, s, None, return_acc=True)
+    np.testing.assert_array_equal(acc, acc_ref)
+    assert (y == y_ref).mean() > 0.999
