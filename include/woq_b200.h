@@ -170,6 +170,19 @@ int woq_b200_linear(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t l
                     const void* const* others, int32_t n_others, void* y, int64_t ldy,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  Same computation as woq_b200_linear for at most 16 tokens,
+ * for callers that may not allocate device memory (memory-planned graphs, servers that forbid
+ * allocation after start-up, sandboxes without a re-entrant allocator): the scratch lives in a
+ * 4 MiB array inside the library's device image, held by every GPU that loads the library
+ * until the process exits.  Calls no cudaMalloc / cudaFree.  Returns WOQ_B200_ERR_INVALID_ARG
+ * for m > 16 and WOQ_B200_ERR_WORKSPACE when the GPU would need more than the 4 MiB (more than
+ * 252 SMs).  The first call on each device looks up the array's address; make that call
+ * outside any stream capture.  All calls on one GPU share the array: they must be
+ * stream-ordered, two that overlap on the device race on the partial tiles and counters. */
+int woq_b200_linear_static_scratch(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
+                                   int32_t fusion, const void* const* others, int32_t n_others,
+                                   void* y, int64_t ldy, void* stream);
+
 /* One expert of a mixture-of-experts layer on gathered tokens:
  * out[row_idx[i], :] = bf16(out[row_idx[i], :] + y[i, :] * row_weight[i]) with
  * y = x[row_idx_in ? row_idx_in[i] : i, :] * W^T.  Replaces fuse_index_unsqueeze /

@@ -23,6 +23,7 @@ CUDA_SOURCES = [
     "woq_pack.cu",
     "woq_decode_int4.cu",
     "woq_int4_tc.cu",
+    "woq_static_scratch.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -8,6 +8,7 @@
 #include <new>
 
 #include "../../include/woq_b200.h"
+#include "woq_internal.h"
 #include "woq_kernels.h"
 
 namespace woq {
@@ -30,6 +31,20 @@ int fail(int code, const char* fmt, ...) {
   va_end(ap);
   return code;
 }
+
+}  // namespace
+
+namespace woq {
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+}  // namespace woq
+
+namespace {
 
 #define CUDA_TRY(expr)                                                                     \
   do {                                                                                     \

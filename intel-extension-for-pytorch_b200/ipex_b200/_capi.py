@@ -38,6 +38,7 @@ EXPORTS = [
     "woq_b200_workspace_header_bytes",
     "woq_b200_linear",
     "woq_b200_linear_scatter",
+    "woq_b200_linear_static_scratch",
     "woq_b200_dump_dequant",
     "woq_b200_int8_internals",
     "woq_b200_workspace_status",
@@ -95,6 +96,7 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_workspace_bytes.restype = sz
     L.woq_b200_workspace_header_bytes.restype = sz
     L.woq_b200_linear.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
+    L.woq_b200_linear_static_scratch.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp]
     L.woq_b200_linear_scatter.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
     L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
@@ -241,6 +243,25 @@ class WoqContext:
                 )
             )
         return out.reshape(*x.shape[:-1], n_out)
+
+    def linear_static_scratch(self, x, fusion=FUSE_NONE, others=(), out=None):
+        """woq_b200_linear_static_scratch: at most 16 tokens, scratch inside the library, no
+        allocation by the library (the output tensor is the caller's)."""
+        x2 = x.reshape(-1, x.shape[-1])
+        m = x2.shape[0]
+        n_out = self.n // 2 if fusion == FUSE_SILU_MUL else self.n
+        if out is None:
+            out = torch.empty((m, n_out), dtype=torch.bfloat16, device=x.device)
+        oth = [o.reshape(m, n_out).contiguous() for o in others]
+        arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
+        with torch.cuda.device(self.device):
+            _check(
+                lib().woq_b200_linear_static_scratch(
+                    self._h, x2.data_ptr(), m, x2.stride(0), fusion, arr, len(oth),
+                    out.data_ptr(), out.stride(0), _stream(),
+                )
+            )
+        return out
 
     def linear_scatter(self, x, row_idx, row_weight, out, workspace=None):
         x2 = x.reshape(-1, x.shape[-1])
