@@ -23,6 +23,7 @@ CUDA_SOURCES = [
     "woq_pack.cu",
     "woq_decode_int4.cu",
     "woq_int4_tc.cu",
+    "woq_int8.cu",
     "woq_static_scratch.cu",
 ]
 NVCC_FLAGS = [

@@ -74,6 +74,8 @@ struct woq_b200_ctx {
   int tiles_tc, kbpg_shift;
   size_t wq_tc_bytes, sz_tc_bytes;
   float* scale_f32;  // INT8: per-channel fp32 scales [n_pad]
+  int is_int8;       // INT8 weights with INT8 compute
+  int kc_per_tile;   // INT8: K / 128
   float* bias;       // fp32 [n] or null
   size_t wq_bytes, sz_bytes;
 };
@@ -93,6 +95,85 @@ __global__ void convert_bias_kernel(const void* src, float* dst, int n, int dtyp
   if (i >= n) return;
   dst[i] = dtype == WOQ_B200_T_F32 ? reinterpret_cast<const float*>(src)[i]
                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i]);
+}
+
+}  // namespace
+
+namespace {
+
+// INT8 symmetric per-channel weights, INT8 compute with per-token symmetric activations
+int create_int8(const woq_b200_desc* d, const void* qweight, const void* scales,
+                const void* zero_points, const void* bias, cudaStream_t stream, woq_b200_ctx** out) {
+  if (d->lowp_mode != WOQ_B200_LOWP_INT8)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 weights are built for lowp_mode INT8 only (got %d)", d->lowp_mode);
+  if (d->act_quant_mode != WOQ_B200_ACT_PER_M_SYM)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "activation quantisation mode %d is not built (per-token symmetric = 6 is)",
+                d->act_quant_mode);
+  if (zero_points) return fail(WOQ_B200_ERR_INVALID_ARG, "INT8 weights with INT8 compute are symmetric: no zero points");
+  if (d->group_size > 0 && d->group_size < d->k)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 compute path takes per-channel weight scales (group_size -1)");
+  if (d->weight_format != WOQ_B200_FMT_PLAIN) return fail(WOQ_B200_ERR_INVALID_ARG, "INT8 weights come in plain format");
+  if (d->k % 128 != 0) return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 path needs K %% 128 == 0 (K=%lld)", (long long)d->k);
+  const int gate_up = (d->layout_flags & WOQ_B200_LAYOUT_GATE_UP) ? 1 : 0;
+  if (gate_up && (d->n % 128 != 0)) return fail(WOQ_B200_ERR_INVALID_ARG, "gate/up layout needs N %% 128 == 0");
+  woq_b200_ctx* c = new (std::nothrow) woq_b200_ctx();
+  if (!c) return fail(WOQ_B200_ERR_CUDA, "out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->desc = *d;
+  c->gate_up = gate_up;
+  c->is_int8 = 1;
+  auto bail = [&](int rc) {
+    if (c->wq) cudaFree(c->wq);
+    if (c->scale_f32) cudaFree(c->scale_f32);
+    if (c->bias) cudaFree(c->bias);
+    delete c;
+    return rc;
+  };
+#define CUDA_TRY_I(expr)                                                                    \
+  do {                                                                                      \
+    cudaError_t e__ = (expr);                                                               \
+    if (e__ != cudaSuccess)                                                                 \
+      return bail(fail(WOQ_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__))); \
+  } while (0)
+  CUDA_TRY_I(cudaGetDevice(&c->device));
+  CUDA_TRY_I(cudaDeviceGetAttribute(&c->num_sms, cudaDevAttrMultiProcessorCount, c->device));
+  c->tiles_tc = static_cast<int>((d->n + 127) / 128);
+  c->kc_per_tile = static_cast<int>(d->k / 128);
+  c->wq_bytes = static_cast<size_t>(c->tiles_tc) * 2 * c->kc_per_tile * 8192;
+  c->sz_bytes = static_cast<size_t>(c->tiles_tc) * 128 * sizeof(float);
+  CUDA_TRY_I(cudaMalloc(&c->wq, c->wq_bytes));
+  CUDA_TRY_I(cudaMalloc(&c->scale_f32, c->sz_bytes));
+  CUDA_TRY_I(woq::launch_pack_int8(static_cast<const int8_t*>(qweight), reinterpret_cast<int8_t*>(c->wq),
+                                   (int)d->n, (int)d->k, c->tiles_tc * 2, gate_up, stream));
+  CUDA_TRY_I(woq::launch_pad_scale(scales, c->scale_f32, (int)d->n, c->tiles_tc * 128, d->scale_dtype, stream));
+  if (bias) {
+    CUDA_TRY_I(cudaMalloc(&c->bias, static_cast<size_t>(d->n) * sizeof(float)));
+    convert_bias_kernel<<<(unsigned)((d->n + 255) / 256), 256, 0, stream>>>(bias, c->bias, (int)d->n, d->bias_dtype);
+    woq::count_launch();
+    CUDA_TRY_I(cudaGetLastError());
+  }
+  CUDA_TRY_I(cudaStreamSynchronize(stream));
+#undef CUDA_TRY_I
+  c->magic = kMagic;
+  *out = c;
+  return WOQ_B200_OK;
+}
+
+struct Int8Workspace {
+  size_t partial_off, sa_off, qa_off, total;
+};
+Int8Workspace int8_ws_layout(const woq_b200_ctx* c, int64_t m) {
+  Int8Workspace w;
+  int n_tok = static_cast<int>(m < 256 ? m : 256);
+  n_tok = (n_tok + 15) / 16 * 16;
+  if (n_tok < 16) n_tok = 16;
+  w.partial_off = kWsHeaderBytes;
+  size_t off = w.partial_off + woq::int8_partial_bytes(c->num_sms, n_tok);
+  w.sa_off = (off + 255) / 256 * 256;
+  off = w.sa_off + static_cast<size_t>((m + 63) / 64 * 64) * sizeof(float);
+  w.qa_off = (off + 1023) / 1024 * 1024;
+  w.total = w.qa_off + static_cast<size_t>(m) * c->desc.k;
+  return w;
 }
 
 }  // namespace
@@ -133,8 +214,7 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
       d->scale_dtype != WOQ_B200_T_BF16)
     return fail(WOQ_B200_ERR_INVALID_ARG, "scales must be fp32, fp16 or bf16");
 
-  if (d->weight_dtype == WOQ_B200_DTYPE_INT8)
-    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 weights are not built yet");
+  if (d->weight_dtype == WOQ_B200_DTYPE_INT8) return create_int8(d, qweight, scales, zero_points, bias, stream, out);
   // ---- INT4 ----
   if (d->lowp_mode == WOQ_B200_LOWP_INT8)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 weights with INT8 compute are not built yet");
@@ -315,6 +395,11 @@ int woq_b200_ctx_unpack(const woq_b200_ctx* c, void* qweight_plain, void* stream
   if (int rc = check_ctx(c)) return rc;
   if (!qweight_plain) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (c->is_int8) {
+    CUDA_TRY(woq::launch_unpack_int8(reinterpret_cast<const int8_t*>(c->wq), static_cast<int8_t*>(qweight_plain),
+                                     (int)c->desc.n, (int)c->desc.k, c->gate_up, stream));
+    return WOQ_B200_OK;
+  }
   if (!c->wq)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "unpack needs the streaming layout (context was packed tensor-core only)");
   CUDA_TRY(woq::launch_unpack_int4(c->wq, static_cast<uint8_t*>(qweight_plain), (int)c->desc.n,
@@ -324,6 +409,7 @@ int woq_b200_ctx_unpack(const woq_b200_ctx* c, void* qweight_plain, void* stream
 
 size_t woq_b200_workspace_bytes(const woq_b200_ctx* c, int64_t m) {
   if (check_ctx(c)) return 0;
+  if (c->is_int8) return int8_ws_layout(c, m < 1 ? 1 : m).total;
   // header + one pair of partial tiles per CTA of the largest grid
   size_t decode = woq::decode_int4_partial_bytes(2 * c->num_sms);
   int n_tok = static_cast<int>(m < 256 ? m : 256);
@@ -461,6 +547,58 @@ static int run_tc(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, 
   return WOQ_B200_OK;
 }
 
+// INT8 compute: quantise the activations per token, then the tcgen05 int8 kernel per 256 tokens
+static int run_int8(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
+                    const void* o0, const void* o1, void* y, int64_t ldy, int8_t* qa_out, float* sa_out,
+                    int32_t* acc_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  const Int8Workspace L = int8_ws_layout(c, m);
+  if (ws_bytes < L.total)
+    return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", ws_bytes, L.total);
+  if (c->tiles_tc > kMaxCounterTiles)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the workspace header");
+  uint8_t* w8 = static_cast<uint8_t*>(ws);
+  float* sa = reinterpret_cast<float*>(w8 + L.sa_off);
+  int8_t* qa = reinterpret_cast<int8_t*>(w8 + L.qa_off);
+  const int64_t k = c->desc.k;
+  CUDA_TRY(woq::launch_quant_act_sym(static_cast<const __nv_bfloat16*>(x), ldx, (int)m, (int)k, qa, sa, stream));
+  if (qa_out) CUDA_TRY(cudaMemcpyAsync(qa_out, qa, static_cast<size_t>(m) * k, cudaMemcpyDeviceToDevice, stream));
+  if (sa_out) CUDA_TRY(cudaMemcpyAsync(sa_out, sa, static_cast<size_t>(m) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  if (!y && !acc_out) return WOQ_B200_OK;
+  const int64_t mt = m < 256 ? m : 256;
+  const int n_tok = static_cast<int>((mt + 15) / 16 * 16);
+  CUtensorMap qamap;
+  if (int rc = make_kmajor_map(&qamap, qa, m, k, k, 1, n_tok)) return rc;
+  for (int64_t m0 = 0; m0 < m; m0 += 256) {
+    const int64_t mm = m - m0 < 256 ? m - m0 : 256;
+    woq::I8Params p{};
+    p.wq = reinterpret_cast<const int8_t*>(c->wq);
+    p.sw = c->scale_f32;
+    p.sa = sa + m0;
+    p.bias = c->bias;
+    p.y = y ? static_cast<__nv_bfloat16*>(y) + m0 * ldy : nullptr;
+    p.other0 = o0 ? static_cast<const __nv_bfloat16*>(o0) + m0 * ldy : nullptr;
+    p.other1 = o1 ? static_cast<const __nv_bfloat16*>(o1) + m0 * ldy : nullptr;
+    p.acc_out = acc_out ? acc_out + m0 * c->desc.n : nullptr;
+    p.status = reinterpret_cast<int*>(w8);
+    p.counters = reinterpret_cast<uint32_t*>(w8 + 256);
+    p.partials = w8 + L.partial_off;
+    p.ldy = ldy;
+    p.m = (int)mm;
+    p.n = (int)c->desc.n;
+    p.n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? (int)(c->desc.n / 2) : (int)c->desc.n;
+    p.m0 = (int)m0;
+    p.n_tok = n_tok;
+    p.tiles = c->tiles_tc;
+    p.kc_per_tile = c->kc_per_tile;
+    p.fusion = fusion;
+    p.gate_up = c->gate_up;
+    const int64_t total = static_cast<int64_t>(c->tiles_tc) * c->kc_per_tile;
+    const int grid = static_cast<int>(total < c->num_sms ? total : c->num_sms);
+    CUDA_TRY(woq::launch_int8_tc(p, qamap, grid, stream));
+  }
+  return WOQ_B200_OK;
+}
+
 static bool use_tc_path(const woq_b200_ctx* c, int64_t m) {
   static int env = -1;
   if (env < 0) {
@@ -505,6 +643,9 @@ int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
   if ((need > 0 && !o0) || (need > 1 && !o1)) return fail(WOQ_B200_ERR_INVALID_ARG, "null extra tensor");
   const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? c->desc.n / 2 : c->desc.n;
   if (ldy < n_out) return fail(WOQ_B200_ERR_INVALID_ARG, "ldy smaller than the output width");
+  if (c->is_int8)
+    return run_int8(c, x, m, ldx, fusion, o0, o1, y, ldy, nullptr, nullptr, nullptr, workspace,
+                    workspace_bytes, stream);
   if (use_tc_path(c, m))
     return run_tc(c, x, m, ldx, fusion, o0, o1, nullptr, nullptr, y, ldy, workspace, workspace_bytes,
                   stream);
@@ -534,6 +675,7 @@ int woq_b200_linear_scatter(const woq_b200_ctx* c, const void* x, int64_t m, int
   if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
     return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
   if (ld_out < c->desc.n) return fail(WOQ_B200_ERR_INVALID_ARG, "ld_out smaller than N");
+  if (c->is_int8) return fail(WOQ_B200_ERR_UNSUPPORTED, "scatter epilogue is built for INT4 contexts");
   if (use_tc_path(c, m))
     return run_tc(c, x, m, ldx, WOQ_B200_FUSE_SCALED_SCATTER_ADD, nullptr, nullptr, row_idx, row_weight,
                   out, ld_out, workspace, workspace_bytes, stream);
@@ -552,6 +694,8 @@ int woq_b200_dump_dequant(const woq_b200_ctx* c, void* w_bf16, void* stream_) {
   if (int rc = check_ctx(c)) return rc;
   if (!w_bf16) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (c->is_int8)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the INT8 compute path never dequantises its weights");
   if (c->wq_tc) {
     // the routine the tensor-core kernel uses for its tiles
     CUDA_TRY(woq::launch_dump_dequant_int4_tc(c->wq_tc, c->sz_tc, static_cast<__nv_bfloat16*>(w_bf16),
@@ -566,10 +710,16 @@ int woq_b200_dump_dequant(const woq_b200_ctx* c, void* w_bf16, void* stream_) {
   return WOQ_B200_OK;
 }
 
-int woq_b200_int8_internals(const woq_b200_ctx* c, const void*, int64_t, int64_t, int8_t*, float*,
-                            int32_t*, void*, size_t, void*) {
+int woq_b200_int8_internals(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int8_t* qa,
+                            float* sa, int32_t* acc, void* workspace, size_t workspace_bytes,
+                            void* stream_) {
   if (int rc = check_ctx(c)) return rc;
-  return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 compute is not built yet");
+  if (!c->is_int8) return fail(WOQ_B200_ERR_INVALID_ARG, "context does not use INT8 compute");
+  if (m <= 0 || !x || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "bad arguments");
+  if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
+  return run_int8(c, x, m, ldx, WOQ_B200_FUSE_NONE, nullptr, nullptr, nullptr, c->desc.n, qa, sa, acc,
+                  workspace, workspace_bytes, static_cast<cudaStream_t>(stream_));
 }
 
 int woq_b200_workspace_status(void* workspace, void* stream_) {

@@ -1,0 +1,499 @@
+// INT8-compute path (WoqLowpMode.INT8 with INT8 symmetric per-channel weights):
+//   * prepack of the plain [N, K] int8 weight into "operand images": tiles of 64 rows x 128 k,
+//     8 KB each, stored exactly as the tensor core wants a K-major 128-byte-swizzled operand
+//     (row r of an 8-row group at r*128 bytes, its 16-byte chunk c at position c ^ r), so a
+//     bulk copy of two consecutive images is a ready 128-row A operand - no tensor map needed;
+//   * dynamic per-token symmetric quantisation of the bf16 activations (true division, round
+//     half to even): the reference's dynamic_quantize_per_block for QUANT_A_PER_M_SYM;
+//   * one tcgen05 kernel (kind::i8, int32 accumulators in TMEM) for every token count: weights
+//     need no dequantisation, so even for one token an MMA covers 4 KB of weights and the
+//     kernel stays memory-bound.  Stream-K over (tile, k-chunk) with int32 partial tiles:
+//     the accumulators do not depend on how K was split.
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
+#include "woq_kernels.h"
+#include "woq_tc_common.cuh"
+
+namespace woq {
+
+namespace {
+
+// ---- operand image layout -------------------------------------------------------------
+__host__ __device__ inline int image_offset(int r /*0..63*/, int kbyte /*0..127*/) {
+  return (r >> 3) * 1024 + (r & 7) * 128 + ((((kbyte >> 4) ^ (r & 7))) << 4) + (kbyte & 15);
+}
+
+__global__ void pack_int8_kernel(const int8_t* plain, int8_t* tiled, int n, int k, int tiles64,
+                                 int kc_per_tile, int gate_up) {
+  // one thread per 16 bytes of the image
+  const int64_t total = static_cast<int64_t>(tiles64) * kc_per_tile * 512;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int chunk = i & 7, r = (i >> 3) & 63;
+  const int64_t blk = i >> 9;
+  const int kc = static_cast<int>(blk % kc_per_tile), t64 = static_cast<int>(blk / kc_per_tile);
+  const int row128 = (t64 & 1) * 64 + r;
+  const int nn = tc_tile_row_to_n(n, gate_up, t64 >> 1, row128);
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (nn < n) v = *reinterpret_cast<const uint4*>(plain + static_cast<int64_t>(nn) * k + kc * 128 + chunk * 16);
+  *reinterpret_cast<uint4*>(tiled + blk * 8192 + image_offset(r, chunk * 16)) = v;
+}
+
+__global__ void unpack_int8_kernel(const int8_t* tiled, int8_t* plain, int n, int k, int kc_per_tile,
+                                   int gate_up) {
+  const int64_t chunks_per_row = k / 16;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<int64_t>(n) * chunks_per_row) return;
+  const int nn = static_cast<int>(i / chunks_per_row), ch = static_cast<int>(i % chunks_per_row);
+  int tile128, row128;
+  if (gate_up) {
+    const int half = n / 2, idx = nn < half ? nn : nn - half;
+    tile128 = idx / 64;
+    row128 = (idx % 64) + (nn < half ? 0 : 64);
+  } else {
+    tile128 = nn / 128;
+    row128 = nn % 128;
+  }
+  const int t64 = tile128 * 2 + (row128 >> 6), r = row128 & 63;
+  const int kc = ch / 8, chunk = ch % 8;
+  const int64_t blk = static_cast<int64_t>(t64) * kc_per_tile + kc;
+  *reinterpret_cast<uint4*>(plain + static_cast<int64_t>(nn) * k + ch * 16) =
+      *reinterpret_cast<const uint4*>(tiled + blk * 8192 + image_offset(r, chunk * 16));
+}
+
+__global__ void pad_scale_kernel(const void* src, float* dst, int n, int n_pad, int dtype) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pad) return;
+  float v = 0.f;
+  if (i < n) {
+    if (dtype == 1) v = reinterpret_cast<const float*>(src)[i];
+    else if (dtype == 2) v = __half2float(reinterpret_cast<const __half*>(src)[i]);
+    else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i]);
+  }
+  dst[i] = v;
+}
+
+// ---- per-token symmetric activation quantisation --------------------------------------
+// scale = max(|max|, |min|) / 127 ; q = clamp(nearbyint(x / scale), -128, 127); a row of zeros
+// gets codes 0.  One CTA per token row.
+__global__ void __launch_bounds__(256) quant_act_sym_kernel(const __nv_bfloat16* x, int64_t ldx, int k,
+                                                            int8_t* qa, float* sa) {
+  __shared__ float red[8];
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* xr = x + static_cast<int64_t>(m) * ldx;
+  float amax = 0.f;
+  for (int i = tid * 8; i < k; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      amax = fmaxf(amax, fabsf(__uint_as_float(w[j] << 16)));
+      amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xffff0000u)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((tid & 31) == 0) red[tid >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  const float scale = __fdiv_rn(amax, 127.0f);
+  if (tid == 0) sa[m] = scale;
+  int8_t* qr = qa + static_cast<int64_t>(m) * k;
+  for (int i = tid * 8; i < k; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t out[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+      float ql = 0.f, qh = 0.f;
+      if (scale > 0.f) {
+        ql = fminf(fmaxf(rintf(__fdiv_rn(lo, scale)), -128.f), 127.f);
+        qh = fminf(fmaxf(rintf(__fdiv_rn(hi, scale)), -128.f), 127.f);
+      }
+      const uint32_t b = (static_cast<uint32_t>(static_cast<int>(ql)) & 0xffu) |
+                         ((static_cast<uint32_t>(static_cast<int>(qh)) & 0xffu) << 8);
+      out[j >> 1] |= b << ((j & 1) * 16);
+    }
+    *reinterpret_cast<uint2*>(qr + i) = make_uint2(out[0], out[1]);
+  }
+}
+
+// ---- tcgen05 int8 GEMM -------------------------------------------------------------------
+constexpr int kEpiWarps = 4;
+constexpr int kI8Threads = (kEpiWarps + 2) * 32;
+constexpr int kI8Producer = kEpiWarps, kI8Mma = kEpiWarps + 1;
+constexpr int kI8MaxStages = 8;
+constexpr int kI8HeaderBytes = 1024;
+constexpr int kI8TmemCols = 256;
+constexpr int kChunkBytes = 16384;  // 128 rows x 128 k
+
+struct I8Header {
+  uint64_t full[kI8MaxStages], empty[kI8MaxStages];
+  uint64_t d_full, d_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+};
+
+__device__ __forceinline__ int i8_owner_of(int64_t b, int64_t total, int64_t ctas) {
+  return static_cast<int>(((b + 1) * ctas - 1) / total);
+}
+
+__device__ __forceinline__ void i8_store(const I8Params& p, int tile, int row, int tok, int acc) {
+  const int n = tc_tile_row_to_n(p.n, p.gate_up, tile, row);
+  if (tok >= p.m || n >= p.n) return;
+  // C = bias + (float(acc) * scale_a) * scale_w   (fp32), then bf16 and the post-op
+  float v = (static_cast<float>(acc) * p.sa[tok]) * p.sw[n];
+  if (p.bias) v = p.bias[n] + v;
+  float r = bf16_round(v);
+  const size_t o = static_cast<size_t>(tok) * p.ldy + n;
+  if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
+    r = bf16_round(r + __bfloat162float(p.other0[o]));
+    if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __bfloat162float(p.other1[o]));
+  } else if (p.fusion == FUSE_MUL) {
+    r = bf16_round(r * __bfloat162float(p.other0[o]));
+  } else {
+    r = unary_post_op(r, p.fusion);
+  }
+  p.y[o] = __float2bfloat16_rn(r);
+}
+
+__global__ void __launch_bounds__(kI8Threads, 1)
+    woq_int8_tc_kernel(const I8Params p, const __grid_constant__ CUtensorMap qamap) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  I8Header* hdr = reinterpret_cast<I8Header*>(smem);
+  const int b_stage_bytes = p.n_tok * 128;
+  const int stage_bytes = kChunkBytes + b_stage_bytes;
+  uint8_t* stages = smem + kI8HeaderBytes;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (smem_u32(smem) & 1023u) {
+    if (tid == 0) atomicCAS(p.status, 0, 99);
+    return;
+  }
+  const int64_t total = static_cast<int64_t>(p.tiles) * p.kc_per_tile;
+  const int64_t b_begin = (static_cast<int64_t>(blockIdx.x) * total) / gridDim.x;
+  const int64_t b_end = (static_cast<int64_t>(blockIdx.x + 1) * total) / gridDim.x;
+
+  if (tid == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&hdr->full[s], 1);
+      mbar_init(&hdr->empty[s], 1);
+    }
+    mbar_init(&hdr->d_full, 1);
+    mbar_init(&hdr->d_empty, kEpiWarps);
+    hdr->abort_flag = 0;
+    hdr->is_last = 0;
+    mbar_fence_init();
+  }
+  if (warp == kI8Mma) {
+    tmem_alloc(&hdr->tmem_base, kI8TmemCols);
+    tmem_relinquish();
+    tc_fence_before_sync();
+  }
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = hdr->tmem_base;
+  volatile int* abort_flag = &hdr->abort_flag;
+
+  // all roles walk the same sequence of k-chunks: chunk index b -> (tile, kc)
+  int tile = static_cast<int>(b_begin / p.kc_per_tile);
+  int kc = static_cast<int>(b_begin % p.kc_per_tile);
+  int64_t b = b_begin;
+  int slot = 0;
+  uint32_t phase = 0;
+  auto advance = [&]() {
+    ++b;
+    if (++kc == p.kc_per_tile) {
+      kc = 0;
+      ++tile;
+    }
+    if (++slot == p.stages) {
+      slot = 0;
+      phase ^= 1;
+    }
+  };
+
+  if (warp == kI8Producer) {
+    if (lane == 0) {
+      while (b < b_end) {
+        uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
+        mbar_wait(&hdr->empty[slot], phase ^ 1, abort_flag, p.status, 21);
+        mbar_arrive_expect_tx(&hdr->full[slot], kChunkBytes + b_stage_bytes);
+        const int8_t* src0 = p.wq + (static_cast<size_t>(2 * tile) * p.kc_per_tile + kc) * 8192;
+        const int8_t* src1 = p.wq + (static_cast<size_t>(2 * tile + 1) * p.kc_per_tile + kc) * 8192;
+        bulk_g2s(st, src0, 8192, &hdr->full[slot]);
+        bulk_g2s(st + 8192, src1, 8192, &hdr->full[slot]);
+        tma_load_2d(st + kChunkBytes, &qamap, kc * 128, p.m0, &hdr->full[slot]);
+        advance();
+      }
+    }
+  } else if (warp == kI8Mma) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(p.n_tok, /*s8*/ 1, /*s32*/ 2);
+      const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
+      const uint32_t base_lo = (smem_u32(stages) & 0x3FFFFu) >> 4;
+      const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
+      uint32_t seg = 0, accumulate = 0;
+      while (b < b_end) {
+        const bool seg_end = (kc + 1 == p.kc_per_tile) || (b + 1 == b_end);
+        mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 22);
+        if (!accumulate) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 23);
+        tc_fence_after_sync();
+        const uint32_t a_lo = base_lo + slot * stage_lo;
+        const uint32_t b_lo = a_lo + (kChunkBytes >> 4);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          umma_i8_ss(tmem_base, desc_hi | (a_lo + ks * 2), desc_hi | (b_lo + ks * 2), idesc, accumulate);
+          accumulate = 1;
+        }
+        tc_commit(&hdr->empty[slot]);
+        if (seg_end) {
+          tc_commit(&hdr->d_full);
+          ++seg;
+          accumulate = 0;
+        }
+        advance();
+      }
+    }
+  } else {
+    // ------------------------------- epilogue warps ----------------------------------------
+    const int row = warp * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const int n_chunks = p.n_tok / 8;
+    int seg = 0, seg_kc0 = kc;
+    bool first_segment = true;
+    int pend_tile = -1;
+    unsigned pend_old = 0;
+    int* partials = reinterpret_cast<int*>(p.partials);
+
+    auto reduce_and_store = [&](int t, bool whole, int own_slot) {
+      const int64_t tb0 = static_cast<int64_t>(t) * p.kc_per_tile;
+      const int c_first = i8_owner_of(tb0, total, gridDim.x);
+      const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
+      for (int tok = 0; tok < p.m; ++tok) {
+        int v = 0, v_up = 0;
+        for (int cc = c_first; cc <= c_last; ++cc) {
+          const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
+          const int slot2 = whole ? own_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
+          const int* src = partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
+                           static_cast<size_t>(tok) * kTcTileN;
+          v += __ldcg(src + row);
+          if (p.fusion == FUSE_SILU_MUL && row < 64) v_up += __ldcg(src + row + 64);
+        }
+        if (p.fusion == FUSE_SILU_MUL) {
+          if (row < 64) {
+            const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
+            if (n_gate < p.n_out) {
+              float g = (static_cast<float>(v) * p.sa[tok]) * p.sw[n_gate];
+              float u = (static_cast<float>(v_up) * p.sa[tok]) * p.sw[n_up];
+              if (p.bias) {
+                g = p.bias[n_gate] + g;
+                u = p.bias[n_up] + u;
+              }
+              p.y[static_cast<size_t>(tok) * p.ldy + n_gate] =
+                  __float2bfloat16_rn(bf16_round(u) * silu_bf16(bf16_round(g)));
+            }
+          }
+        } else {
+          i8_store(p, t, row, tok, v);
+        }
+      }
+    };
+
+    while (b < b_end) {
+      const bool seg_end = (kc + 1 == p.kc_per_tile) || (b + 1 == b_end);
+      if (seg_end) {
+        const bool whole = (seg_kc0 == 0 && kc + 1 == p.kc_per_tile);
+        mbar_wait(&hdr->d_full, seg & 1, abort_flag, p.status, 24);
+        tc_fence_after_sync();
+        if (whole && p.fusion != FUSE_SILU_MUL) {
+          for (int ch = 0; ch < n_chunks; ++ch) {
+            uint32_t v[8];
+            tmem_ld_x8(lane_addr + ch * 8, v);
+            tc_wait_ld();
+            if (p.acc_out) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int tok = ch * 8 + e, n = tc_tile_row_to_n(p.n, p.gate_up, tile, row);
+                if (tok < p.m && n < p.n) p.acc_out[static_cast<size_t>(tok) * p.n + n] = static_cast<int>(v[e]);
+              }
+            }
+            if (p.y) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) i8_store(p, tile, row, ch * 8 + e, static_cast<int>(v[e]));
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&hdr->d_empty);
+        } else {
+          const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
+          int* dst = partials + static_cast<size_t>(my_slot) * p.n_tok * kTcTileN;
+          for (int ch = 0; ch < n_chunks; ++ch) {
+            uint32_t v[8];
+            tmem_ld_x8(lane_addr + ch * 8, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (ch * 8 + e < p.m)
+                __stcg(dst + static_cast<size_t>(ch * 8 + e) * kTcTileN + row, static_cast<int>(v[e]));
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&hdr->d_empty);
+          named_bar_sync(1, kEpiWarps * 32);
+          const bool defer = !whole && first_segment && (b + 1 < b_end);
+          if (defer) {
+            if (tid == 0) {
+              __threadfence();
+              pend_old = atomicAdd(p.counters + tile, 1u);
+            }
+            pend_tile = tile;
+          } else {
+            if (tid == 0) {
+              int last = 1;
+              if (!whole) {
+                const int64_t tb0 = static_cast<int64_t>(tile) * p.kc_per_tile;
+                const int c_first = i8_owner_of(tb0, total, gridDim.x);
+                const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
+                __threadfence();
+                const unsigned old = atomicAdd(p.counters + tile, 1u);
+                last = (old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
+                if (last) p.counters[tile] = 0;
+              }
+              hdr->is_last = last;
+            }
+            named_bar_sync(1, kEpiWarps * 32);
+            if (hdr->is_last) {
+              __threadfence();
+              if (p.acc_out) {
+                // accumulators of a split tile: sum of the partial tiles
+                const int64_t tb0 = static_cast<int64_t>(tile) * p.kc_per_tile;
+                const int c_first = i8_owner_of(tb0, total, gridDim.x);
+                const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
+                const int n = tc_tile_row_to_n(p.n, p.gate_up, tile, row);
+                for (int tok = 0; tok < p.m && n < p.n; ++tok) {
+                  int v = 0;
+                  for (int cc = c_first; cc <= c_last; ++cc) {
+                    const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
+                    const int slot2 = whole ? my_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
+                    v += __ldcg(partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
+                                static_cast<size_t>(tok) * kTcTileN + row);
+                  }
+                  p.acc_out[static_cast<size_t>(tok) * p.n + n] = v;
+                }
+              }
+              if (p.y) reduce_and_store(tile, whole, my_slot);
+            }
+            named_bar_sync(1, kEpiWarps * 32);
+          }
+        }
+        ++seg;
+        first_segment = false;
+      }
+      advance();
+      if (seg_end) seg_kc0 = kc;
+    }
+    if (pend_tile >= 0) {
+      if (tid == 0) {
+        const int64_t tb0 = static_cast<int64_t>(pend_tile) * p.kc_per_tile;
+        const int c_first = i8_owner_of(tb0, total, gridDim.x);
+        const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
+        const int last = (pend_old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
+        if (last) p.counters[pend_tile] = 0;
+        hdr->is_last = last;
+      }
+      named_bar_sync(1, kEpiWarps * 32);
+      if (hdr->is_last) {
+        __threadfence();
+        if (p.acc_out) {
+          const int64_t tb0 = static_cast<int64_t>(pend_tile) * p.kc_per_tile;
+          const int c_first = i8_owner_of(tb0, total, gridDim.x);
+          const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
+          const int n = tc_tile_row_to_n(p.n, p.gate_up, pend_tile, row);
+          for (int tok = 0; tok < p.m && n < p.n; ++tok) {
+            int v = 0;
+            for (int cc = c_first; cc <= c_last; ++cc) {
+              const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
+              v += __ldcg(partials + static_cast<size_t>(cc * 2 + (cb >= tb0 ? 0 : 1)) * p.n_tok * kTcTileN +
+                          static_cast<size_t>(tok) * kTcTileN + row);
+            }
+            p.acc_out[static_cast<size_t>(tok) * p.n + n] = v;
+          }
+        }
+        if (p.y) reduce_and_store(pend_tile, false, 0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kI8Mma) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kI8TmemCols);
+  }
+}
+
+inline unsigned blocks_for(int64_t n, int threads) {
+  return static_cast<unsigned>((n + threads - 1) / threads);
+}
+
+}  // namespace
+
+cudaError_t launch_pack_int8(const int8_t* plain, int8_t* tiled, int n, int k, int tiles64,
+                             int gate_up, cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(tiles64) * (k / 128) * 512;
+  pack_int8_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(plain, tiled, n, k, tiles64, k / 128,
+                                                               gate_up);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_unpack_int8(const int8_t* tiled, int8_t* plain, int n, int k, int gate_up,
+                               cudaStream_t stream) {
+  const int64_t total = static_cast<int64_t>(n) * (k / 16);
+  unpack_int8_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(tiled, plain, n, k, k / 128, gate_up);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pad_scale(const void* src, float* dst, int n, int n_pad, int dtype,
+                             cudaStream_t stream) {
+  pad_scale_kernel<<<blocks_for(n_pad, 256), 256, 0, stream>>>(src, dst, n, n_pad, dtype);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_quant_act_sym(const __nv_bfloat16* x, int64_t ldx, int m, int k, int8_t* qa,
+                                 float* sa, cudaStream_t stream) {
+  quant_act_sym_kernel<<<m, 256, 0, stream>>>(x, ldx, k, qa, sa);
+  count_launch();
+  return cudaGetLastError();
+}
+
+size_t int8_partial_bytes(int grid, int n_tok) {
+  return static_cast<size_t>(grid) * 2 * n_tok * kTcTileN * sizeof(int);
+}
+
+cudaError_t launch_int8_tc(I8Params p, const CUtensorMap& qamap, int grid, cudaStream_t stream) {
+  const int stage_bytes = kChunkBytes + p.n_tok * 128;
+  int stages = (200 * 1024 - kI8HeaderBytes) / stage_bytes;
+  if (stages > kI8MaxStages) stages = kI8MaxStages;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  p.stages = stages;
+  const size_t smem = kI8HeaderBytes + static_cast<size_t>(stages) * stage_bytes;
+  cudaError_t e = cudaFuncSetAttribute(woq_int8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  woq_int8_tc_kernel<<<grid, kI8Threads, smem, stream>>>(p, qamap);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace woq

@@ -81,6 +81,36 @@ __host__ __device__ inline int tc_tile_row_to_n(int n_total, int gate_up, int ti
   return tile * kTcTileN + row;
 }
 
+// ---- INT8 compute path ----------------------------------------------------------------------
+struct I8Params {
+  const int8_t* wq;     // operand images [tiles64][kc_per_tile][8192]
+  const float* sw;      // per-channel weight scales [n_pad]
+  const float* sa;      // per-token activation scales [m]
+  const float* bias;
+  __nv_bfloat16* y;     // may be null when only the accumulators are wanted
+  const __nv_bfloat16* other0;
+  const __nv_bfloat16* other1;
+  int* acc_out;         // optional [m][n] int32 accumulators
+  void* partials;       // int32 [2 * grid][n_tok][128]
+  uint32_t* counters;
+  int* status;
+  int64_t ldy;
+  int m, n, n_out;
+  int m0, n_tok;
+  int tiles, kc_per_tile;  // 128-row tiles, 128-k chunks
+  int stages, fusion, gate_up;
+};
+cudaError_t launch_pack_int8(const int8_t* plain, int8_t* tiled, int n, int k, int tiles64,
+                             int gate_up, cudaStream_t stream);
+cudaError_t launch_unpack_int8(const int8_t* tiled, int8_t* plain, int n, int k, int gate_up,
+                               cudaStream_t stream);
+cudaError_t launch_pad_scale(const void* src, float* dst, int n, int n_pad, int dtype,
+                             cudaStream_t stream);
+cudaError_t launch_quant_act_sym(const __nv_bfloat16* x, int64_t ldx, int m, int k, int8_t* qa,
+                                 float* sa, cudaStream_t stream);
+size_t int8_partial_bytes(int grid, int n_tok);
+cudaError_t launch_int8_tc(I8Params p, const CUtensorMap& qamap, int grid, cudaStream_t stream);
+
 // ---- pack / unpack / dump ------------------------------------------------------------
 struct PackInt4Args {
   const uint8_t* plain;  // [n][ceil(k/2)]

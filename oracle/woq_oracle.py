@@ -406,10 +406,11 @@ INT8_BLOCK_K = 128  # get_block_k for lowp INT8 (csrc/cpu/aten/Linear.cpp:362-37
 
 
 def int8_accumulators(qa: np.ndarray, qw: np.ndarray) -> np.ndarray:
-    """Exact int32 accumulators acc[m,n] = sum_k qa[m,k]*qw[n,k] over the whole K."""
-    return (qa.astype(np.int64) @ np.ascontiguousarray(qw).view(np.int8).astype(np.int64).T).astype(
-        np.int32
-    )
+    """Exact int32 accumulators acc[m,n] = sum_k qa[m,k]*qw[n,k] over the whole K.
+    Computed with a float64 matrix product, which is exact here (|sum| < 2^53)."""
+    a = qa.astype(np.float64)
+    w = np.ascontiguousarray(qw).view(np.int8).astype(np.float64)
+    return np.rint(a @ w.T).astype(np.int64).astype(np.int32)
 
 
 def woq_linear_int8(
@@ -438,8 +439,8 @@ def woq_linear_int8(
     C = np.zeros((M, N), dtype=np.float32)
     if bias is not None:
         C += np.asarray(bias, dtype=np.float32)[None, :]
-    qa64 = qa.astype(np.int64)
-    qw64 = qw.astype(np.int64)
+    qa64 = qa.astype(np.float64)  # float64 products and sums of int8 codes are exact
+    qw64 = qw.astype(np.float64)
     for k0 in range(0, K, block_k):
         qc = (qa64[:, k0 : k0 + block_k] @ qw64[:, k0 : k0 + block_k].T).astype(np.float32)
         C = (C + ((qc * sa[:, None]).astype(np.float32) * sw[None, :]).astype(np.float32)).astype(
