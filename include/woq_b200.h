@@ -86,6 +86,9 @@ extern "C" {
  * kernel whose tiling exists (the streaming kernel takes large M in 16-token passes). */
 #define WOQ_B200_LAYOUT_STREAM_ONLY 0x2
 #define WOQ_B200_LAYOUT_TC_ONLY 0x4
+/* GPTQ / AWQ weights whose scales and zero points were already brought to [N, groups]
+ * (what the reference's Python loaders hand to weight_only_qlinear_prepack_int4). */
+#define WOQ_B200_LAYOUT_SCALES_NK 0x8
 
 /* kernel selection for INT4 weights.  AUTO, TENSOR_CORE and STREAM all multiply by the
  * bf16-rounded dequantised weights bf16((q - zp) * bf16(scale)) and differ only in summation

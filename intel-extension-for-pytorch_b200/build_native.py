@@ -29,7 +29,7 @@ CUDA_SOURCES = [
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17",
-    "--shared", "-Xcompiler", "-fPIC",
+    "--shared", "-Xcompiler", "-fPIC", "-Xlinker", "-soname=libwoq_b200.so",
 ]
 
 

@@ -1,0 +1,419 @@
+// PyTorch operator registration for the WOQ linear path, CUDA dispatch key.
+//
+// Mirrors the reference's op surface for this path so that its Python modules work unchanged:
+//   torch_ipex::{ipex_woq_linear, woq_linear_gelu, woq_linear_new_gelu, woq_linear_relu,
+//                woq_linear_silu, woq_linear_add, woq_linear_add_add, woq_linear_mul, woq_linear}
+//       (reference: csrc/cpu/aten/Linear.cpp:1025-1108)
+//   ipex_prepack::{weight_only_qlinear_prepack, weight_only_qlinear_prepack_int4,
+//                  woq_linear_unpack_weight} and the class ipex_prepack.WoqLinearOpContext
+//       (reference: csrc/cpu/jit/cpu/kernels/RegisterOpContextClass.cpp:127-222)
+// plus torch_ipex::woq_linear_silu_mul (the reference's two-op gate/up composition as one op).
+// Everything numeric happens behind the C ABI of libwoq_b200.so; this file only converts
+// between tensors and pointers.  A missing CUDA device or library is an error, never a
+// fallback.
+#include <ATen/ATen.h>
+#include <ATen/autocast_mode.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/custom_class.h>
+#include <torch/library.h>
+
+#include <map>
+#include <mutex>
+
+#include "../../include/woq_b200.h"
+
+namespace {
+
+constexpr int64_t kHandleMagic = 0x574f5148414e444cll;  // "WOQHANDL"
+
+int dtype_code(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return WOQ_B200_T_F32;
+    case at::kHalf: return WOQ_B200_T_F16;
+    case at::kBFloat16: return WOQ_B200_T_BF16;
+    case at::kByte: return WOQ_B200_T_U8;
+    case at::kChar: return WOQ_B200_T_S8;
+    default: TORCH_CHECK(false, "WOQ: unsupported tensor dtype ", t.scalar_type());
+  }
+}
+
+#define WOQ_CHECK(expr)                                                       \
+  do {                                                                        \
+    int rc__ = (expr);                                                        \
+    TORCH_CHECK(rc__ == WOQ_B200_OK, "WOQ: ", woq_b200_last_error(), " (status ", rc__, ")"); \
+  } while (0)
+
+// One zeroed workspace per (device, stream); grows on demand.  Calls on one stream are ordered,
+// which is what a shared workspace needs.
+at::Tensor& workspace_for(c10::DeviceIndex dev, cudaStream_t stream, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, at::Tensor> pool;
+  std::lock_guard<std::mutex> lock(mu);
+  auto& t = pool[{dev, stream}];
+  if (!t.defined() || static_cast<size_t>(t.numel()) < bytes) {
+    t = at::zeros({static_cast<int64_t>(bytes)},
+                  at::TensorOptions().dtype(at::kByte).device(at::Device(at::kCUDA, dev)));
+  }
+  return t;
+}
+
+struct WoqLinearOpContext : torch::CustomClassHolder {
+  int64_t magic = kHandleMagic;
+  woq_b200_ctx* ctx = nullptr;
+  // constructor arguments, kept so that the context can be pickled in a layout-independent way
+  int64_t weight_dtype, group_size, lowp_mode, act_quant_mode;
+  bool cache_weight_for_large_batch;
+  std::vector<int64_t> weight_shape;  // [N, K]
+  at::Tensor scales, zero_points, bias, g_idx;
+  c10::optional<int64_t> batch_size;
+  c10::DeviceIndex device = 0;
+  int layout_flags = 0;
+
+  ~WoqLinearOpContext() override {
+    if (ctx) woq_b200_ctx_destroy(ctx);
+  }
+
+  static c10::intrusive_ptr<WoqLinearOpContext> create(
+      at::Tensor weight, int64_t weight_dtype, std::vector<int64_t> weight_shape, at::Tensor scales,
+      c10::optional<at::Tensor> zero_points, c10::optional<at::Tensor> bias,
+      c10::optional<at::Tensor> g_idx, c10::optional<int64_t> batch_size, int64_t group_size,
+      int64_t lowp_mode, int64_t act_quant_mode, bool cache_weight_for_large_batch,
+      int64_t weight_format, int64_t layout_flags) {
+    TORCH_CHECK(!(g_idx.has_value() && g_idx->defined()),
+                "WOQ: GPTQ act-order (g_idx) is not supported by this build");
+    TORCH_CHECK(weight_shape.size() == 2, "WOQ: weight_shape must be [N, K]");
+    auto self = c10::make_intrusive<WoqLinearOpContext>();
+    // everything lives on the weight's CUDA device (CPU tensors are moved to the current one)
+    at::Device dev = weight.is_cuda() ? weight.device()
+                                      : at::Device(at::kCUDA, at::cuda::current_device());
+    c10::cuda::CUDAGuard guard(dev);
+    auto to_dev = [&](const at::Tensor& t) { return t.to(dev).contiguous(); };
+    at::Tensor w = to_dev(weight);
+    at::Tensor s = to_dev(scales.dim() > 2 ? scales.squeeze() : scales);
+    if (s.scalar_type() == at::kDouble) s = s.to(at::kFloat);
+    at::Tensor z, b;
+    if (zero_points.has_value() && zero_points->defined()) {
+      z = to_dev(zero_points->dim() > 2 ? zero_points->squeeze() : *zero_points);
+      if (z.scalar_type() != at::kFloat && z.scalar_type() != at::kByte) z = z.to(at::kFloat);
+    }
+    if (bias.has_value() && bias->defined()) {
+      b = to_dev(*bias);
+      if (b.scalar_type() != at::kFloat && b.scalar_type() != at::kBFloat16) b = b.to(at::kFloat);
+    }
+    woq_b200_desc d{};
+    d.n = weight_shape[0];
+    d.k = weight_shape[1];
+    d.weight_dtype = static_cast<int32_t>(weight_dtype);
+    d.group_size = static_cast<int32_t>(group_size);
+    d.lowp_mode = static_cast<int32_t>(lowp_mode);
+    d.act_quant_mode = static_cast<int32_t>(act_quant_mode);
+    d.weight_format = static_cast<int32_t>(weight_format);
+    d.scale_dtype = dtype_code(s);
+    d.zp_dtype = z.defined() ? dtype_code(z) : WOQ_B200_T_NONE;
+    d.bias_dtype = b.defined() ? dtype_code(b) : WOQ_B200_T_NONE;
+    d.layout_flags = static_cast<int32_t>(layout_flags) | WOQ_B200_LAYOUT_SCALES_NK;
+    d.kernel_hint = WOQ_B200_HINT_AUTO;
+    auto stream = at::cuda::getCurrentCUDAStream(dev.index());
+    WOQ_CHECK(woq_b200_ctx_create(&d, w.data_ptr(), s.data_ptr(), z.defined() ? z.data_ptr() : nullptr,
+                                  b.defined() ? b.data_ptr() : nullptr, stream.stream(), &self->ctx));
+    self->weight_dtype = weight_dtype;
+    self->group_size = group_size;
+    self->lowp_mode = lowp_mode;
+    self->act_quant_mode = act_quant_mode;
+    self->cache_weight_for_large_batch = cache_weight_for_large_batch;
+    self->weight_shape = weight_shape;
+    self->scales = s;
+    self->zero_points = z;
+    self->bias = b;
+    self->batch_size = batch_size;
+    self->device = dev.index();
+    self->layout_flags = static_cast<int>(layout_flags);
+    return self;
+  }
+
+  // plain [N, K/2] u8 (INT4) or [N, K] s8 (INT8): the reference's to_public(get_weight())
+  at::Tensor get_weight() {
+    c10::cuda::CUDAGuard guard(device);
+    const bool int4 = weight_dtype == WOQ_B200_DTYPE_INT4;
+    auto out = at::empty({weight_shape[0], int4 ? (weight_shape[1] + 1) / 2 : weight_shape[1]},
+                         at::TensorOptions().dtype(int4 ? at::kByte : at::kChar).device(at::kCUDA, device));
+    WOQ_CHECK(woq_b200_ctx_unpack(ctx, out.data_ptr(), at::cuda::getCurrentCUDAStream(device).stream()));
+    return out;
+  }
+  at::Tensor to_public(const at::Tensor& w) { return w; }
+  c10::optional<at::Tensor> get_bias() { return bias.defined() ? c10::make_optional(bias) : c10::nullopt; }
+  at::Tensor get_scales() { return scales; }
+  c10::optional<at::Tensor> get_zero_points() {
+    return zero_points.defined() ? c10::make_optional(zero_points) : c10::nullopt;
+  }
+  std::vector<int64_t> get_weight_shape() { return weight_shape; }
+  c10::optional<at::Tensor> get_g_idx() { return c10::nullopt; }
+  c10::optional<at::Tensor> get_cached_weight() { return c10::nullopt; }
+  c10::optional<at::Tensor> get_cached_compensation() { return c10::nullopt; }
+  at::Tensor pack(const at::Tensor& w) { return w; }
+  // CPU int64 tensor holding the raw pointer to this object (non-owning), as in the reference
+  at::Tensor get_data_handle() {
+    auto t = at::empty({1}, at::TensorOptions().dtype(at::kLong));
+    t.data_ptr<int64_t>()[0] = reinterpret_cast<int64_t>(this);
+    return t;
+  }
+};
+
+WoqLinearOpContext* from_handle(const at::Tensor& handle) {
+  TORCH_CHECK(handle.device().is_cpu() && handle.scalar_type() == at::kLong && handle.numel() == 1,
+              "WOQ: W_prepack must be the 1-element CPU int64 handle of a WoqLinearOpContext");
+  auto* c = reinterpret_cast<WoqLinearOpContext*>(handle.data_ptr<int64_t>()[0]);
+  TORCH_CHECK(c != nullptr && c->magic == kHandleMagic, "WOQ: stale or foreign op-context handle");
+  return c;
+}
+
+at::Tensor run(WoqLinearOpContext* c, const at::Tensor& input, int32_t fusion,
+               const std::vector<at::Tensor>& others) {
+  TORCH_CHECK(input.is_cuda(), "WOQ: input must be a CUDA tensor");
+  TORCH_CHECK(input.get_device() == c->device, "WOQ: input is on cuda:", input.get_device(),
+              " but the weights are on cuda:", static_cast<int>(c->device));
+  const int64_t K = c->weight_shape[1], N = c->weight_shape[0];
+  TORCH_CHECK(input.size(-1) == K, "WOQ: the last dimension of input (", input.size(-1),
+              ") does not match the weight's in_features (", K, ")");
+  c10::cuda::CUDAGuard guard(c->device);
+  at::Tensor x = input.reshape({-1, K});
+  const auto in_dtype = x.scalar_type();
+  if (in_dtype != at::kBFloat16) x = x.to(at::kBFloat16);  // compute dtype of this path
+  if (x.stride(-1) != 1 || (x.stride(0) % 8) != 0 || (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15))
+    x = x.contiguous();
+  const int64_t M = x.size(0);
+  const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? N / 2 : N;
+  at::Tensor y = at::empty({M, n_out}, x.options());
+  std::vector<at::Tensor> oth;
+  std::vector<const void*> optr;
+  for (auto& o : others) {
+    at::Tensor t = o.reshape({-1, n_out});
+    TORCH_CHECK(t.size(0) == M, "WOQ: extra operand has ", t.size(0), " rows, expected ", M);
+    if (t.scalar_type() != at::kBFloat16) t = t.to(at::kBFloat16);
+    oth.push_back(t.contiguous());
+    optr.push_back(oth.back().data_ptr());
+  }
+  auto stream = at::cuda::getCurrentCUDAStream(c->device);
+  if (M > 0) {
+    const size_t need = woq_b200_workspace_bytes(c->ctx, M);
+    at::Tensor& ws = workspace_for(c->device, stream.stream(), need);
+    WOQ_CHECK(woq_b200_linear(c->ctx, x.data_ptr(), M, x.stride(0), fusion,
+                              optr.empty() ? nullptr : optr.data(), static_cast<int32_t>(optr.size()),
+                              y.data_ptr(), y.stride(0), ws.data_ptr(), ws.numel(), stream.stream()));
+  }
+  auto sizes = input.sizes().vec();
+  sizes.back() = n_out;
+  y = y.view(sizes);
+  return in_dtype == at::kBFloat16 ? y : y.to(in_dtype);
+}
+
+at::Tensor woq_unary(const at::Tensor& input, const at::Tensor& handle, int32_t fusion) {
+  return run(from_handle(handle), input, fusion, {});
+}
+
+at::Tensor ipex_woq_linear(const at::Tensor& i, const at::Tensor& h) { return woq_unary(i, h, WOQ_B200_FUSE_NONE); }
+at::Tensor woq_linear_gelu(const at::Tensor& i, const at::Tensor& h) { return woq_unary(i, h, WOQ_B200_FUSE_GELU_ERF); }
+at::Tensor woq_linear_new_gelu(const at::Tensor& i, const at::Tensor& h) { return woq_unary(i, h, WOQ_B200_FUSE_GELU_TANH); }
+at::Tensor woq_linear_relu(const at::Tensor& i, const at::Tensor& h) { return woq_unary(i, h, WOQ_B200_FUSE_RELU); }
+at::Tensor woq_linear_silu(const at::Tensor& i, const at::Tensor& h) { return woq_unary(i, h, WOQ_B200_FUSE_SILU); }
+at::Tensor woq_linear_silu_mul(const at::Tensor& i, const at::Tensor& h) { return woq_unary(i, h, WOQ_B200_FUSE_SILU_MUL); }
+at::Tensor woq_linear_add(const at::Tensor& i, const at::Tensor& h, const std::vector<at::Tensor>& o) {
+  TORCH_CHECK(o.size() >= 1, "WOQ: woq_linear_add takes one extra tensor");
+  return run(from_handle(h), i, WOQ_B200_FUSE_ADD, {o[0]});
+}
+at::Tensor woq_linear_add_add(const at::Tensor& i, const at::Tensor& h, const std::vector<at::Tensor>& o) {
+  TORCH_CHECK(o.size() >= 2, "WOQ: woq_linear_add_add takes two extra tensors");
+  return run(from_handle(h), i, WOQ_B200_FUSE_ADD_ADD, {o[0], o[1]});
+}
+at::Tensor woq_linear_mul(const at::Tensor& i, const at::Tensor& h, const std::vector<at::Tensor>& o) {
+  TORCH_CHECK(o.size() >= 1, "WOQ: woq_linear_mul takes one extra tensor");
+  return run(from_handle(h), i, WOQ_B200_FUSE_MUL, {o[0]});
+}
+
+int64_t dtype_from_str(const std::string& s) {
+  if (s == "int8") return WOQ_B200_DTYPE_INT8;
+  if (s == "int4") return WOQ_B200_DTYPE_INT4;
+  if (s == "nf4") return WOQ_B200_DTYPE_NF4;
+  if (s == "fp8") return WOQ_B200_DTYPE_FP8;
+  TORCH_CHECK(false, "WOQ: Unexpected weight dtype: ", s);
+}
+
+// context-free form: packs, runs, and drops the context (reference: Linear.cpp:556-617)
+at::Tensor woq_linear(const at::Tensor& input, const at::Tensor& qweight, const std::string& weight_dtype,
+                      const std::vector<int64_t>& weight_shape, const std::vector<at::Tensor>& weight_scales,
+                      const c10::optional<std::vector<at::Tensor>>& weight_zeros,
+                      const c10::optional<std::vector<at::Tensor>>& bias,
+                      const c10::optional<at::Tensor>& g_idx, int64_t group_size, int64_t lowp_mode,
+                      int64_t act_quant_mode, const c10::optional<at::Tensor>& compensation) {
+  TORCH_CHECK(!weight_scales.empty(), "WOQ: weight_scales is empty");
+  c10::optional<at::Tensor> z, b;
+  if (weight_zeros.has_value() && !weight_zeros->empty()) z = (*weight_zeros)[0];
+  if (bias.has_value() && !bias->empty() && (*bias)[0].defined()) b = (*bias)[0];
+  auto ctx = WoqLinearOpContext::create(qweight, dtype_from_str(weight_dtype), weight_shape, weight_scales[0],
+                                        z, b, g_idx, c10::nullopt, group_size, lowp_mode, act_quant_mode,
+                                        false, WOQ_B200_FMT_PLAIN, 0);
+  return run(ctx.get(), input, WOQ_B200_FUSE_NONE, {});
+}
+
+c10::intrusive_ptr<WoqLinearOpContext> prepack(
+    at::Tensor W, int64_t W_dtype, std::vector<int64_t> W_shape, at::Tensor scales,
+    c10::optional<at::Tensor> zero_points, c10::optional<at::Tensor> B, c10::optional<at::Tensor> g_idx,
+    c10::optional<int64_t> batch_size, int64_t group_size, int64_t lowp_mode, int64_t act_quant_mode,
+    bool cache_weight_for_large_batch) {
+  return WoqLinearOpContext::create(W, W_dtype, W_shape, scales, zero_points, B, g_idx, batch_size,
+                                    group_size, lowp_mode, act_quant_mode, cache_weight_for_large_batch,
+                                    WOQ_B200_FMT_PLAIN, 0);
+}
+
+c10::intrusive_ptr<WoqLinearOpContext> prepack_int4(
+    at::Tensor W, at::Tensor scales, c10::optional<at::Tensor> zeros, c10::optional<at::Tensor> B,
+    c10::optional<at::Tensor> g_idx, c10::optional<int64_t> batch_size, int64_t group_size,
+    int64_t lowp_mode, int64_t act_quant_mode, bool cache_weight_for_large_batch, int64_t weight_format) {
+  // scales / zeros arrive as [N, groups] (the Python side has converted checkpoint layouts)
+  int64_t N, K;
+  if (weight_format == WOQ_B200_FMT_GPTQ) {
+    N = W.size(1);
+    K = W.size(0) * 8;
+  } else if (weight_format == WOQ_B200_FMT_AWQ) {
+    N = W.size(1) * 8;
+    K = W.size(0);
+  } else {
+    N = W.size(0);
+    K = W.size(1) * (W.scalar_type() == at::kInt ? 8 : 2);
+    if (W.scalar_type() == at::kInt) W = W.contiguous().view(at::kByte);  // 8 nibbles, low first
+  }
+  c10::optional<at::Tensor> z;
+  if (zeros.has_value() && zeros->defined()) z = zeros->to(at::kFloat);
+  return WoqLinearOpContext::create(W, WOQ_B200_DTYPE_INT4, {N, K}, scales, z, B, g_idx, batch_size,
+                                    group_size, lowp_mode, act_quant_mode, cache_weight_for_large_batch,
+                                    weight_format, 0);
+}
+
+c10::intrusive_ptr<WoqLinearOpContext> prepack_gate_up(
+    at::Tensor W, int64_t W_dtype, std::vector<int64_t> W_shape, at::Tensor scales,
+    c10::optional<at::Tensor> zero_points, c10::optional<at::Tensor> B, int64_t group_size,
+    int64_t lowp_mode, int64_t act_quant_mode) {
+  return WoqLinearOpContext::create(W, W_dtype, W_shape, scales, zero_points, B, c10::nullopt, c10::nullopt,
+                                    group_size, lowp_mode, act_quant_mode, false, WOQ_B200_FMT_PLAIN,
+                                    WOQ_B200_LAYOUT_GATE_UP);
+}
+
+at::Tensor unpack_weight(const at::Tensor& weight, const std::string&, const std::vector<int64_t>&, int64_t) {
+  return weight;  // weights handed out by get_weight() are already in the public plain format
+}
+
+// AutocastCUDA: cast the activation to the autocast dtype, like the reference's AutocastCPU
+// wrappers (csrc/cpu/aten/Linear.cpp:874-1005)
+at::Tensor autocast_input(const at::Tensor& x) {
+  return x.is_floating_point() ? x.to(at::autocast::get_autocast_dtype(at::kCUDA)) : x;
+}
+#define AUTOCAST_UNARY(name)                                                          \
+  at::Tensor name##_autocast(const at::Tensor& i, const at::Tensor& h) {              \
+    c10::impl::ExcludeDispatchKeyGuard no_autocast(c10::DispatchKey::AutocastCUDA);   \
+    return name(autocast_input(i), h);                                                \
+  }
+AUTOCAST_UNARY(ipex_woq_linear)
+AUTOCAST_UNARY(woq_linear_gelu)
+AUTOCAST_UNARY(woq_linear_new_gelu)
+AUTOCAST_UNARY(woq_linear_relu)
+AUTOCAST_UNARY(woq_linear_silu)
+AUTOCAST_UNARY(woq_linear_silu_mul)
+#define AUTOCAST_BINARY(name)                                                                        \
+  at::Tensor name##_autocast(const at::Tensor& i, const at::Tensor& h, const std::vector<at::Tensor>& o) { \
+    c10::impl::ExcludeDispatchKeyGuard no_autocast(c10::DispatchKey::AutocastCUDA);                  \
+    return name(autocast_input(i), h, o);                                                            \
+  }
+AUTOCAST_BINARY(woq_linear_add)
+AUTOCAST_BINARY(woq_linear_add_add)
+AUTOCAST_BINARY(woq_linear_mul)
+
+}  // namespace
+
+TORCH_LIBRARY(ipex_prepack, m) {
+  m.class_<WoqLinearOpContext>("WoqLinearOpContext")
+      .def("get_weight", &WoqLinearOpContext::get_weight)
+      .def("get_bias", &WoqLinearOpContext::get_bias)
+      .def("get_scales", &WoqLinearOpContext::get_scales)
+      .def("get_zero_points", &WoqLinearOpContext::get_zero_points)
+      .def("get_weight_shape", &WoqLinearOpContext::get_weight_shape)
+      .def("get_g_idx", &WoqLinearOpContext::get_g_idx)
+      .def("get_cached_weight", &WoqLinearOpContext::get_cached_weight)
+      .def("get_cached_compensation", &WoqLinearOpContext::get_cached_compensation)
+      .def("pack", &WoqLinearOpContext::pack)
+      .def("to_public", &WoqLinearOpContext::to_public)
+      .def("get_data_handle", &WoqLinearOpContext::get_data_handle)
+      .def_pickle(
+          // state: plain weight + every constructor argument (layout-independent)
+          [](const c10::intrusive_ptr<WoqLinearOpContext>& self) {
+            return std::make_tuple(self->get_weight().cpu(), self->weight_dtype, self->weight_shape,
+                                   self->scales.cpu(),
+                                   self->zero_points.defined() ? c10::make_optional(self->zero_points.cpu()) : c10::nullopt,
+                                   self->bias.defined() ? c10::make_optional(self->bias.cpu()) : c10::nullopt,
+                                   c10::optional<at::Tensor>(), self->batch_size, self->group_size,
+                                   self->lowp_mode, self->act_quant_mode, self->cache_weight_for_large_batch,
+                                   static_cast<int64_t>(self->layout_flags));
+          },
+          [](std::tuple<at::Tensor, int64_t, std::vector<int64_t>, at::Tensor, c10::optional<at::Tensor>,
+                        c10::optional<at::Tensor>, c10::optional<at::Tensor>, c10::optional<int64_t>, int64_t,
+                        int64_t, int64_t, bool, int64_t> st) {
+            return WoqLinearOpContext::create(std::get<0>(st), std::get<1>(st), std::get<2>(st), std::get<3>(st),
+                                              std::get<4>(st), std::get<5>(st), std::get<6>(st), std::get<7>(st),
+                                              std::get<8>(st), std::get<9>(st), std::get<10>(st), std::get<11>(st),
+                                              WOQ_B200_FMT_PLAIN, std::get<12>(st));
+          });
+  m.def("weight_only_qlinear_prepack(Tensor W, int W_dtype, int[] W_shape, Tensor scales, Tensor? zero_points, "
+        "Tensor? B, Tensor? g_idx, int? batch_size, int group_size, int lowp_mode, int act_quant_mode, "
+        "bool cache_weight_for_large_batch=False) -> __torch__.torch.classes.ipex_prepack.WoqLinearOpContext",
+        prepack);
+  m.def("weight_only_qlinear_prepack_int4(Tensor W, Tensor scales, Tensor? zeros, Tensor? B, Tensor? g_idx, "
+        "int? batch_size, int group_size, int lowp_mode, int act_quant_mode, "
+        "bool cache_weight_for_large_batch=False, int weight_format=0) -> "
+        "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext",
+        prepack_int4);
+  m.def("weight_only_qlinear_prepack_gate_up(Tensor W, int W_dtype, int[] W_shape, Tensor scales, "
+        "Tensor? zero_points, Tensor? B, int group_size, int lowp_mode, int act_quant_mode) -> "
+        "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext",
+        prepack_gate_up);
+  m.def("woq_linear_unpack_weight(Tensor W, str W_dtype, int[] W_shape, int lowp_mode) -> Tensor", unpack_weight);
+}
+
+TORCH_LIBRARY(torch_ipex, m) {
+  m.def("ipex_woq_linear(Tensor input, Tensor W_prepack) -> Tensor");
+  m.def("woq_linear_gelu(Tensor input, Tensor W_prepack) -> Tensor");
+  m.def("woq_linear_new_gelu(Tensor input, Tensor W_prepack) -> Tensor");
+  m.def("woq_linear_relu(Tensor input, Tensor W_prepack) -> Tensor");
+  m.def("woq_linear_silu(Tensor input, Tensor W_prepack) -> Tensor");
+  m.def("woq_linear_silu_mul(Tensor input, Tensor W_prepack) -> Tensor");
+  m.def("woq_linear_add(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
+  m.def("woq_linear_add_add(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
+  m.def("woq_linear_mul(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
+  m.def("woq_linear(Tensor input, Tensor qweight, str weight_dtype, int[] weight_shape, Tensor[] weight_scales, "
+        "Tensor[]? weight_zeros, Tensor[]? bias, Tensor? g_idx, int group_size, int lowp_mode, "
+        "int act_quant_mode, Tensor? compensation) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(torch_ipex, CUDA, m) {
+  m.impl("ipex_woq_linear", ipex_woq_linear);
+  m.impl("woq_linear_gelu", woq_linear_gelu);
+  m.impl("woq_linear_new_gelu", woq_linear_new_gelu);
+  m.impl("woq_linear_relu", woq_linear_relu);
+  m.impl("woq_linear_silu", woq_linear_silu);
+  m.impl("woq_linear_silu_mul", woq_linear_silu_mul);
+  m.impl("woq_linear_add", woq_linear_add);
+  m.impl("woq_linear_add_add", woq_linear_add_add);
+  m.impl("woq_linear_mul", woq_linear_mul);
+  m.impl("woq_linear", woq_linear);
+}
+
+TORCH_LIBRARY_IMPL(torch_ipex, AutocastCUDA, m) {
+  m.impl("ipex_woq_linear", ipex_woq_linear_autocast);
+  m.impl("woq_linear_gelu", woq_linear_gelu_autocast);
+  m.impl("woq_linear_new_gelu", woq_linear_new_gelu_autocast);
+  m.impl("woq_linear_relu", woq_linear_relu_autocast);
+  m.impl("woq_linear_silu", woq_linear_silu_autocast);
+  m.impl("woq_linear_silu_mul", woq_linear_silu_mul_autocast);
+  m.impl("woq_linear_add", woq_linear_add_autocast);
+  m.impl("woq_linear_add_add", woq_linear_add_add_autocast);
+  m.impl("woq_linear_mul", woq_linear_mul_autocast);
+}

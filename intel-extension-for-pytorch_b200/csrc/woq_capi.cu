@@ -306,7 +306,7 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
       CUDA_TRY_C(woq::launch_gptq_to_plain(static_cast<const int32_t*>(qweight), tmp_plain,
                                            (int)d->n, (int)d->k, stream));
     plain = tmp_plain;
-    transposed = 1;
+    transposed = (d->layout_flags & WOQ_B200_LAYOUT_SCALES_NK) ? 0 : 1;
     if (zero_points && d->zp_dtype != WOQ_B200_T_F32 && d->zp_dtype != WOQ_B200_T_U8) {
       // packed int32 zero points [groups][N/8]
       CUDA_TRY_C(cudaMalloc(&tmp_zp, static_cast<size_t>(d->n) * c->groups));

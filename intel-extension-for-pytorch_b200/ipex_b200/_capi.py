@@ -22,7 +22,7 @@ FMT_PLAIN, FMT_GPTQ, FMT_AWQ = 0, 1, 2
 FUSE_NONE, FUSE_GELU_ERF, FUSE_GELU_TANH, FUSE_RELU, FUSE_SILU = 0, 1, 2, 3, 4
 FUSE_ADD, FUSE_ADD_ADD, FUSE_MUL, FUSE_SILU_MUL = 0x10, 0x20, 0x30, 0x100
 T_NONE, T_F32, T_F16, T_BF16, T_U8, T_S8, T_I32 = 0, 1, 2, 3, 4, 5, 6
-LAYOUT_GATE_UP, LAYOUT_STREAM_ONLY, LAYOUT_TC_ONLY = 1, 2, 4
+LAYOUT_GATE_UP, LAYOUT_STREAM_ONLY, LAYOUT_TC_ONLY, LAYOUT_SCALES_NK = 1, 2, 4, 8
 HINT_AUTO, HINT_TENSOR_CORE, HINT_STREAM, HINT_STREAM_FAST = 0, 1, 2, 3
 
 EXPORTS = [

@@ -1,0 +1,87 @@
+"""CPU-only checks of the Python surface: the extension loads, the operators exist with the
+reference's schemas, and the tensor-parallel helper reduces over a 2-rank gloo group."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+@pytest.fixture(scope="module")
+def ipex():
+    import importlib.util
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "build_ext", os.path.join(root, "intel-extension-for-pytorch_b200", "build_ext.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+    import ipex_b200
+
+    ipex_b200.load_ops()
+    return ipex_b200
+
+
+def test_operator_schemas(ipex):
+    s = str(torch.ops.torch_ipex.ipex_woq_linear.default._schema)
+    assert s == "torch_ipex::ipex_woq_linear(Tensor input, Tensor W_prepack) -> Tensor"
+    for name in ("woq_linear_gelu", "woq_linear_new_gelu", "woq_linear_relu", "woq_linear_silu"):
+        assert "(Tensor input, Tensor W_prepack) -> Tensor" in str(getattr(torch.ops.torch_ipex, name).default._schema)
+    for name in ("woq_linear_add", "woq_linear_add_add", "woq_linear_mul"):
+        assert "Tensor[] others" in str(getattr(torch.ops.torch_ipex, name).default._schema)
+    s = str(torch.ops.torch_ipex.woq_linear.default._schema)
+    assert "str weight_dtype, int[] weight_shape, Tensor[] weight_scales" in s
+    s = str(torch.ops.ipex_prepack.weight_only_qlinear_prepack.default._schema)
+    assert "int W_dtype, int[] W_shape, Tensor scales, Tensor? zero_points" in s
+    assert "WoqLinearOpContext" in s
+    s = str(torch.ops.ipex_prepack.weight_only_qlinear_prepack_int4.default._schema)
+    assert "int weight_format=0" in s
+
+
+def test_cpu_tensors_are_refused_not_computed(ipex):
+    """There is no CPU kernel behind these operators."""
+    x = torch.randn(2, 64).bfloat16()
+    h = torch.zeros(1, dtype=torch.int64)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.torch_ipex.ipex_woq_linear(x, h)
+
+
+def test_surface_names(ipex):
+    q = ipex.quantization
+    assert int(q.WoqWeightDtype.INT4) == 2 and int(q.WoqLowpMode.INT8) == 3
+    assert int(q.WoqActQuantMode.PER_BATCH_SYM) == 6
+    from ipex_b200.llm.quantization import IPEXWeightOnlyQuantizedLinear, QuantDtype, QuantMethod
+    from ipex_b200.nn.modules import IpexWoqLinearAllreduce, WeightOnlyQuantizedLinear, WoqWeightFormat
+
+    assert "cuda" in IPEXWeightOnlyQuantizedLinear.module_mapping
+    assert int(WoqWeightFormat.AWQ_FORMAT) == 2 and int(QuantMethod.AWQ_GEMM) == 1 and int(QuantDtype.INT4) == 0
+    assert issubclass(IpexWoqLinearAllreduce, WeightOnlyQuantizedLinear)
+
+
+def _tp_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "intel-extension-for-pytorch_b200"))
+    from ipex_b200.nn.modules.weight_only_quantization import all_reduce_and_bias_add
+
+    torch.manual_seed(0)
+    full = torch.randn(4, 8, 32)           # [rank, M, N] partial outputs of a row-parallel layer
+    bias = torch.randn(32)
+    out = all_reduce_and_bias_add(None, bias, full[rank].clone())
+    expect = full[:world].sum(0) + bias
+    ret[rank] = bool(torch.allclose(out, expect, atol=1e-6))
+    dist.destroy_process_group()
+
+
+def test_row_parallel_reduce_two_ranks_gloo(ipex):
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29500 + os.getpid() % 500
+    mp.spawn(_tp_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert all(ret[r] for r in range(world))
