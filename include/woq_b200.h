@@ -196,6 +196,16 @@ int woq_b200_linear_scatter(const woq_b200_ctx* ctx, const void* x, int64_t m, i
                             int64_t ld_out, void* workspace, size_t workspace_bytes,
                             void* stream);
 
+/* One expert of a Mixtral-style layer in one call: gather the expert's tokens
+ * x = hidden[token_idx[i], :], a = silu(gate(x)) * up(x) on the stacked gate/up weight `w13`
+ * (created with WOQ_B200_LAYOUT_GATE_UP), y = w2(a), out[token_idx[i], :] = bf16(out + y[i] * w[i]).
+ * Replaces mixtral_moe_woq_kernl_impl (csrc/cpu/aten/kernels/MoEKrnl.cpp:254-285).  token_weight is
+ * bf16 [tokens]; a token may appear at most once per call. */
+size_t woq_b200_moe_workspace_bytes(const woq_b200_ctx* w13, const woq_b200_ctx* w2, int64_t tokens);
+int woq_b200_moe_expert(const woq_b200_ctx* w13, const woq_b200_ctx* w2, const void* hidden, int64_t ldh,
+                        const int32_t* token_idx, const void* token_weight, int64_t tokens, void* out,
+                        int64_t ld_out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Parity hooks -------------------------------------------------------------------------
  * Dequantised weight [N, K] bf16 produced by the same device routine the tensor-core kernel
  * uses for its tiles (the reference's Dequantize<bfloat16>, csrc/cpu/aten/utils/woq.h:1501-1581). */

@@ -231,6 +231,35 @@ at::Tensor woq_linear_mul(const at::Tensor& i, const at::Tensor& h, const std::v
   return run(from_handle(h), i, WOQ_B200_FUSE_MUL, {o[0]});
 }
 
+// reference: csrc/cpu/aten/MoE.cpp:260-288 + kernels/MoEKrnl.cpp:254-285.  top_x = the tokens routed to
+// this expert, idx = which of their top-k slots; the three handles are the expert's w1 / w3 / w2.
+at::Tensor mixtral_moe_woq(const at::Tensor& hidden_states, const at::Tensor& top_x, const at::Tensor& idx,
+                           const at::Tensor& gate_wei, const at::Tensor& up_wei, const at::Tensor& down_wei,
+                           const at::Tensor& routing_weights, at::Tensor output, bool is_distributed) {
+  if (top_x.size(0) == 0) return output;
+  TORCH_CHECK(!is_distributed, "WOQ: the distributed MoE all-reduce is done by the caller in this build");
+  TORCH_CHECK(output.is_cuda() && output.scalar_type() == at::kBFloat16 && output.is_contiguous(),
+              "WOQ: MoE output must be a contiguous bf16 CUDA tensor");
+  auto* g = from_handle(gate_wei);
+  auto* u = from_handle(up_wei);
+  auto* d = from_handle(down_wei);
+  c10::cuda::CUDAGuard guard(d->device);
+  at::Tensor tx = top_x.to(hidden_states.device());
+  at::Tensor x = hidden_states.index_select(0, tx);
+  at::Tensor a = run(u, x, WOQ_B200_FUSE_MUL, {run(g, x, WOQ_B200_FUSE_SILU, {})});
+  at::Tensor w = routing_weights.index({tx, idx.to(hidden_states.device())}).to(at::kBFloat16).contiguous();
+  at::Tensor ti = tx.to(at::kInt).contiguous();
+  if (a.scalar_type() != at::kBFloat16) a = a.to(at::kBFloat16);
+  a = a.contiguous();
+  const int64_t M = a.size(0);
+  auto stream = at::cuda::getCurrentCUDAStream(d->device);
+  at::Tensor& ws = workspace_for(d->device, stream.stream(), woq_b200_workspace_bytes(d->ctx, M));
+  WOQ_CHECK(woq_b200_linear_scatter(d->ctx, a.data_ptr(), M, a.stride(0), ti.data_ptr<int32_t>(), w.data_ptr(),
+                                    output.data_ptr(), output.stride(0), ws.data_ptr(), ws.numel(),
+                                    stream.stream()));
+  return output;
+}
+
 int64_t dtype_from_str(const std::string& s) {
   if (s == "int8") return WOQ_B200_DTYPE_INT8;
   if (s == "int4") return WOQ_B200_DTYPE_INT4;
@@ -388,6 +417,8 @@ TORCH_LIBRARY(torch_ipex, m) {
   m.def("woq_linear_add(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
   m.def("woq_linear_add_add(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
   m.def("woq_linear_mul(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
+  m.def("mixtral_moe_woq(Tensor hidden_states, Tensor top_x, Tensor idx, Tensor gate_wei, Tensor up_wei, "
+        "Tensor down_wei, Tensor routing_weights, Tensor output, bool is_distributed) -> Tensor");
   m.def("woq_linear(Tensor input, Tensor qweight, str weight_dtype, int[] weight_shape, Tensor[] weight_scales, "
         "Tensor[]? weight_zeros, Tensor[]? bias, Tensor? g_idx, int group_size, int lowp_mode, "
         "int act_quant_mode, Tensor? compensation) -> Tensor");
@@ -404,6 +435,7 @@ TORCH_LIBRARY_IMPL(torch_ipex, CUDA, m) {
   m.impl("woq_linear_add_add", woq_linear_add_add);
   m.impl("woq_linear_mul", woq_linear_mul);
   m.impl("woq_linear", woq_linear);
+  m.impl("mixtral_moe_woq", mixtral_moe_woq);
 }
 
 TORCH_LIBRARY_IMPL(torch_ipex, AutocastCUDA, m) {

@@ -690,6 +690,44 @@ int woq_b200_linear_scatter(const woq_b200_ctx* c, const void* x, int64_t m, int
   return WOQ_B200_OK;
 }
 
+size_t woq_b200_moe_workspace_bytes(const woq_b200_ctx* w13, const woq_b200_ctx* w2, int64_t tokens) {
+  if (check_ctx(w13) || check_ctx(w2) || tokens < 0) return 0;
+  size_t a = woq_b200_workspace_bytes(w13, tokens), b = woq_b200_workspace_bytes(w2, tokens);
+  size_t lin = ((a > b ? a : b) + 1023) / 1024 * 1024;
+  return lin + static_cast<size_t>(tokens) * (w13->desc.k + w13->desc.n / 2) * 2 + 2048;
+}
+
+int woq_b200_moe_expert(const woq_b200_ctx* w13, const woq_b200_ctx* w2, const void* hidden, int64_t ldh,
+                        const int32_t* token_idx, const void* token_weight, int64_t tokens, void* out,
+                        int64_t ld_out, void* workspace, size_t workspace_bytes, void* stream_) {
+  if (int rc = check_ctx(w13)) return rc;
+  if (int rc = check_ctx(w2)) return rc;
+  if (tokens == 0) return WOQ_B200_OK;
+  if (!hidden || !token_idx || !token_weight || !out || !workspace || tokens < 0)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "null or negative argument");
+  if (!w13->gate_up) return fail(WOQ_B200_ERR_INVALID_ARG, "w13 must be packed with the gate/up layout");
+  if (w13->desc.n / 2 != w2->desc.k || w2->desc.n > ld_out || (w13->desc.k % 8) != 0)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "expert shapes do not chain (w13 %lldx%lld, w2 %lldx%lld)",
+                (long long)w13->desc.n, (long long)w13->desc.k, (long long)w2->desc.n, (long long)w2->desc.k);
+  const size_t need = woq_b200_moe_workspace_bytes(w13, w2, tokens);
+  if (workspace_bytes < need)
+    return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", workspace_bytes, need);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  size_t a = woq_b200_workspace_bytes(w13, tokens), b = woq_b200_workspace_bytes(w2, tokens);
+  const size_t lin = ((a > b ? a : b) + 1023) / 1024 * 1024;
+  uint8_t* w8 = static_cast<uint8_t*>(workspace);
+  __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(w8 + lin);
+  __nv_bfloat16* act = xg + tokens * w13->desc.k;
+  act = reinterpret_cast<__nv_bfloat16*>((reinterpret_cast<uintptr_t>(act) + 1023) / 1024 * 1024);
+  CUDA_TRY(woq::launch_gather_rows(static_cast<const __nv_bfloat16*>(hidden), ldh, token_idx, xg, tokens,
+                                   (int)w13->desc.k, stream));
+  if (int rc = woq_b200_linear(w13, xg, tokens, w13->desc.k, WOQ_B200_FUSE_SILU_MUL, nullptr, 0, act,
+                               w13->desc.n / 2, workspace, lin, stream_))
+    return rc;
+  return woq_b200_linear_scatter(w2, act, tokens, w2->desc.k, token_idx, token_weight, out, ld_out, workspace,
+                                 lin, stream_);
+}
+
 int woq_b200_dump_dequant(const woq_b200_ctx* c, void* w_bf16, void* stream_) {
   if (int rc = check_ctx(c)) return rc;
   if (!w_bf16) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");

@@ -142,6 +142,9 @@ cudaError_t launch_dump_dequant_int4_tc(const uint8_t* tiled, const uint32_t* sz
                                         int n, int k, int tiles, int kb_per_tile, int kbpg_shift,
                                         int groups, int gate_up, cudaStream_t stream);
 
+cudaError_t launch_gather_rows(const __nv_bfloat16* x, int64_t ldx, const int32_t* idx,
+                               __nv_bfloat16* out, int64_t rows, int k, cudaStream_t stream);
+
 // AWQ / GPTQ int32 checkpoints -> plain nibble layout [n][k/2]
 cudaError_t launch_awq_to_plain(const int32_t* qweight_kn8, uint8_t* plain, int n, int k,
                                 cudaStream_t stream);

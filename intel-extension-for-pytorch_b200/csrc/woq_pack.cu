@@ -230,6 +230,19 @@ __global__ void unpack_qzeros_kernel(const int32_t* qz, uint8_t* zps, int n, int
   zps[i] = static_cast<uint8_t>((v + (plus_one ? 1u : 0u)) & 0xF);
 }
 
+// out[i, :] = x[idx[i], :] for bf16 rows of k elements (k % 8 == 0): the token gather of an
+// expert (reference: fuse_index_unsqueeze, csrc/cpu/aten/kernels/MoEKrnl.cpp:123-160)
+__global__ void gather_rows_kernel(const __nv_bfloat16* x, int64_t ldx, const int32_t* idx,
+                                   __nv_bfloat16* out, int64_t rows, int k) {
+  const int chunks = k / 8;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * chunks) return;
+  const int64_t r = i / chunks;
+  const int c = static_cast<int>(i % chunks);
+  reinterpret_cast<uint4*>(out + r * k)[c] =
+      reinterpret_cast<const uint4*>(x + static_cast<int64_t>(idx[r]) * ldx)[c];
+}
+
 inline unsigned blocks_for(int64_t n, int threads) {
   return static_cast<unsigned>((n + threads - 1) / threads);
 }
@@ -280,6 +293,13 @@ cudaError_t launch_dump_dequant_int4_tc(const uint8_t* tiled, const uint32_t* sz
   dump_dequant_int4_tc_kernel<<<blocks_for(words, 256), 256, 0, stream>>>(
       reinterpret_cast<const uint32_t*>(tiled), sz, w, n, k, tiles, kb_per_tile, kbpg_shift, groups,
       gate_up);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather_rows(const __nv_bfloat16* x, int64_t ldx, const int32_t* idx,
+                               __nv_bfloat16* out, int64_t rows, int k, cudaStream_t stream) {
+  gather_rows_kernel<<<blocks_for(rows * (k / 8), 256), 256, 0, stream>>>(x, ldx, idx, out, rows, k);
   count_launch();
   return cudaGetLastError();
 }

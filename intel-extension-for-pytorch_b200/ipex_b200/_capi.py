@@ -39,6 +39,8 @@ EXPORTS = [
     "woq_b200_linear",
     "woq_b200_linear_scatter",
     "woq_b200_linear_static_scratch",
+    "woq_b200_moe_workspace_bytes",
+    "woq_b200_moe_expert",
     "woq_b200_dump_dequant",
     "woq_b200_int8_internals",
     "woq_b200_workspace_status",
@@ -98,6 +100,9 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_linear.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
     L.woq_b200_linear_static_scratch.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp]
     L.woq_b200_linear_scatter.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
+    L.woq_b200_moe_workspace_bytes.argtypes = [vp, vp, i64]
+    L.woq_b200_moe_workspace_bytes.restype = sz
+    L.woq_b200_moe_expert.argtypes = [vp, vp, vp, i64, vp, vp, i64, vp, i64, vp, sz, vp]
     L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
     L.woq_b200_workspace_status.argtypes = [vp, vp]
@@ -307,6 +312,22 @@ class WoqContext:
                 )
             )
         return qa, sa, acc
+
+
+def moe_expert(w13: "WoqContext", w2: "WoqContext", hidden, token_idx, token_weight, out, workspace=None):
+    """woq_b200_moe_expert on torch tensors; token_idx int32 [t], token_weight bf16 [t]."""
+    t = int(token_idx.numel())
+    need = lib().woq_b200_moe_workspace_bytes(w13._h, w2._h, t)
+    ws = workspace if workspace is not None and workspace.nbytes >= need else Workspace(need, hidden.device)
+    with torch.cuda.device(hidden.device):
+        _check(
+            lib().woq_b200_moe_expert(
+                w13._h, w2._h, hidden.data_ptr(), hidden.stride(0), token_idx.data_ptr(),
+                token_weight.data_ptr(), t, out.data_ptr(), out.stride(0), ws.buf.data_ptr(), ws.nbytes,
+                _stream(),
+            )
+        )
+    return ws
 
 
 def kernel_launches() -> int:
