@@ -197,12 +197,21 @@ def run_ours(args):
     assert p == args.gpus or p == 1, f"--gpus {args.gpus} but WORLD_SIZE={p}"
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    def log(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     if p > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+
+        # a collective that cannot complete ends the run with an error instead of hanging it
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
     capi.lib()
+    log("process group up")
     m = args.m
     n_layers = args.layers
     layers = build_layers(torch, capi, quant, p, rank, n_layers, device)
+    log("layers built")
     ws = capi.Workspace(layers[0]["qkv"].workspace_bytes(m), device)
 
     bf = dict(dtype=torch.bfloat16, device=device)
@@ -247,6 +256,7 @@ def run_ours(args):
     # eager warm-up (also initialises NCCL), then capture one step in a CUDA graph
     step(hidden)
     torch.cuda.synchronize()
+    log("eager step done")
     graph = None
     if not args.no_graph:
         try:
@@ -277,9 +287,11 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    log(f"graph captured: {graph is not None}")
     for _ in range(max(3, args.warmup)):
         run_step()
     barrier()
+    log("warm-up done")
     sampler = ClockSampler(local) if rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -295,6 +307,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
+    log(f"timed region done: {ms_per_step:.3f} ms/step")
     total_w = full_layer_weight_bytes() * n_layers  # all ranks together stream the whole model
     value = total_w / (ms_per_step * 1e-3) / 1e9
     ws.status()
@@ -377,9 +390,57 @@ def run_ours(args):
         }
         if p == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = cpu_baseline(m)
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if p > 1:
-        dist.destroy_process_group()
+        # Tearing down NCCL communicators that were captured into CUDA graphs can block for
+        # minutes; every rank has its result by now, so leave without the teardown.
+        del graph, kgraph
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def run_single(args):
+    """A few launches of one linear shape (for `ncu` captures of a small case):
+    --single NxK --m M [--hint H] launches the linear `--steps` times on two weight copies."""
+    import torch
+
+    from ipex_b200 import _capi as capi
+    from ipex_b200 import quantization as quant
+
+    n, k = (int(v) for v in args.single.lower().split("x"))
+    torch.cuda.set_device(0)
+    ctxs = []
+    for i in range(2):
+        g = torch.Generator(device="cuda").manual_seed(i)
+        w = torch.randn((n, k), device="cuda", generator=g) * 0.02
+        if args.int8:
+            qw, s, _ = quant.quantize_per_channel(w, quant.WoqWeightDtype.INT8, sym_quant=True)
+            ctxs.append(capi.WoqContext(qw, s, None, None, n, k, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
+                                        act_quant_mode=capi.ACT_PER_M_SYM))
+        else:
+            qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
+            ctxs.append(capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP, capi.LOWP_BF16,
+                                        kernel_hint=args.hint))
+    x = torch.randn((args.m, k), device="cuda").bfloat16()
+    y = torch.empty((args.m, n), device="cuda", dtype=torch.bfloat16)
+    ws = capi.Workspace(ctxs[0].workspace_bytes(args.m), "cuda")
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for c in ctxs:
+        c.linear(x, out=y, workspace=ws)
+    e0.record()
+    for _ in range(args.steps):
+        for c in ctxs:
+            c.linear(x, out=y, workspace=ws)
+    e1.record()
+    torch.cuda.synchronize()
+    ws.status()
+    us = e0.elapsed_time(e1) * 1e3 / (2 * args.steps)
+    print(json.dumps({"single": args.single, "m": args.m, "int8": args.int8, "hint": args.hint,
+                      "us_per_launch": us, "weight_GBps": (n * k if args.int8 else weight_bytes(n, k)) / us / 1e3,
+                      "tflops": 2 * args.m * n * k / us / 1e6}))
 
 
 def main():
@@ -391,11 +452,17 @@ def main():
     ap.add_argument("--m", type=int, default=1, help="decode batch (tokens per step)")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--verbose", action="store_true", help="phase messages on stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
+    ap.add_argument("--int8", action="store_true", help="--single: INT8 weights with INT8 compute")
+    ap.add_argument("--hint", type=int, default=0, help="--single: kernel hint (see include/woq_b200.h)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture (profiles/)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.single:
+        run_single(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -28,7 +28,15 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kProducerWarp = kConsumerWarps, kFirstEpilogueWarp = kConsumerWarps + 1;
+// Epilogue warps take tile segments round-robin, so the global-memory round trips of one
+// segment's partial-tile protocol overlap the next segment's.
+__host__ __device__ constexpr int epilogue_warps(int tb) { return tb == 1 ? 3 : 4; }
+__host__ __device__ constexpr int block_threads(int tb) {
+  return (kConsumerWarps + 1 + epilogue_warps(tb)) * 32;
+}
+// named barriers: 1 + e "segment for epilogue warp e is in shared memory", 5 + e "... is drained"
+constexpr int kBarRedFull = 1, kBarRedFree = 5;
 constexpr int kStageKBlocks = kConsumerWarps;                 // k-blocks per stage
 constexpr int kXRowBytes = kStageKBlocks * kBlockK * 2 + 16;  // +16: bank spread between tokens
 constexpr int kRedTokStride = 68;                             // floats; conflict-free scatter
@@ -39,7 +47,6 @@ struct SmemHeader {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   int abort_flag;
-  int is_last;
 };
 
 __device__ __forceinline__ int owner_of(int64_t b, int64_t total, int64_t ctas) {
@@ -47,12 +54,59 @@ __device__ __forceinline__ int owner_of(int64_t b, int64_t total, int64_t ctas) 
   return static_cast<int>(((b + 1) * ctas - 1) / total);
 }
 
+// bias, rounding and the fused post-op for one (row, token) of tile `tl`
+__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tl, int row, int tok, float r) {
+  const int n = decode_row_to_n(p, tl, row);
+  if (tok >= p.m || n >= p.n) return;
+  if (p.bias) r += p.bias[n];
+  r = bf16_round(r);
+  if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
+    const size_t o = static_cast<size_t>(p.row_idx[tok]) * p.ldy + n;
+    const float w = __bfloat162float(p.row_w[tok]);
+    p.y[o] = __float2bfloat16_rn(__bfloat162float(p.y[o]) + r * w);
+    return;
+  }
+  const size_t o = static_cast<size_t>(tok) * p.ldy + n;
+  if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
+    r = bf16_round(r + __bfloat162float(p.other0[o]));
+    if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __bfloat162float(p.other1[o]));
+  } else if (p.fusion == FUSE_MUL) {
+    r = bf16_round(r * __bfloat162float(p.other0[o]));
+  } else {
+    r = unary_post_op(r, p.fusion);
+  }
+  p.y[o] = __float2bfloat16_rn(r);
+}
+
+// The stages a CTA walks: its share [b_begin, b_end) of the k-block sequence cut at tile
+// boundaries ("segments") and then into runs of up to kStageKBlocks k-blocks.  Producer and
+// consumers step through the same sequence.
+struct StageIter {
+  int tile, kb, k1, left, kbpt;  // current tile, next k-block, segment end, k-blocks left
+  __device__ StageIter(int tile0, int kb0, int left0, int kbpt0)
+      : tile(tile0), kb(kb0), k1(min(kbpt0, kb0 + left0)), left(left0), kbpt(kbpt0) {}
+  __device__ bool done() const { return left <= 0; }
+  __device__ int nkb() const { return min(kStageKBlocks, k1 - kb); }
+  __device__ void next(int n) {
+    kb += n;
+    left -= n;
+    if (kb == k1) {
+      if (kb == kbpt) {
+        kb = 0;
+        ++tile;
+      }
+      k1 = min(kbpt, kb + left);
+    }
+  }
+};
+
 template <int TB, bool EXACT>
-__global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
+__global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
     woq_int4_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
   constexpr int NTOK = 8 * TB;
+  constexpr int E = epilogue_warps(TB);
   const int sz_stage_bytes = (p.gps + 1) * 256;
   const int stage_bytes = kStageKBlocks * kBlockBytes + sz_stage_bytes + p.x_rows * kXRowBytes;
   const int red_tok = p.red_tok;  // tokens kept in the cross-warp reduction buffer
@@ -63,6 +117,9 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
   const int64_t total = static_cast<int64_t>(p.tiles) * p.kb_per_tile;
   const int64_t b_begin = (static_cast<int64_t>(blockIdx.x) * total) / gridDim.x;
   const int64_t b_end = (static_cast<int64_t>(blockIdx.x + 1) * total) / gridDim.x;
+  const int tile0 = static_cast<int>(b_begin / p.kb_per_tile);
+  const int kb00 = static_cast<int>(b_begin - static_cast<int64_t>(tile0) * p.kb_per_tile);
+  const int share = static_cast<int>(b_end - b_begin);
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -70,64 +127,182 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
       mbar_init(&hdr->empty[s], kConsumerWarps);
     }
     hdr->abort_flag = 0;
-    hdr->is_last = 0;
     mbar_fence_init();
   }
   __syncthreads();
+  // A following launch that opted into programmatic dependent launch may start its weight
+  // stream while this grid is still running.
+  grid_launch_dependents();
   volatile int* abort_flag = &hdr->abort_flag;
 
-  // producer and consumers walk the same sequence of stages (never across a tile boundary)
-  int tile = static_cast<int>(b_begin / p.kb_per_tile);
-  int kb0 = static_cast<int>(b_begin % p.kb_per_tile);
-  int64_t b = b_begin;
-  int slot = 0;
-  uint32_t phase = 0;
-  auto stage_len = [&]() {
-    int nkb = p.kb_per_tile - kb0;
-    if (nkb > kStageKBlocks) nkb = kStageKBlocks;
-    if (nkb > b_end - b) nkb = static_cast<int>(b_end - b);
-    return nkb;
-  };
-  auto advance = [&](int nkb) {
-    b += nkb;
-    kb0 += nkb;
-    if (kb0 == p.kb_per_tile) {
-      kb0 = 0;
-      ++tile;
-    }
-    if (++slot == p.stages) {
-      slot = 0;
-      phase ^= 1;
-    }
-  };
-
-  if (warp == kConsumerWarps) {
+  if (warp == kProducerWarp) {
     // ------------------------------ producer warp ------------------------------------
-    while (b < b_end) {
-      const int nkb = stage_len();
+    // Weights and scales never depend on the previous kernel in the stream, x does: the
+    // first pipeline fill issues the weight copies, then waits for the previous grid, then
+    // issues the x copies.
+    auto issue_weights = [&](const StageIter& it, int slot) {
+      const int nkb = it.nkb();
       uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
+      const int g0 = it.kb >> p.kbpg_shift;
+      const int ng = ((it.kb + nkb - 1) >> p.kbpg_shift) - g0 + 1;
+      uint32_t bytes = nkb * kBlockBytes;
+      if (!(p.debug & 4)) bytes += ng * 256;
+      if (!(p.debug & 2)) bytes += p.m * nkb * (kBlockK * 2);
+      mbar_arrive_expect_tx(&hdr->full[slot], bytes);
+      bulk_g2s(st, p.wq + (static_cast<size_t>(it.tile) * p.kb_per_tile + it.kb) * kBlockBytes,
+               nkb * kBlockBytes, &hdr->full[slot]);
+      if (!(p.debug & 4))
+        bulk_g2s(st + kStageKBlocks * kBlockBytes,
+                 p.sz + (static_cast<size_t>(it.tile) * p.groups + g0) * 64, ng * 256,
+                 &hdr->full[slot]);
+    };
+    auto issue_x = [&](const StageIter& it, int slot) {  // lane = token
+      if (lane < p.m && !(p.debug & 2)) {
+        uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
+        bulk_g2s(st + kStageKBlocks * kBlockBytes + sz_stage_bytes + lane * kXRowBytes,
+                 p.x + static_cast<size_t>(lane) * p.ldx + static_cast<size_t>(it.kb) * kBlockK,
+                 it.nkb() * (kBlockK * 2), &hdr->full[slot]);
+      }
+    };
+    StageIter it(tile0, kb00, share, p.kb_per_tile);
+    {
+      StageIter fill = it;
+      if (lane == 0)
+        for (int s = 0; s < p.stages && !fill.done(); ++s) {
+          issue_weights(fill, s);
+          fill.next(fill.nkb());
+        }
+      grid_dependency_wait();
+      __syncwarp();
+      for (int s = 0; s < p.stages && !it.done(); ++s) {
+        issue_x(it, s);
+        it.next(it.nkb());
+      }
+    }
+    int slot = 0;
+    uint32_t phase = 1;  // the slots are on their second use from here on
+    while (!it.done()) {
       if (lane == 0) {
         mbar_wait(&hdr->empty[slot], phase ^ 1, abort_flag, p.status, 1);
-        const int g0 = kb0 >> p.kbpg_shift;
-        const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
-        uint32_t bytes = nkb * kBlockBytes;
-        if (!(p.debug & 4)) bytes += ng * 256;
-        if (!(p.debug & 2)) bytes += p.m * nkb * (kBlockK * 2);
-        mbar_arrive_expect_tx(&hdr->full[slot], bytes);
-        bulk_g2s(st, p.wq + (static_cast<size_t>(tile) * p.kb_per_tile + kb0) * kBlockBytes,
-                 nkb * kBlockBytes, &hdr->full[slot]);
-        if (!(p.debug & 4))
-          bulk_g2s(st + kStageKBlocks * kBlockBytes,
-                   p.sz + (static_cast<size_t>(tile) * p.groups + g0) * 64, ng * 256,
-                   &hdr->full[slot]);
+        if (p.debug & 8)
+          mbar_arrive(&hdr->full[slot]);  // experiment: consumers re-read the stale stage
+        else
+          issue_weights(it, slot);
       }
       __syncwarp();
-      if (lane < p.m && !(p.debug & 2)) {
-        bulk_g2s(st + kStageKBlocks * kBlockBytes + sz_stage_bytes + lane * kXRowBytes,
-                 p.x + static_cast<size_t>(lane) * p.ldx + static_cast<size_t>(kb0) * kBlockK,
-                 nkb * (kBlockK * 2), &hdr->full[slot]);
+      if (!(p.debug & 8)) issue_x(it, slot);
+      it.next(it.nkb());
+      if (++slot == p.stages) {
+        slot = 0;
+        phase ^= 1;
       }
-      advance(nkb);
+    }
+    return;
+  }
+
+  if (warp >= kFirstEpilogueWarp) {
+    // ------------------------------ epilogue warps -------------------------------------
+    // Take the eight consumer warps' partial sums of a finished tile segment out of shared
+    // memory, so the consumers go straight on to the next tile; then either run the fused
+    // epilogue or park a partial tile and, if this CTA is the last contributor to arrive,
+    // reduce the tile in a fixed order.  Segments go round-robin over the epilogue warps.
+    const int me = warp - kFirstEpilogueWarp;
+    int turn = 0;
+    int tl = tile0, k0 = kb00, left = share;
+    bool first_segment = true;
+    bool waited = false;
+    for (; left > 0; first_segment = false, turn = (turn + 1 == E) ? 0 : turn + 1) {
+      const int k1 = min(p.kb_per_tile, k0 + left);
+      const bool whole = (k0 == 0 && k1 == p.kb_per_tile);
+      const int seg_tile = tl;
+      left -= k1 - k0;
+      k0 = 0;
+      ++tl;
+      if (turn != me) continue;
+      named_bar_sync(kBarRedFull + me, kConsumerThreads + 32);
+      // lane -> rows lane and lane + 32 (in the gate/up layout: a gate row and its up row)
+      float v0[NTOK], v1[NTOK];
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok) {
+        float s0 = 0.f, s1 = 0.f;
+        if (tok < red_tok) {
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) {
+            const float* r = red + w * (red_tok * kRedTokStride) + tok * kRedTokStride;
+            s0 += r[lane];
+            s1 += r[lane + 32];
+          }
+        }
+        v0[tok] = s0;
+        v1[tok] = s1;
+      }
+      __threadfence_block();
+      named_bar_arrive(kBarRedFree + me, kConsumerThreads + 32);
+      if (!waited) {
+        grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
+        waited = true;
+      }
+      bool do_epilogue = whole;
+      if (!whole) {
+        const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
+        float* dst = p.partials + static_cast<size_t>(my_slot) * (16 * kTileN);
+#pragma unroll
+        for (int tok = 0; tok < NTOK; ++tok)
+          if (tok < p.m) {
+            __stcg(dst + tok * kTileN + lane, v0[tok]);
+            __stcg(dst + tok * kTileN + lane + 32, v1[tok]);
+          }
+        __threadfence();
+        __syncwarp();
+        const int64_t tb0 = static_cast<int64_t>(seg_tile) * p.kb_per_tile;
+        const int c_first = owner_of(tb0, total, gridDim.x);
+        const int c_last = owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
+        unsigned old = 0;
+        if (lane == 0) old = atomicAdd(p.counters + seg_tile, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == static_cast<unsigned>(c_last - c_first)) {
+          __threadfence();
+#pragma unroll
+          for (int tok = 0; tok < NTOK; ++tok) v0[tok] = v1[tok] = 0.f;
+          for (int c = c_first; c <= c_last; ++c) {
+            const int64_t cb = (static_cast<int64_t>(c) * total) / gridDim.x;
+            const float* src =
+                p.partials + static_cast<size_t>(c * 2 + (cb >= tb0 ? 0 : 1)) * (16 * kTileN);
+#pragma unroll
+            for (int tok = 0; tok < NTOK; ++tok)
+              if (tok < p.m) {
+                v0[tok] += __ldcg(src + tok * kTileN + lane);
+                v1[tok] += __ldcg(src + tok * kTileN + lane + 32);
+              }
+          }
+          if (lane == 0) p.counters[seg_tile] = 0;
+          do_epilogue = true;
+        }
+      }
+      if (do_epilogue) {
+        if (p.fusion == FUSE_SILU_MUL) {
+          const int col = seg_tile * 32 + lane;
+          const int n_gate = decode_row_to_n(p, seg_tile, lane);
+          const int n_up = decode_row_to_n(p, seg_tile, lane + 32);
+#pragma unroll
+          for (int tok = 0; tok < NTOK; ++tok)
+            if (tok < p.m && col < p.n_out) {
+              float gate = v0[tok], up = v1[tok];
+              if (p.bias) {
+                gate += p.bias[n_gate];
+                up += p.bias[n_up];
+              }
+              p.y[static_cast<size_t>(tok) * p.ldy + col] =
+                  __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
+            }
+        } else {
+#pragma unroll
+          for (int tok = 0; tok < NTOK; ++tok) {
+            decode_epilogue(p, seg_tile, lane, tok, v0[tok]);
+            decode_epilogue(p, seg_tile, lane + 32, tok, v1[tok]);
+          }
+        }
+      }
     }
     return;
   }
@@ -141,92 +316,12 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
     for (int tb = 0; tb < TB; ++tb)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[rt][tb][i] = 0.f;
+  int seg = 0;  // segment number modulo E
 
-  int seg_kb0 = kb0;
-  bool first_segment = true;
-  int pend_tile = -1;     // first partial segment whose arrival count is looked at at the end
-  unsigned pend_old = 0;  // (thread 0) what the arrival atomic returned
-
-  // bias, rounding and the fused post-op for one (row, token) of tile `tl`
-  auto epilogue = [&](int tl, int row, int tok, float r) {
-    const int n = decode_row_to_n(p, tl, row);
-    if (tok >= p.m || n >= p.n) return;
-    if (p.bias) r += p.bias[n];
-    r = bf16_round(r);
-    if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
-      const size_t o = static_cast<size_t>(p.row_idx[tok]) * p.ldy + n;
-      const float w = __bfloat162float(p.row_w[tok]);
-      p.y[o] = __float2bfloat16_rn(__bfloat162float(p.y[o]) + r * w);
-      return;
-    }
-    const size_t o = static_cast<size_t>(tok) * p.ldy + n;
-    if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
-      r = bf16_round(r + __bfloat162float(p.other0[o]));
-      if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __bfloat162float(p.other1[o]));
-    } else if (p.fusion == FUSE_MUL) {
-      r = bf16_round(r * __bfloat162float(p.other0[o]));
-    } else {
-      r = unary_post_op(r, p.fusion);
-    }
-    p.y[o] = __float2bfloat16_rn(r);
-  };
-
-  // thread -> (row, tokens q*4 + tid/64): finish tile `tl` from the values v[] (or, for a
-  // split tile, from the contributors' partial tiles summed in CTA order)
-  auto finish_tile = [&](int tl, bool from_partials, float (&v)[NTOK / 4]) {
-    const int row = tid & 63;
-    if (from_partials) {
-      const int64_t tb0 = static_cast<int64_t>(tl) * p.kb_per_tile;
-      const int c_first = owner_of(tb0, total, gridDim.x);
-      const int c_last = owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
-#pragma unroll
-      for (int q = 0; q < NTOK / 4; ++q) v[q] = 0.f;
-      for (int c = c_first; c <= c_last; ++c) {
-        const int64_t cb = (static_cast<int64_t>(c) * total) / gridDim.x;
-        const float* src =
-            p.partials + static_cast<size_t>(c * 2 + (cb >= tb0 ? 0 : 1)) * (16 * kTileN);
-#pragma unroll
-        for (int q = 0; q < NTOK / 4; ++q) {
-          const int tok = q * 4 + (tid >> 6);
-          if (tok < p.m) v[q] += __ldcg(src + tok * kTileN + row);
-        }
-      }
-    }
-    if (p.fusion == FUSE_SILU_MUL) {
-      // rows 0..31 of the tile are gate rows, rows 32..63 the matching up rows
-      float* fin = red;
-#pragma unroll
-      for (int q = 0; q < NTOK / 4; ++q) {
-        const int tok = q * 4 + (tid >> 6);
-        if (tok < red_tok) {
-          const int n = decode_row_to_n(p, tl, row);
-          float r = v[q];
-          if (n < p.n && p.bias) r += p.bias[n];
-          fin[tok * kRedTokStride + row] = bf16_round(r);
-        }
-      }
-      named_bar_sync(1, kConsumerThreads);
-      if (row < 32) {
-        const int col = tl * 32 + row;
-#pragma unroll
-        for (int q = 0; q < NTOK / 4; ++q) {
-          const int tok = q * 4 + (tid >> 6);
-          if (tok < p.m && col < p.n_out) {
-            const float gate = fin[tok * kRedTokStride + row];
-            const float up = fin[tok * kRedTokStride + row + 32];
-            p.y[static_cast<size_t>(tok) * p.ldy + col] = __float2bfloat16_rn(up * silu_bf16(gate));
-          }
-        }
-      }
-    } else {
-#pragma unroll
-      for (int q = 0; q < NTOK / 4; ++q) epilogue(tl, row, q * 4 + (tid >> 6), v[q]);
-    }
-  };
-
-  // end of a tile segment [seg_kb0, seg_kb1) of tile `tl`; `more` = this CTA has more work
-  auto flush = [&](int tl, int seg_kb1, bool more) {
-    // 1. this warp's partial sums -> red[warp][tok][row]
+  // end of a tile segment: hand this warp's partial sums to an epilogue warp and go on
+  auto flush = [&](bool first) {
+    // the buffer is free once the previous segment's epilogue warp has read it
+    if (!first) named_bar_sync(kBarRedFree + (seg == 0 ? E - 1 : seg - 1), kConsumerThreads + 32);
     float* my = red + warp * (red_tok * kRedTokStride);
 #pragma unroll
     for (int rt = 0; rt < 4; ++rt)
@@ -239,65 +334,18 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
           if (tok < red_tok) my[tok * kRedTokStride + row] = acc[rt][tb][i];
           acc[rt][tb][i] = 0.f;
         }
-    named_bar_sync(1, kConsumerThreads);
-    // 2. sum over the warps
-    const int row = tid & 63;
-    float v[NTOK / 4];
-#pragma unroll
-    for (int q = 0; q < NTOK / 4; ++q) {
-      const int tok = q * 4 + (tid >> 6);
-      float s = 0.f;
-      if (tok < red_tok) {
-#pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w)
-          s += red[w * (red_tok * kRedTokStride) + tok * kRedTokStride + row];
-      }
-      v[q] = s;
-    }
-    const bool whole = (seg_kb0 == 0 && seg_kb1 == p.kb_per_tile);
-    if (whole) {
-      if (p.fusion == FUSE_SILU_MUL) named_bar_sync(1, kConsumerThreads);  // red is reused
-      finish_tile(tl, false, v);
-    } else {
-      // partial: park it in the workspace, the last contributor to arrive reduces
-      const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
-      float* dst = p.partials + static_cast<size_t>(my_slot) * (16 * kTileN);
-#pragma unroll
-      for (int q = 0; q < NTOK / 4; ++q) {
-        const int tok = q * 4 + (tid >> 6);
-        if (tok < p.m) __stcg(dst + tok * kTileN + row, v[q]);
-      }
-      named_bar_sync(1, kConsumerThreads);
-      if (first_segment && more) {
-        if (tid == 0) {
-          __threadfence();
-          pend_old = atomicAdd(p.counters + tl, 1u);
-        }
-        pend_tile = tl;
-      } else {
-        if (tid == 0) {
-          const int64_t tb0 = static_cast<int64_t>(tl) * p.kb_per_tile;
-          const int c_first = owner_of(tb0, total, gridDim.x);
-          const int c_last = owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
-          __threadfence();
-          const unsigned old = atomicAdd(p.counters + tl, 1u);
-          const int last = (old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
-          if (last) p.counters[tl] = 0;
-          hdr->is_last = last;
-        }
-        named_bar_sync(1, kConsumerThreads);
-        if (hdr->is_last) {
-          __threadfence();
-          finish_tile(tl, true, v);
-        }
-      }
-    }
-    named_bar_sync(1, kConsumerThreads);  // red and is_last are free again
-    first_segment = false;
+    __threadfence_block();
+    named_bar_arrive(kBarRedFull + seg, kConsumerThreads + 32);
+    seg = (seg + 1 == E) ? 0 : seg + 1;
   };
 
-  while (b < b_end) {
-    const int nkb = stage_len();
+  StageIter it(tile0, kb00, share, p.kb_per_tile);
+  int slot = 0;
+  uint32_t phase = 0;
+  bool first_flush = true;
+  while (!it.done()) {
+    const int nkb = it.nkb();
+    const int kb0 = it.kb;
     const uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
     mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 2);
 
@@ -406,25 +454,14 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&hdr->empty[slot]);
-    const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
-    if (seg_end) flush(tile, kb0 + nkb, b + nkb < b_end);
-    advance(nkb);
-    if (seg_end) seg_kb0 = kb0;
-  }
-  if (pend_tile >= 0) {
-    if (tid == 0) {
-      const int64_t tb0 = static_cast<int64_t>(pend_tile) * p.kb_per_tile;
-      const int c_first = owner_of(tb0, total, gridDim.x);
-      const int c_last = owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
-      const int last = (pend_old == static_cast<unsigned>(c_last - c_first)) ? 1 : 0;
-      if (last) p.counters[pend_tile] = 0;
-      hdr->is_last = last;
+    if (kb0 + nkb == it.k1) {
+      flush(first_flush);
+      first_flush = false;
     }
-    named_bar_sync(1, kConsumerThreads);
-    if (hdr->is_last) {
-      __threadfence();
-      float v[NTOK / 4];
-      finish_tile(pend_tile, true, v);
+    it.next(nkb);
+    if (++slot == p.stages) {
+      slot = 0;
+      phase ^= 1;
     }
   }
 }
@@ -465,8 +502,24 @@ cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  kern<<<grid, kThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  // Programmatic dependent launch: this grid may start streaming weights while the previous
+  // kernel in the stream drains (it waits for that kernel before it touches x, y or the
+  // workspace).  After a kernel that never signals, or after a copy, this is ordinary ordering.
+  static const bool pdl = [] {
+    const char* e = getenv("WOQ_B200_PDL");
+    return !(e && atoi(e) == 0);
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block_threads(tb));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 }  // namespace woq
