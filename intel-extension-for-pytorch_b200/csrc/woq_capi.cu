@@ -75,6 +75,7 @@ struct woq_b200_ctx {
   size_t wq_tc_bytes, sz_tc_bytes;
   float* scale_f32;  // INT8: per-channel fp32 scales [n_pad]
   int is_int8;       // INT8 weights with INT8 compute
+  int plain_scales;  // INT4: every scale is normal and below 0.5, every zero point below 16
   int kc_per_tile;   // INT8: K / 128
   float* bias;       // fp32 [n] or null
   size_t wq_bytes, sz_bytes;
@@ -358,8 +359,9 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
   int h_flag = 0;
   CUDA_TRY_C(cudaMemcpyAsync(&h_flag, d_flag, sizeof(int), cudaMemcpyDeviceToHost, stream));
   CUDA_TRY_C(cudaStreamSynchronize(stream));
-  if (h_flag)
+  if (h_flag & 1)
     return cleanup(fail(WOQ_B200_ERR_INVALID_ARG, "zero points must be integers in [0, 127]"));
+  c->plain_scales = (h_flag & 2) ? 0 : 1;
 #undef CUDA_TRY_C
   c->magic = kMagic;
   *out = c;
@@ -451,11 +453,11 @@ static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t l
   p.kb_per_tile = c->kb_per_tile;
   p.kbpg_shift = c->kbpg_shift;
   p.groups = c->groups;
-  p.gps = c->kb_per_group >= 8 ? 1 : 8 / c->kb_per_group;
   p.fusion = fusion;
   p.gate_up = c->gate_up;
-  p.exact = c->desc.kernel_hint == WOQ_B200_HINT_STREAM_FAST ? 0 : 1;
-  woq::DecodeShape shape{(int)m, c->tiles, c->kb_per_tile};
+  p.exact = c->desc.kernel_hint == WOQ_B200_HINT_STREAM_FAST ? 0 : c->plain_scales ? 2 : 1;
+  p.unit = woq::decode_int4_unit((int)m, c->kb_per_group);
+  woq::DecodeShape shape{(int)m, c->tiles, c->kb_per_tile, p.unit};
   const int grid = woq::decode_int4_pick_grid(shape, c->num_sms);
   CUDA_TRY(woq::launch_decode_int4(p, grid, stream));
   woq::count_launch();

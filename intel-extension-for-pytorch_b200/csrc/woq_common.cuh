@@ -11,10 +11,10 @@ namespace woq {
 // INT4 tiled layout.
 //
 // The weight [N, K] is cut into tiles of 64 output rows x 64 k ("k-block").  A k-block of a
-// tile is 2048 bytes: 4 row-tiles of 16 rows, each 32 lanes x 16 bytes, so that lane l of a
-// warp fetches everything it needs for four m16n8k16 steps of one row-tile with a single
-// 128-bit shared-memory load.  With g = l / 4 and t = l % 4, word j (0..3) of lane l holds,
-// for rows r0 = 16*rt + g and r1 = r0 + 8 and k0 = 64*kb + 16*t + 4*j:
+// tile is 2048 bytes: 4 k-steps j, each 32 lanes x 16 bytes, so that lane l of a warp fetches
+// what it needs for one m16n8k16 step of all four 16-row row-tiles with a single 128-bit
+// shared-memory load.  With g = l / 4 and t = l % 4, word rt (0..3) of lane l in k-step j
+// holds, for rows r0 = 16*rt + g and r1 = r0 + 8 and k0 = 64*kb + 16*t + 4*j:
 //   bits  3: 0  q[r0][k0+0]     bits 19:16  q[r0][k0+1]
 //   bits  7: 4  q[r1][k0+0]     bits 23:20  q[r1][k0+1]
 //   bits 11: 8  q[r0][k0+2]     bits 27:24  q[r0][k0+3]
@@ -40,7 +40,7 @@ __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + 
 __host__ __device__ inline void int4_slot(int r, int k, int& word, int& shift) {
   const int rt = r >> 4, rr = r & 15, g = rr & 7, h = rr >> 3;
   const int t = k >> 4, kk = k & 15, j = kk >> 2, c = kk & 3;
-  word = ((rt * 32) + (g * 4 + t)) * 4 + j;
+  word = ((j * 32) + (g * 4 + t)) * 4 + rt;
   // c: 0 -> bits 3:0 (+4 if h), 1 -> bits 19:16, 2 -> bits 11:8, 3 -> bits 27:24
   shift = ((c & 1) ? 16 : 0) + ((c & 2) ? 8 : 0) + (h ? 4 : 0);
 }

@@ -1,21 +1,29 @@
 // INT4 weight-only-quantised skinny GEMM for M <= 16 tokens ("decode"): an HBM-bound stream
 // of packed weights.
 //
-// Persistent kernel, two CTAs per SM (one for 9..16 tokens).  The weight is a linear sequence
-// of k-blocks (64 rows x 64 k, 2 KB each, tile-major); CTA c owns an equal contiguous share.
-// One producer warp moves up to eight k-blocks of one tile per pipeline stage (weights, their
-// group scales and the matching slice of x) with bulk asynchronous copies that complete on
-// an mbarrier; eight consumer warps take one k-block each:
-//   * nibbles become bf16 "128 + q" A-fragments with one lop3 per register (no subtract, no
-//     multiply): the tensor core accumulates sum_k x*(128+q) per k-block in fp32, a fifth
-//     MMA with an all-ones A-fragment gives sum_k x, and the group's scale and zero point
-//     are applied once per k-block:  acc += s * (sum - (128 + zp) * sum_x);
-//   * at a tile boundary the eight warps' partial sums are added in shared memory; a CTA
-//     that saw the whole K of the tile writes y directly, otherwise the partial goes to the
-//     workspace and the last contributor to arrive sums all partials in a fixed order
-//     (results do not depend on timing) and runs the fused epilogue.  A CTA that still has
-//     tiles to stream does not wait for the arrival count: it looks at it after its last
-//     tile.
+// Persistent kernel, two CTAs per SM (one for 9..16 tokens), ten warps each.  The weight is a
+// linear sequence of k-blocks (64 rows x 64 k, 2 KB each, tile-major); CTA c owns an equal
+// contiguous share, cut at tile boundaries into "segments".
+//   * The producer warp moves 8 or 16 k-blocks of one tile per pipeline stage (weights, their
+//     group scales and the matching slice of x) with bulk asynchronous copies that complete
+//     on an mbarrier.  Under programmatic dependent launch the first pipeline fill of
+//     weights is issued before the previous kernel in the stream has finished; x is not
+//     touched until it has.
+//   * Eight consumer warps take one or two k-blocks of a stage each.  Default dequantiser:
+//     bf16((q - zp) * bf16 scale) per weight, bit for bit the reference's tile dequantiser,
+//     as bf16x2 A-fragments of mma.m16n8k16 (x is the B operand, fp32 accumulation).
+//     Nibbles at bits 0..3 of a half-word are OR-ed into the mantissa of 128.0 (one lop3);
+//     nibbles at bits 4..7 are used in place: masked, the half-word read as bf16 is
+//     16 q * 2^-133 exactly, and the scale for those rows is pre-multiplied by 2^129.
+//     Fast variant (hint STREAM_FAST): no subtract or multiply per weight; the tensor core
+//     accumulates sum_k x * (128 + q) per k-block, an MMA with an all-ones A-fragment gives
+//     sum_k x, and scale and zero point are applied to the sums per k-block.
+//   * At the end of a segment the consumers drop their partial sums in shared memory and go
+//     on; the epilogue warp adds them.  A CTA that saw the whole K of the tile writes y
+//     (bias, rounding, fused post-op); otherwise the partial goes to the workspace and the
+//     last contributor to arrive sums all partials in CTA order (results do not depend on
+//     timing) and runs the epilogue.  Nobody waits for an arrival count.  The CTA's last
+//     segment is taken by the producer warp, idle by then.
 // The memory system needs about 2.5 us x 44 GB/s = 110+ KB in flight per SM to stay busy,
 // which sets the number of pipeline stages.
 #include <cstdlib>
@@ -28,17 +36,21 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kProducerWarp = kConsumerWarps, kFirstEpilogueWarp = kConsumerWarps + 1;
-// Epilogue warps take tile segments round-robin, so the global-memory round trips of one
-// segment's partial-tile protocol overlap the next segment's.
-__host__ __device__ constexpr int epilogue_warps(int tb) { return tb == 1 ? 3 : 4; }
-__host__ __device__ constexpr int block_threads(int tb) {
-  return (kConsumerWarps + 1 + epilogue_warps(tb)) * 32;
-}
-// named barriers: 1 + e "segment for epilogue warp e is in shared memory", 5 + e "... is drained"
-constexpr int kBarRedFull = 1, kBarRedFree = 5;
-constexpr int kStageKBlocks = kConsumerWarps;                 // k-blocks per stage
-constexpr int kXRowBytes = kStageKBlocks * kBlockK * 2 + 16;  // +16: bank spread between tokens
+constexpr int kProducerWarp = kConsumerWarps, kEpilogueWarp = kConsumerWarps + 1;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;
+// named barriers: "a segment's partial sums are in shared memory" for the epilogue warp and,
+// for a CTA's last segment, for the producer warp; "the buffer has been read"
+constexpr int kBarRedFull = 1, kBarRedFullLast = 2, kBarRedFree = 3;
+// k-blocks per pipeline stage: each consumer warp takes KPW (1 or 2) adjacent k-blocks
+__host__ __device__ constexpr int stage_kblocks(int kpw) { return kConsumerWarps * kpw; }
+// bytes of one token's x slice in a stage; +16: bank spread between tokens
+__host__ __device__ constexpr int x_row_bytes(int kpw) { return stage_kblocks(kpw) * kBlockK * 2 + 16; }
+// how the weights become bf16
+enum DequantMode {
+  kScaleAfterSum = 0,  // approximate: scale and zero point applied to fp32 sums per k-block
+  kExactShift = 1,     // bf16((q - zp) * s) per weight, every nibble shifted down to bit 0
+  kExactInPlace = 2    // the same values; nibbles at bits 4..7 are used where they are
+};
 constexpr int kRedTokStride = 68;                             // floats; conflict-free scatter
 constexpr int kHeaderBytes = 1024;
 constexpr int kMaxStages = 8;
@@ -49,9 +61,10 @@ struct SmemHeader {
   int abort_flag;
 };
 
-__device__ __forceinline__ int owner_of(int64_t b, int64_t total, int64_t ctas) {
-  // CTA c owns k-blocks [c*total/ctas, (c+1)*total/ctas)
-  return static_cast<int>(((b + 1) * ctas - 1) / total);
+// The k-block sequence is dealt out in units of `unit` k-blocks: CTA c owns units
+// [c*units/ctas, (c+1)*units/ctas).
+__device__ __forceinline__ int owner_of(int64_t b, int unit, int64_t units, int64_t ctas) {
+  return static_cast<int>(((b / unit + 1) * ctas - 1) / units);
 }
 
 // bias, rounding and the fused post-op for one (row, token) of tile `tl`
@@ -82,11 +95,11 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tl, i
 // boundaries ("segments") and then into runs of up to kStageKBlocks k-blocks.  Producer and
 // consumers step through the same sequence.
 struct StageIter {
-  int tile, kb, k1, left, kbpt;  // current tile, next k-block, segment end, k-blocks left
-  __device__ StageIter(int tile0, int kb0, int left0, int kbpt0)
-      : tile(tile0), kb(kb0), k1(min(kbpt0, kb0 + left0)), left(left0), kbpt(kbpt0) {}
+  int tile, kb, k1, left, kbpt, skb;  // tile, next k-block, segment end, k-blocks left, ...
+  __device__ StageIter(int tile0, int kb0, int left0, int kbpt0, int skb0)
+      : tile(tile0), kb(kb0), k1(min(kbpt0, kb0 + left0)), left(left0), kbpt(kbpt0), skb(skb0) {}
   __device__ bool done() const { return left <= 0; }
-  __device__ int nkb() const { return min(kStageKBlocks, k1 - kb); }
+  __device__ int nkb() const { return min(skb, k1 - kb); }
   __device__ void next(int n) {
     kb += n;
     left -= n;
@@ -100,13 +113,14 @@ struct StageIter {
   }
 };
 
-template <int TB, bool EXACT>
-__global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
+template <int TB, int MODE, int KPW>
+__global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
     woq_int4_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
   constexpr int NTOK = 8 * TB;
-  constexpr int E = epilogue_warps(TB);
+  constexpr int kStageKBlocks = stage_kblocks(KPW);
+  constexpr int kXRowBytes = x_row_bytes(KPW);
   const int sz_stage_bytes = (p.gps + 1) * 256;
   const int stage_bytes = kStageKBlocks * kBlockBytes + sz_stage_bytes + p.x_rows * kXRowBytes;
   const int red_tok = p.red_tok;  // tokens kept in the cross-warp reduction buffer
@@ -114,9 +128,9 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
   float* red = reinterpret_cast<float*>(stages + static_cast<size_t>(p.stages) * stage_bytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t total = static_cast<int64_t>(p.tiles) * p.kb_per_tile;
-  const int64_t b_begin = (static_cast<int64_t>(blockIdx.x) * total) / gridDim.x;
-  const int64_t b_end = (static_cast<int64_t>(blockIdx.x + 1) * total) / gridDim.x;
+  const int64_t units = static_cast<int64_t>(p.tiles) * p.kb_per_tile / p.unit;
+  const int64_t b_begin = (static_cast<int64_t>(blockIdx.x) * units) / gridDim.x * p.unit;
+  const int64_t b_end = (static_cast<int64_t>(blockIdx.x + 1) * units) / gridDim.x * p.unit;
   const int tile0 = static_cast<int>(b_begin / p.kb_per_tile);
   const int kb00 = static_cast<int>(b_begin - static_cast<int64_t>(tile0) * p.kb_per_tile);
   const int share = static_cast<int>(b_end - b_begin);
@@ -134,6 +148,112 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
   // stream while this grid is still running.
   grid_launch_dependents();
   volatile int* abort_flag = &hdr->abort_flag;
+
+  // Segments of this CTA's share: [kb00, ...) of tile0, then whole tiles, the last maybe short.
+  const int seg0_len = min(share, p.kb_per_tile - kb00);
+  const int nseg = share <= 0 ? 0 : 1 + (share - seg0_len + p.kb_per_tile - 1) / p.kb_per_tile;
+
+  // ---- end-of-segment work, done by the epilogue warp; the CTA's last segment goes to the
+  // producer warp (idle by then), so that the global-memory round trips of a short CTA's two
+  // partial tiles overlap.  The warp takes the eight consumer warps' partial sums out of
+  // shared memory, so the consumers go straight on to the next tile; then it either runs the
+  // fused epilogue or parks a partial tile and, if this CTA is the last contributor to
+  // arrive, reduces the tile in a fixed order.
+  auto run_epilogue = [&](int tl, const float* a0, const float* a1) {
+    if (p.fusion == FUSE_SILU_MUL) {
+      // gate/up layout: row lane is a gate row, row lane + 32 its up row
+      const int col = tl * 32 + lane;
+      const int n_gate = decode_row_to_n(p, tl, lane);
+      const int n_up = decode_row_to_n(p, tl, lane + 32);
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < p.m && col < p.n_out) {
+          float gate = a0[tok], up = a1[tok];
+          if (p.bias) {
+            gate += p.bias[n_gate];
+            up += p.bias[n_up];
+          }
+          p.y[static_cast<size_t>(tok) * p.ldy + col] =
+              __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
+        }
+    } else {
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok) {
+        decode_epilogue(p, tl, lane, tok, a0[tok]);
+        decode_epilogue(p, tl, lane + 32, tok, a1[tok]);
+      }
+    }
+  };
+  // `old` (lane 0) is what the arrival counter of tile tl held before this CTA counted in:
+  // the last contributor adds all partials in CTA order and runs the epilogue
+  auto resolve = [&](int tl, unsigned old, float* a0, float* a1) {
+    old = __shfl_sync(0xffffffffu, old, 0);
+    const int64_t tb0 = static_cast<int64_t>(tl) * p.kb_per_tile;
+    const int c_first = owner_of(tb0, p.unit, units, gridDim.x);
+    const int c_last = owner_of(tb0 + p.kb_per_tile - 1, p.unit, units, gridDim.x);
+    if (old != static_cast<unsigned>(c_last - c_first)) return;
+    __threadfence();
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok) a0[tok] = a1[tok] = 0.f;
+    for (int c = c_first; c <= c_last; ++c) {
+      const int64_t cb = (static_cast<int64_t>(c) * units) / gridDim.x * p.unit;
+      const float* src =
+          p.partials + static_cast<size_t>(c * 2 + (cb >= tb0 ? 0 : 1)) * (16 * kTileN);
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < p.m) {
+          a0[tok] += __ldcg(src + tok * kTileN + lane);
+          a1[tok] += __ldcg(src + tok * kTileN + lane + 32);
+        }
+    }
+    if (lane == 0) p.counters[tl] = 0;
+    run_epilogue(tl, a0, a1);
+  };
+  // v0/v1: lane -> rows lane and lane + 32 of the tile, all tokens
+  auto take_segment = [&](int bar_full, bool signal_free, int seg_tile, bool whole, bool first_segment,
+                          float* v0, float* v1, int& pend_tile, unsigned& pend_old) {
+    named_bar_sync(bar_full, kConsumerThreads + 32);
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok) {
+      float s0 = 0.f, s1 = 0.f;
+      if (tok < red_tok) {
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          const float* r = red + w * (red_tok * kRedTokStride) + tok * kRedTokStride;
+          s0 += r[lane];
+          s1 += r[lane + 32];
+        }
+      }
+      v0[tok] = s0;
+      v1[tok] = s1;
+    }
+    if (signal_free) {
+      __threadfence_block();
+      named_bar_arrive(kBarRedFree, kConsumerThreads + 32);
+    }
+    if (whole) {
+      run_epilogue(seg_tile, v0, v1);
+      return;
+    }
+    // Park the partial tile and count this CTA in.  Whether it was the last contributor is
+    // looked at after the next partial segment (or at the end): the atomic's round trip then
+    // overlaps other work instead of stalling this warp.
+    const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
+    float* dst = p.partials + static_cast<size_t>(my_slot) * (16 * kTileN);
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok)
+      if (tok < p.m) {
+        __stcg(dst + tok * kTileN + lane, v0[tok]);
+        __stcg(dst + tok * kTileN + lane + 32, v1[tok]);
+      }
+    __threadfence();
+    __syncwarp();
+    unsigned old = 0;
+    if (lane == 0) old = atomicAdd(p.counters + seg_tile, 1u);
+    if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
+    pend_tile = seg_tile;
+    pend_old = old;
+  };
 
   if (warp == kProducerWarp) {
     // ------------------------------ producer warp ------------------------------------
@@ -164,7 +284,7 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
                  it.nkb() * (kBlockK * 2), &hdr->full[slot]);
       }
     };
-    StageIter it(tile0, kb00, share, p.kb_per_tile);
+    StageIter it(tile0, kb00, share, p.kb_per_tile, kStageKBlocks);
     {
       StageIter fill = it;
       if (lane == 0)
@@ -181,7 +301,7 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
     }
     int slot = 0;
     uint32_t phase = 1;  // the slots are on their second use from here on
-    while (!it.done()) {
+    while (!it.done() && !(p.debug & 16)) {
       if (lane == 0) {
         mbar_wait(&hdr->empty[slot], phase ^ 1, abort_flag, p.status, 1);
         if (p.debug & 8)
@@ -197,113 +317,31 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
         phase ^= 1;
       }
     }
+    if (nseg > 0) {
+      // the CTA's last segment
+      float v0[NTOK], v1[NTOK];
+      int pend_tile = -1;
+      unsigned pend_old = 0;
+      const int k0 = nseg == 1 ? kb00 : 0;
+      const int len = nseg == 1 ? share : share - seg0_len - (nseg - 2) * p.kb_per_tile;
+      take_segment(kBarRedFullLast, false, tile0 + nseg - 1, k0 == 0 && len == p.kb_per_tile,
+                   nseg == 1, v0, v1, pend_tile, pend_old);
+      if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
+    }
     return;
   }
 
-  if (warp >= kFirstEpilogueWarp) {
-    // ------------------------------ epilogue warps -------------------------------------
-    // Take the eight consumer warps' partial sums of a finished tile segment out of shared
-    // memory, so the consumers go straight on to the next tile; then either run the fused
-    // epilogue or park a partial tile and, if this CTA is the last contributor to arrive,
-    // reduce the tile in a fixed order.  Segments go round-robin over the epilogue warps.
-    const int me = warp - kFirstEpilogueWarp;
-    int turn = 0;
-    int tl = tile0, k0 = kb00, left = share;
-    bool first_segment = true;
-    bool waited = false;
-    for (; left > 0; first_segment = false, turn = (turn + 1 == E) ? 0 : turn + 1) {
-      const int k1 = min(p.kb_per_tile, k0 + left);
-      const bool whole = (k0 == 0 && k1 == p.kb_per_tile);
-      const int seg_tile = tl;
-      left -= k1 - k0;
-      k0 = 0;
-      ++tl;
-      if (turn != me) continue;
-      named_bar_sync(kBarRedFull + me, kConsumerThreads + 32);
-      // lane -> rows lane and lane + 32 (in the gate/up layout: a gate row and its up row)
-      float v0[NTOK], v1[NTOK];
-#pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok) {
-        float s0 = 0.f, s1 = 0.f;
-        if (tok < red_tok) {
-#pragma unroll
-          for (int w = 0; w < kConsumerWarps; ++w) {
-            const float* r = red + w * (red_tok * kRedTokStride) + tok * kRedTokStride;
-            s0 += r[lane];
-            s1 += r[lane + 32];
-          }
-        }
-        v0[tok] = s0;
-        v1[tok] = s1;
-      }
-      __threadfence_block();
-      named_bar_arrive(kBarRedFree + me, kConsumerThreads + 32);
-      if (!waited) {
-        grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
-        waited = true;
-      }
-      bool do_epilogue = whole;
-      if (!whole) {
-        const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
-        float* dst = p.partials + static_cast<size_t>(my_slot) * (16 * kTileN);
-#pragma unroll
-        for (int tok = 0; tok < NTOK; ++tok)
-          if (tok < p.m) {
-            __stcg(dst + tok * kTileN + lane, v0[tok]);
-            __stcg(dst + tok * kTileN + lane + 32, v1[tok]);
-          }
-        __threadfence();
-        __syncwarp();
-        const int64_t tb0 = static_cast<int64_t>(seg_tile) * p.kb_per_tile;
-        const int c_first = owner_of(tb0, total, gridDim.x);
-        const int c_last = owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
-        unsigned old = 0;
-        if (lane == 0) old = atomicAdd(p.counters + seg_tile, 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == static_cast<unsigned>(c_last - c_first)) {
-          __threadfence();
-#pragma unroll
-          for (int tok = 0; tok < NTOK; ++tok) v0[tok] = v1[tok] = 0.f;
-          for (int c = c_first; c <= c_last; ++c) {
-            const int64_t cb = (static_cast<int64_t>(c) * total) / gridDim.x;
-            const float* src =
-                p.partials + static_cast<size_t>(c * 2 + (cb >= tb0 ? 0 : 1)) * (16 * kTileN);
-#pragma unroll
-            for (int tok = 0; tok < NTOK; ++tok)
-              if (tok < p.m) {
-                v0[tok] += __ldcg(src + tok * kTileN + lane);
-                v1[tok] += __ldcg(src + tok * kTileN + lane + 32);
-              }
-          }
-          if (lane == 0) p.counters[seg_tile] = 0;
-          do_epilogue = true;
-        }
-      }
-      if (do_epilogue) {
-        if (p.fusion == FUSE_SILU_MUL) {
-          const int col = seg_tile * 32 + lane;
-          const int n_gate = decode_row_to_n(p, seg_tile, lane);
-          const int n_up = decode_row_to_n(p, seg_tile, lane + 32);
-#pragma unroll
-          for (int tok = 0; tok < NTOK; ++tok)
-            if (tok < p.m && col < p.n_out) {
-              float gate = v0[tok], up = v1[tok];
-              if (p.bias) {
-                gate += p.bias[n_gate];
-                up += p.bias[n_up];
-              }
-              p.y[static_cast<size_t>(tok) * p.ldy + col] =
-                  __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
-            }
-        } else {
-#pragma unroll
-          for (int tok = 0; tok < NTOK; ++tok) {
-            decode_epilogue(p, seg_tile, lane, tok, v0[tok]);
-            decode_epilogue(p, seg_tile, lane + 32, tok, v1[tok]);
-          }
-        }
-      }
+  if (warp == kEpilogueWarp) {
+    // ------------------------------ epilogue warp --------------------------------------
+    float v0[NTOK], v1[NTOK];
+    int pend_tile = -1;
+    unsigned pend_old = 0;
+    grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
+    for (int sg = 0; sg + 1 < nseg; ++sg) {
+      take_segment(kBarRedFull, true, tile0 + sg, sg > 0 || kb00 == 0, sg == 0, v0, v1, pend_tile,
+                   pend_old);
     }
+    if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
     return;
   }
 
@@ -316,12 +354,12 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
     for (int tb = 0; tb < TB; ++tb)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[rt][tb][i] = 0.f;
-  int seg = 0;  // segment number modulo E
+  int seg = 0;  // segments flushed so far
 
-  // end of a tile segment: hand this warp's partial sums to an epilogue warp and go on
-  auto flush = [&](bool first) {
-    // the buffer is free once the previous segment's epilogue warp has read it
-    if (!first) named_bar_sync(kBarRedFree + (seg == 0 ? E - 1 : seg - 1), kConsumerThreads + 32);
+  // end of a tile segment: hand this warp's partial sums over and go on
+  auto flush = [&]() {
+    // the buffer is free once the epilogue warp has read the previous segment
+    if (seg > 0) named_bar_sync(kBarRedFree, kConsumerThreads + 32);
     float* my = red + warp * (red_tok * kRedTokStride);
 #pragma unroll
     for (int rt = 0; rt < 4; ++rt)
@@ -335,70 +373,92 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
           acc[rt][tb][i] = 0.f;
         }
     __threadfence_block();
-    named_bar_arrive(kBarRedFull + seg, kConsumerThreads + 32);
-    seg = (seg + 1 == E) ? 0 : seg + 1;
+    ++seg;
+    named_bar_arrive(seg == nseg ? kBarRedFullLast : kBarRedFull, kConsumerThreads + 32);
   };
 
-  StageIter it(tile0, kb00, share, p.kb_per_tile);
+  StageIter it(tile0, kb00, share, p.kb_per_tile, kStageKBlocks);
   int slot = 0;
   uint32_t phase = 0;
-  bool first_flush = true;
+  // per-row constants of the current group, rows g, g+8 of each row-tile
+  uint32_t cz[8], cs[8];
+  // per-lane offsets inside a stage.  A lane whose token does not exist reads the last real
+  // token's x instead: its MMA columns are never written out, and columns do not mix.
+  const int w_off = lane * 16;
+  const int s_off = kStageKBlocks * kBlockBytes + g * 32;
+  int x_off[TB];
+#pragma unroll
+  for (int tb = 0; tb < TB; ++tb)
+    x_off[tb] = kStageKBlocks * kBlockBytes + sz_stage_bytes + min(tb * 8 + g, p.m - 1) * kXRowBytes + t * 32;
   while (!it.done()) {
     const int nkb = it.nkb();
     const int kb0 = it.kb;
     const uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
-    mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 2);
+    if (!(p.debug & 16)) mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 2);
 
-    if (warp < nkb && !(p.debug & 1)) {
-      const int kb = kb0 + warp;
-      // packed weights: four row-tiles x four k-steps
-      const uint4* wp = reinterpret_cast<const uint4*>(st + warp * kBlockBytes) + lane;
+    // one k-block (64 rows x 64 k) of the stage: index idx, constants reloaded if `prep`
+    auto do_kblock = [&](const int idx, const bool prep) {
+      const int kb = kb0 + idx;
+      // packed weights: one 128-bit load per k-step covers the four row-tiles
+      const uint4* wp = reinterpret_cast<const uint4*>(st + idx * kBlockBytes + w_off);
       uint4 wv[4];
 #pragma unroll
-      for (int rt = 0; rt < 4; ++rt) wv[rt] = wp[rt * 32];
+      for (int j = 0; j < 4; ++j) wv[j] = wp[j * 32];
       // activations: this lane's 16 k of token g (+8)
       uint32_t xb[TB][8];
-      const uint8_t* xs = st + kStageKBlocks * kBlockBytes + sz_stage_bytes;
 #pragma unroll
       for (int tb = 0; tb < TB; ++tb) {
-        const int tok = tb * 8 + g;
-        if (tok < p.m) {
-          const uint4* xp =
-              reinterpret_cast<const uint4*>(xs + tok * kXRowBytes + warp * (kBlockK * 2) + t * 32);
-          const uint4 a = xp[0], c = xp[1];
-          xb[tb][0] = a.x; xb[tb][1] = a.y; xb[tb][2] = a.z; xb[tb][3] = a.w;
-          xb[tb][4] = c.x; xb[tb][5] = c.y; xb[tb][6] = c.z; xb[tb][7] = c.w;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) xb[tb][i] = 0u;
-        }
+        const uint4* xp = reinterpret_cast<const uint4*>(st + x_off[tb] + idx * (kBlockK * 2));
+        const uint4 a = xp[0], c = xp[1];
+        xb[tb][0] = a.x; xb[tb][1] = a.y; xb[tb][2] = a.z; xb[tb][3] = a.w;
+        xb[tb][4] = c.x; xb[tb][5] = c.y; xb[tb][6] = c.z; xb[tb][7] = c.w;
       }
-      // scales of this k-block's group for rows g, g+8 of each row-tile
-      const int gl = (kb >> p.kbpg_shift) - (kb0 >> p.kbpg_shift);
-      const uint4* sp =
-          reinterpret_cast<const uint4*>(st + kStageKBlocks * kBlockBytes + gl * 256 + g * 32);
-      const uint4 s_lo = sp[0], s_hi = sp[1];
-      const uint32_t szw[8] = {s_lo.x, s_lo.y, s_lo.z, s_lo.w, s_hi.x, s_hi.y, s_hi.z, s_hi.w};
-
-      if constexpr (EXACT) {
-        // bf16((q - zp) * bf16 scale) per weight, exactly the reference's tile dequantiser;
-        // the MMAs accumulate straight into the running sums
-        uint32_t zz[8], ss[8];
+      // {bf16 scale, bf16 128 + zp} of this k-block's group for rows g, g+8 of each row-tile
+      if (prep) {
+        const int gl = (kb >> p.kbpg_shift) - (kb0 >> p.kbpg_shift);
+        const uint4* sp = reinterpret_cast<const uint4*>(st + s_off + gl * 256);
+        const uint4 s_lo = sp[0], s_hi = sp[1];
+        const uint32_t szw[8] = {s_lo.x, s_lo.y, s_lo.z, s_lo.w, s_hi.x, s_hi.y, s_hi.z, s_hi.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          zz[i] = __byte_perm(szw[i], 0, 0x1010);
-          ss[i] = __byte_perm(szw[i], 0, 0x3232);
+          if constexpr (MODE == kScaleAfterSum) {
+            cs[i] = szw[i] & 0xffff0000u;  // scale as fp32 bits
+            cz[i] = szw[i] << 16;          // 128 + zp as fp32 bits
+          } else if (MODE == kExactInPlace && (i & 1)) {
+            // row g+8 takes its nibbles from bits 4..7 / 20..23 without a shift: read as bf16
+            // the masked half-word is 16 q * 2^-133 exactly (the encoding is linear below
+            // 2^-125), so subtract 16 zp * 2^-133 and multiply by scale * 2^129
+            cz[i] = (szw[i] & 0xfu) * 0x00100010u;
+            cs[i] = __byte_perm(szw[i], 0, 0x3232) + 0x40804080u;
+          } else {
+            cz[i] = __byte_perm(szw[i], 0, 0x1010);
+            cs[i] = __byte_perm(szw[i], 0, 0x3232);
+          }
         }
+      }
+
+      if constexpr (MODE != kScaleAfterSum) {
+        // bf16((q - zp) * bf16 scale) per weight, exactly the reference's tile dequantiser;
+        // the MMAs accumulate straight into the running sums
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
 #pragma unroll
           for (int rt = 0; rt < 4; ++rt) {
-            const uint32_t w = (j == 0) ? wv[rt].x : (j == 1) ? wv[rt].y : (j == 2) ? wv[rt].z : wv[rt].w;
+            const uint32_t w = (rt == 0) ? wv[j].x : (rt == 1) ? wv[j].y : (rt == 2) ? wv[j].z : wv[j].w;
+            const uint32_t z0 = cz[rt * 2], z1 = cz[rt * 2 + 1], s0 = cs[rt * 2], s1 = cs[rt * 2 + 1];
             uint32_t a[4];
-            a[0] = bf16x2_mul(bf16x2_sub(lop3_and_or(w, 0x000f000fu, kBf16Magic), zz[rt * 2]), ss[rt * 2]);
-            a[1] = bf16x2_mul(bf16x2_sub(lop3_and_or(w >> 4, 0x000f000fu, kBf16Magic), zz[rt * 2 + 1]), ss[rt * 2 + 1]);
-            a[2] = bf16x2_mul(bf16x2_sub(lop3_and_or(w >> 8, 0x000f000fu, kBf16Magic), zz[rt * 2]), ss[rt * 2]);
-            a[3] = bf16x2_mul(bf16x2_sub(lop3_and_or(w >> 12, 0x000f000fu, kBf16Magic), zz[rt * 2 + 1]), ss[rt * 2 + 1]);
+            if constexpr (MODE == kExactInPlace) {
+              const uint32_t u = w >> 8;
+              a[0] = bf16x2_mul(bf16x2_sub(lop3_and_or(w, 0x000f000fu, kBf16Magic), z0), s0);
+              a[1] = bf16x2_mul(bf16x2_sub(w & 0x00f000f0u, z1), s1);
+              a[2] = bf16x2_mul(bf16x2_sub(lop3_and_or(u, 0x000f000fu, kBf16Magic), z0), s0);
+              a[3] = bf16x2_mul(bf16x2_sub(u & 0x00f000f0u, z1), s1);
+            } else {
+              a[0] = bf16x2_mul(bf16x2_sub(lop3_and_or(w, 0x000f000fu, kBf16Magic), z0), s0);
+              a[1] = bf16x2_mul(bf16x2_sub(lop3_and_or(w >> 4, 0x000f000fu, kBf16Magic), z1), s1);
+              a[2] = bf16x2_mul(bf16x2_sub(lop3_and_or(w >> 8, 0x000f000fu, kBf16Magic), z0), s0);
+              a[3] = bf16x2_mul(bf16x2_sub(lop3_and_or(w >> 12, 0x000f000fu, kBf16Magic), z1), s1);
+            }
 #pragma unroll
             for (int tb = 0; tb < TB; ++tb)
               mma_bf16_16816(acc[rt][tb], a, xb[tb][2 * j], xb[tb][2 * j + 1]);
@@ -424,7 +484,7 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
             mma_bf16_16816(sx[tb], ones, xb[tb][2 * j], xb[tb][2 * j + 1]);
 #pragma unroll
           for (int rt = 0; rt < 4; ++rt) {
-            const uint32_t w = (j == 0) ? wv[rt].x : (j == 1) ? wv[rt].y : (j == 2) ? wv[rt].z : wv[rt].w;
+            const uint32_t w = (rt == 0) ? wv[j].x : (rt == 1) ? wv[j].y : (rt == 2) ? wv[j].z : wv[j].w;
             uint32_t a[4];
             a[0] = lop3_and_or(w, 0x000f000fu, kBf16Magic);
             a[1] = lop3_and_or(w >> 4, 0x000f000fu, kBf16Magic);
@@ -439,9 +499,8 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
         for (int rt = 0; rt < 4; ++rt)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint32_t word = szw[rt * 2 + h];
-            const float s = __uint_as_float(word & 0xffff0000u);
-            const float nz = -__uint_as_float(word << 16);
+            const float s = __uint_as_float(cs[rt * 2 + h]);
+            const float nz = -__uint_as_float(cz[rt * 2 + h]);
 #pragma unroll
             for (int tb = 0; tb < TB; ++tb)
 #pragma unroll
@@ -451,13 +510,21 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
               }
           }
       }
+    };
+    const int nkb_do = (p.debug & 1) ? 0 : nkb;
+    if (nkb_do == kStageKBlocks) {
+      // full stage: straight-line code, the second k-block's loads overlap the first's math
+      // (a warp's two k-blocks share their group unless a group is a single k-block)
+#pragma unroll
+      for (int kk = 0; kk < KPW; ++kk) do_kblock(KPW * warp + kk, kk == 0 || p.kbpg_shift == 0);
+    } else {
+#pragma unroll 1
+      for (int kk = 0; kk < KPW; ++kk)
+        if (KPW * warp + kk < nkb_do) do_kblock(KPW * warp + kk, true);
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&hdr->empty[slot]);
-    if (kb0 + nkb == it.k1) {
-      flush(first_flush);
-      first_flush = false;
-    }
+    if (lane == 0 && !(p.debug & 16)) mbar_arrive(&hdr->empty[slot]);
+    if (kb0 + nkb == it.k1) flush();
     it.next(nkb);
     if (++slot == p.stages) {
       slot = 0;
@@ -471,7 +538,7 @@ __global__ void __launch_bounds__(block_threads(TB), TB == 1 ? 2 : 1)
 size_t decode_int4_partial_bytes(int grid) { return static_cast<size_t>(grid) * 2 * 16 * kTileN * 4; }
 
 int decode_int4_pick_grid(const DecodeShape& s, int num_sms) {
-  const int64_t total = static_cast<int64_t>(s.tiles) * s.kb_per_tile;
+  const int64_t total = static_cast<int64_t>(s.tiles) * s.kb_per_tile / s.unit;
   int per_sm = s.m <= 8 ? 2 : 1;
   if (const char* e = getenv("WOQ_B200_GRID_PER_SM")) per_sm = atoi(e) > 1 && s.m <= 8 ? 2 : 1;
   int64_t grid = static_cast<int64_t>(num_sms) * per_sm;
@@ -479,26 +546,55 @@ int decode_int4_pick_grid(const DecodeShape& s, int num_sms) {
   return static_cast<int>(grid < 1 ? 1 : grid);
 }
 
+namespace {
+
+int env_int(const char* name, int fallback) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : fallback;
+}
+
+// consumer warps take two adjacent k-blocks per stage while x is small enough to leave room
+// for three 32 KB stages
+int pick_kpw(int m) { return env_int("WOQ_B200_KPW", m <= 4 ? 2 : 1) == 2 && m <= 8 ? 2 : 1; }
+
+template <int TB, int KPW>
+void (*pick_kernel(int mode))(const DecodeParams) {
+  switch (mode) {
+    case kScaleAfterSum: return woq_int4_decode_kernel<TB, kScaleAfterSum, KPW>;
+    case kExactShift: return woq_int4_decode_kernel<TB, kExactShift, KPW>;
+    default: return woq_int4_decode_kernel<TB, kExactInPlace, KPW>;
+  }
+}
+
+}  // namespace
+
+int decode_int4_unit(int m, int kb_per_group) {
+  // shares are dealt in pairs of k-blocks when a warp takes two, so that a pair never
+  // straddles two groups
+  return pick_kpw(m) == 2 && kb_per_group % 2 == 0 ? 2 : 1;
+}
+
 cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
   const int tb = p.m <= 8 ? 1 : 2;
+  const int kpw = pick_kpw(p.m);
   p.x_rows = p.m;
   p.red_tok = (p.m + 1) & ~1;
-  const int stage_bytes = kStageKBlocks * kBlockBytes + (p.gps + 1) * 256 + p.x_rows * kXRowBytes;
+  const int skb = stage_kblocks(kpw);
+  p.gps = (skb >> p.kbpg_shift) + 1;  // groups a stage can touch
+  const int stage_bytes = skb * kBlockBytes + (p.gps + 1) * 256 + p.x_rows * x_row_bytes(kpw);
   const int red_bytes = kConsumerWarps * p.red_tok * kRedTokStride * 4;
   const int budget = (tb == 1 ? 112 : 224) * 1024;
   int stages = (budget - kHeaderBytes - red_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (const char* e = getenv("WOQ_B200_STAGES")) {
-    const int want = atoi(e);
-    if (want >= 2 && want <= stages) stages = want;
-  }
-  if (const char* e = getenv("WOQ_B200_DEBUG")) p.debug = atoi(e);
+  const int want = env_int("WOQ_B200_STAGES", 0);
+  if (want >= 2 && want <= stages) stages = want;
+  p.debug = env_int("WOQ_B200_DEBUG", p.debug);
   if (stages < 2) return cudaErrorInvalidConfiguration;
   p.stages = stages;
   const size_t smem = kHeaderBytes + static_cast<size_t>(stages) * stage_bytes + red_bytes;
+  const int mode = env_int("WOQ_B200_DEQUANT_MODE", p.exact);
   void (*kern)(const DecodeParams) =
-      tb == 1 ? (p.exact ? woq_int4_decode_kernel<1, true> : woq_int4_decode_kernel<1, false>)
-              : (p.exact ? woq_int4_decode_kernel<2, true> : woq_int4_decode_kernel<2, false>);
+      tb == 2 ? pick_kernel<2, 1>(mode) : kpw == 2 ? pick_kernel<1, 2>(mode) : pick_kernel<1, 1>(mode);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
@@ -511,7 +607,7 @@ cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
   }();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(block_threads(tb));
+  cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -24,13 +24,16 @@ struct DecodeParams {
   int m, n, n_out, k;
   int tiles, kb_per_tile, kbpg_shift, groups, gps;  // gps = groups a full stage can touch
   int fusion, gate_up, stages;
-  int exact;            // 1: per-weight bf16 rounding (tile dequantiser); 0: scale after the sum
+  int exact;  // 0: scale after the sum; 1, 2: per-weight bf16 rounding (2: shift-free high nibbles)
+  int unit;   // CTA shares are multiples of this many k-blocks
   int x_rows, red_tok;  // shared-memory rows for x per stage / tokens in the reduction buffer
-  int debug;  // experiment switches: 1 skip math, 2 skip x copies, 4 skip scale copies
+  // experiment switches (timing only, results are wrong): 1 skip math, 2 skip x copies, 4 skip
+  // scale copies, 8 copy only the first pipeline fill, 16 consumers never wait
+  int debug;
 };
 
 struct DecodeShape {
-  int m, tiles, kb_per_tile;
+  int m, tiles, kb_per_tile, unit;
 };
 
 __device__ __forceinline__ int decode_row_to_n(const DecodeParams& p, int tile, int row) {
@@ -39,6 +42,7 @@ __device__ __forceinline__ int decode_row_to_n(const DecodeParams& p, int tile, 
 }
 
 int decode_int4_pick_grid(const DecodeShape& s, int num_sms);
+int decode_int4_unit(int m, int kb_per_group);
 size_t decode_int4_partial_bytes(int grid);
 cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream);
 
@@ -126,7 +130,7 @@ struct PackScaleArgs {
   const void* scales;  // [n][groups] (or transposed [groups][n])
   const void* zps;     // same shape or null
   uint32_t* sz;        // [tiles][groups][64]
-  int* bad_zp;         // set to 1 if a zero point is not an integer in 0..127
+  int* bad_zp;         // bit 0: a zero point is not an integer in 0..127; bit 1: see pack_scales_kernel
   int n, tiles, groups, gate_up;
   int transposed;     // scales are [groups][n]
   int zp_transposed;  // zero points are [groups][n]

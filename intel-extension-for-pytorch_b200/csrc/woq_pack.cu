@@ -20,7 +20,7 @@ __global__ void pack_int4_kernel(PackInt4Args a) {
   const int64_t total_words = static_cast<int64_t>(a.tiles) * a.kb_per_tile * 512;
   const int64_t wi = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (wi >= total_words) return;
-  const int j = wi & 3, lane = (wi >> 2) & 31, rt = (wi >> 7) & 3;
+  const int rt = wi & 3, lane = (wi >> 2) & 31, j = (wi >> 7) & 3;
   const int64_t blk = wi >> 9;
   const int kb = static_cast<int>(blk % a.kb_per_tile), tile = static_cast<int>(blk / a.kb_per_tile);
   const int g = lane >> 2, t = lane & 3;
@@ -151,7 +151,7 @@ __global__ void pack_scales_kernel(PackScaleArgs a) {
                                            : static_cast<int64_t>(n) * a.groups + grp;
       z = load_as_float(a.zps, zsrc, a.zp_dtype);
       if (!(z >= 0.f && z <= 127.f && z == rintf(z))) {
-        *a.bad_zp = 1;
+        atomicOr(a.bad_zp, 1);
         z = 0.f;
       }
     }
@@ -160,6 +160,10 @@ __global__ void pack_scales_kernel(PackScaleArgs a) {
   // fp32 value); 128 + zp is exact in bf16.
   const uint32_t sb = __bfloat16_as_ushort(__float2bfloat16_rn(s));
   const uint32_t zb = __bfloat16_as_ushort(__float2bfloat16_rn(128.f + z));
+  // The decode kernel's shift-free dequantiser multiplies by scale * 2^129 and keeps 16 * zp in
+  // eight bits: it needs a normal scale below 0.5 and a zero point below 16.
+  const uint32_t sexp = (sb >> 7) & 0xffu;
+  if (n < a.n && (sexp < 1u || sexp > 125u || z > 15.f)) atomicOr(a.bad_zp, 2);
   a.sz[(static_cast<int64_t>(tile) * a.groups + grp) * tn + (a.tc ? row : scale_slot(row))] =
       (sb << 16) | zb;
 }
@@ -170,7 +174,7 @@ __global__ void dump_dequant_int4_kernel(const uint32_t* tiled, const uint32_t* 
   const int64_t total_words = static_cast<int64_t>(tiles) * kb_per_tile * 512;
   const int64_t wi = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (wi >= total_words) return;
-  const int j = wi & 3, lane = (wi >> 2) & 31, rt = (wi >> 7) & 3;
+  const int rt = wi & 3, lane = (wi >> 2) & 31, j = (wi >> 7) & 3;
   const int64_t blk = wi >> 9;
   const int kb = static_cast<int>(blk % kb_per_tile), tile = static_cast<int>(blk / kb_per_tile);
   const int g = lane >> 2, t = lane & 3;

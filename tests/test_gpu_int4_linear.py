@@ -60,6 +60,27 @@ def test_dequantised_weights_bit_exact(capi, n, k, g, sym):
     np.testing.assert_array_equal(w.view(np.uint32), w_ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("m", [1, 3, 8, 16])
+@pytest.mark.parametrize("n,k,g,std", [(256, 512, 128, 0.02), (192, 1024, 64, 0.02), (128, 768, -1, 0.02),
+                                       (256, 512, 128, 3.0), (128, 512, 256, 1e-3)])
+def test_decode_kernels_use_the_exact_dequantised_weights(capi, m, n, k, g, std):
+    """A one-hot activation row picks out one column of the dequantised weight, so the decode
+    kernels' own dequantisers (every nibble position, both small and large scales) must
+    reproduce bf16((q - zp) * bf16(scale)) bit for bit."""
+    layer = make_int4_layer(n, k, g, seed=n + k + m, std=std)
+    ctx = make_ctx(capi, layer)
+    w_ref = O.dequantize_weight(layer["qw"], layer["s16"], layer["z"], O.WOQ_DTYPE_INT4, k, g)
+    rng = np.random.default_rng(m)
+    for start in range(0, 64, m):
+        cols = [(start + i) * (k // 64) % k + (start + i) % 64 for i in range(m)]
+        cols = [c % k for c in cols]
+        x = np.zeros((m, k), np.float32)
+        x[np.arange(m), cols] = 1.0
+        y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda")))
+        np.testing.assert_array_equal(y.view(np.uint32), w_ref[:, cols].T.copy().view(np.uint32))
+    ctx.workspace(m).status()
+
+
 @pytest.mark.parametrize("m", [1, 4, 32, 256])
 def test_config1_single_linear(capi, m):
     """N = K = 4096, INT4 asymmetric, group 128, no bias, M in {1, 4, 32, 256}."""
