@@ -227,10 +227,27 @@ def run_ours(args):
     attn_slice = attn_in[:, rank * (HIDDEN // p):(rank + 1) * (HIDDEN // p)]
 
     launches_per_step = [0]
+    # With more than one GPU the exchange is part of the linear kernels' epilogue (stores into the
+    # peers' buffers over NVLink); `--collective nccl` runs the NCCL collectives after the
+    # kernels instead, for comparison.
+    fused = p > 1 and args.collective == "fused" and m <= 16
+    comm = None
+    if fused:
+        act_off = (m * QKV_N * 2 + 255) // 256 * 256
+        comm = capi.Comm(rank, p, max(HIDDEN, 2 * FFN // p, QKV_N // p), act_off + m * FFN * 2, device)
 
     def step(x):
         n_launch = 0
         for L in layers:
+            if fused:
+                L["qkv"].linear_allgather(comm, x, gather_offset=0, workspace=ws)
+                L["o_proj"].linear_allreduce(comm, attn_slice, capi.FUSE_ADD, [resid], out=o_out, workspace=ws)
+                L["gate_up"].linear_allgather(comm, o_out, capi.FUSE_SILU_MUL, gather_offset=act_off, workspace=ws)
+                # the row-parallel layer reads this rank's own block of the gathered activation
+                act_mine = comm.gathered(act_off, m, FFN)[:, rank * (FFN // p):(rank + 1) * (FFN // p)]
+                L["down_proj"].linear_allreduce(comm, act_mine, capi.FUSE_ADD, [resid], out=d_out, workspace=ws)
+                n_launch += 4
+                continue
             L["qkv"].linear(x, out=qkv_local, workspace=ws)
             if p > 1:
                 dist.all_gather_into_tensor(qkv_full, qkv_local)
@@ -254,6 +271,9 @@ def run_ours(args):
         return d_out
 
     # eager warm-up (also initialises NCCL), then capture one step in a CUDA graph
+    if p > 1:
+        torch.cuda.synchronize()
+        dist.barrier()  # the fused exchange waits about 2 s for a peer, not for its set-up
     step(hidden)
     torch.cuda.synchronize()
     log("eager step done")
@@ -383,6 +403,8 @@ def run_ours(args):
             "config": {"workload": "llama3-70b linears (QKV 10240x8192, o 8192x8192, gate_up 57344x8192 "
                                    "silu_mul, down 8192x28672), INT4 asym g128, lowp BF16, decode",
                        "m": m, "layers": n_layers, "parallelism": f"tp{p}",
+                       "collective": ("none" if p == 1 else "fused into the linear kernels (peer stores over NVLink)"
+                                      if fused else "nccl"),
                        "l2": "weights (35.8 GB per step over all ranks) exceed L2; no flush needed",
                        "cuda_graph": graph is not None},
             "roofline": roofline, "e2e": e2e, "gpu_launches": n_launch * args.steps,
@@ -453,6 +475,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="phase messages on stderr")
+    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: exchange inside the linear kernels, or NCCL after them")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
     ap.add_argument("--int8", action="store_true", help="--single: INT8 weights with INT8 compute")

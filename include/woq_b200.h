@@ -173,6 +173,52 @@ int woq_b200_linear(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t l
                     const void* const* others, int32_t n_others, void* y, int64_t ldy,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- Tensor-parallel layers on the GPUs of one node ------------------------------------------
+ * The reference shards column-parallel layers along N and row-parallel layers along K and
+ * exchanges through its communication back end after the linear
+ * (intel_extension_for_pytorch/nn/modules/weight_only_quantization.py:536-633,
+ * csrc/cpu/aten/kernels/TPPSHMAllreduceAddKrnl.cpp:183-197 for the shared-memory all-reduce).
+ * Here the exchange is part of the decode kernel's epilogue: every rank owns a buffer of the
+ * same layout ("comm"), maps its peers' buffers through CUDA IPC, and the kernel stores its
+ * tile of the result straight into every rank's buffer over NVLink.  All ranks must issue the
+ * same sequence of calls on a comm, within about two seconds of each other (a kernel that has
+ * waited that long for a peer gives up and sets the workspace status).  One process per GPU; at most 8 ranks; 1..16 tokens. */
+typedef struct woq_b200_comm woq_b200_comm;
+#define WOQ_B200_COMM_HANDLE_BYTES 64
+
+/* Allocates this rank's buffer on the current device: exchange slots for layers whose local
+ * weight has up to max_n rows (row-parallel: N; column-parallel: this rank's N shard) and a
+ * gather area of gather_bytes. */
+int woq_b200_comm_create(int32_t rank, int32_t world, int64_t max_n, size_t gather_bytes,
+                         woq_b200_comm** out);
+/* Writes the 64-byte handle the other ranks need to map this rank's buffer. */
+int woq_b200_comm_export(const woq_b200_comm* comm, void* handle);
+/* `handles`: world x 64 bytes in rank order (this rank's own entry is ignored). */
+int woq_b200_comm_connect(woq_b200_comm* comm, const void* handles);
+/* Device address of this rank's gather area. */
+void* woq_b200_comm_gather_ptr(const woq_b200_comm* comm);
+int woq_b200_comm_destroy(woq_b200_comm* comm);
+
+/* Row-parallel linear fused with the all-reduce: x[M, K_local], this rank's K shard of the
+ * weight; y[M, N] = post_op( bf16(sum over ranks of bf16(x_r W_r^T)) + bias ) on every rank,
+ * the partial outputs added in rank order in fp32 (IpexWoqLinearAllreduce.forward ->
+ * all_reduce_and_bias_add, nn/utils/_weight_prepack.py:139-158).  `bias`: fp32 [N] on the
+ * device or null; the context itself must have been packed without bias. */
+int woq_b200_linear_allreduce(const woq_b200_ctx* ctx, const woq_b200_comm* comm, const void* x,
+                              int64_t m, int64_t ldx, int32_t fusion, const void* const* others,
+                              int32_t n_others, const float* bias, void* y, int64_t ldy,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* Column-parallel linear fused with the all-gather: this rank's N shard; the gathered
+ * [M, world * N_out_local] bf16 tensor appears at byte `gather_offset` of every rank's
+ * gather area (rank r's columns at r * N_out_local) and is complete there when the kernel has
+ * finished.  A gather destination may be written again only after a later exchange on the
+ * same comm has completed on this rank. */
+int woq_b200_linear_allgather(const woq_b200_ctx* ctx, const woq_b200_comm* comm, const void* x,
+                              int64_t m, int64_t ldx, int32_t fusion, const void* const* others,
+                              int32_t n_others, size_t gather_offset, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  Same computation as woq_b200_linear for at most 16 tokens,
  * for callers that may not allocate device memory (memory-planned graphs, servers that forbid
  * allocation after start-up, sandboxes without a re-entrant allocator): the scratch lives in a

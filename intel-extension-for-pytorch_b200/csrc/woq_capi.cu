@@ -423,7 +423,9 @@ size_t woq_b200_workspace_bytes(const woq_b200_ctx* c, int64_t m) {
 
 static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
                       const void* o0, const void* o1, const int32_t* row_idx, const void* row_w,
-                      void* y, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream) {
+                      void* y, int64_t ldy, void* ws, size_t ws_bytes, cudaStream_t stream,
+                      const woq::CommParams* comm = nullptr, const float* bias_override = nullptr,
+                      int64_t ldo_override = 0) {
   if (ws_bytes < woq_b200_workspace_bytes(c, m))
     return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", ws_bytes,
                 woq_b200_workspace_bytes(c, m));
@@ -445,6 +447,7 @@ static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t l
   p.partials = reinterpret_cast<float*>(w8 + kWsHeaderBytes);
   p.ldx = ldx;
   p.ldy = ldy;
+  p.ldo = ldy;
   p.m = (int)m;
   p.n = (int)c->desc.n;
   p.n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? (int)(c->desc.n / 2) : (int)c->desc.n;
@@ -457,6 +460,9 @@ static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t l
   p.gate_up = c->gate_up;
   p.exact = c->desc.kernel_hint == WOQ_B200_HINT_STREAM_FAST ? 0 : c->plain_scales ? 2 : 1;
   p.unit = woq::decode_int4_unit((int)m, c->kb_per_group);
+  if (comm) p.comm = *comm;
+  if (ldo_override) p.ldo = ldo_override;
+  if (bias_override) p.bias = bias_override;
   woq::DecodeShape shape{(int)m, c->tiles, c->kb_per_tile, p.unit};
   const int grid = woq::decode_int4_pick_grid(shape, c->num_sms);
   CUDA_TRY(woq::launch_decode_int4(p, grid, stream));
@@ -663,6 +669,161 @@ int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
       return rc;
   }
   return WOQ_B200_OK;
+}
+
+// ---- tensor-parallel exchange (one node, CUDA IPC) ---------------------------------------
+struct woq_b200_comm {
+  uint64_t magic;
+  int rank, world, device;
+  int64_t ar_n;         // row length of an all-reduce slot (multiple of 64)
+  size_t gather_off, gather_bytes, total_bytes;
+  uint8_t* local;       // this rank's buffer (cudaMalloc)
+  uint8_t* peer[woq::kCommMaxRanks];
+  bool connected;
+};
+
+static int check_comm(const woq_b200_comm* cm) {
+  if (!cm) return fail(WOQ_B200_ERR_INVALID_ARG, "comm is null");
+  if (cm->magic != kMagic + 1) return fail(WOQ_B200_ERR_BAD_HANDLE, "comm magic mismatch");
+  return WOQ_B200_OK;
+}
+
+int woq_b200_comm_create(int32_t rank, int32_t world, int64_t max_n, size_t gather_bytes,
+                         woq_b200_comm** out) {
+  if (!out) return fail(WOQ_B200_ERR_INVALID_ARG, "out is null");
+  if (world < 1 || world > woq::kCommMaxRanks || rank < 0 || rank >= world)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "rank %d of %d: at most %d ranks", rank, world, woq::kCommMaxRanks);
+  if (max_n < 1 || max_n > static_cast<int64_t>(woq::kCommMaxTiles) * woq::kTileN)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "max_n out of range");
+  woq_b200_comm* cm = new woq_b200_comm();
+  cm->rank = rank;
+  cm->world = world;
+  cm->ar_n = (max_n + woq::kTileN - 1) / woq::kTileN * woq::kTileN;
+  // {2 x bf16, stamp} words: [2 parities][8 sources][ar_n / 64 tiles][16 tokens][32 lanes] x 8 B
+  const size_t ar_bytes = static_cast<size_t>(cm->ar_n) * 1024;
+  cm->gather_off = (woq::kCommCtlBytes + ar_bytes + 255) / 256 * 256;
+  cm->gather_bytes = (gather_bytes + 255) / 256 * 256;
+  cm->total_bytes = cm->gather_off + cm->gather_bytes;
+  cm->connected = false;
+  for (auto& q : cm->peer) q = nullptr;
+  cudaError_t e = cudaGetDevice(&cm->device);
+  if (e == cudaSuccess) e = cudaMalloc(&cm->local, cm->total_bytes);
+  if (e == cudaSuccess) e = cudaMemset(cm->local, 0, cm->total_bytes);
+  if (e != cudaSuccess) {
+    delete cm;
+    return fail(WOQ_B200_ERR_CUDA, "comm buffer: %s", cudaGetErrorString(e));
+  }
+  cm->peer[rank] = cm->local;
+  cm->magic = kMagic + 1;
+  *out = cm;
+  return WOQ_B200_OK;
+}
+
+int woq_b200_comm_export(const woq_b200_comm* cm, void* handle) {
+  if (int rc = check_comm(cm)) return rc;
+  static_assert(sizeof(cudaIpcMemHandle_t) == WOQ_B200_COMM_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t h;
+  CUDA_TRY(cudaIpcGetMemHandle(&h, cm->local));
+  memcpy(handle, &h, sizeof(h));
+  return WOQ_B200_OK;
+}
+
+int woq_b200_comm_connect(woq_b200_comm* cm, const void* handles) {
+  if (int rc = check_comm(cm)) return rc;
+  if (cm->connected) return fail(WOQ_B200_ERR_INVALID_ARG, "comm is already connected");
+  for (int q = 0; q < cm->world; ++q) {
+    if (q == cm->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(handles) + q * sizeof(h), sizeof(h));
+    void* ptr = nullptr;
+    CUDA_TRY(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    cm->peer[q] = static_cast<uint8_t*>(ptr);
+  }
+  cm->connected = true;
+  return WOQ_B200_OK;
+}
+
+void* woq_b200_comm_gather_ptr(const woq_b200_comm* cm) {
+  if (check_comm(cm)) return nullptr;
+  return cm->local + cm->gather_off;
+}
+
+int woq_b200_comm_destroy(woq_b200_comm* cm) {
+  if (int rc = check_comm(cm)) return rc;
+  cm->magic = 0;
+  for (int q = 0; q < cm->world; ++q)
+    if (q != cm->rank && cm->peer[q]) cudaIpcCloseMemHandle(cm->peer[q]);
+  cudaFree(cm->local);
+  delete cm;
+  return WOQ_B200_OK;
+}
+
+static int comm_params(const woq_b200_ctx* c, const woq_b200_comm* cm, int64_t m, woq::CommParams* cp) {
+  if (int rc = check_ctx(c)) return rc;
+  if (int rc = check_comm(cm)) return rc;
+  if (!cm->connected && cm->world > 1) return fail(WOQ_B200_ERR_INVALID_ARG, "comm is not connected");
+  if (c->is_int8 || m > 16 || m < 1)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the fused exchange covers INT4 weights and 1..16 tokens");
+  if (!c->wq) return fail(WOQ_B200_ERR_UNSUPPORTED, "context was packed without the streaming layout");
+  if (c->tiles > woq::kCommMaxTiles) return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the stamp table");
+  for (int q = 0; q < woq::kCommMaxRanks; ++q) cp->peer[q] = cm->peer[q];
+  cp->world = cm->world;
+  cp->rank = cm->rank;
+  cp->ar_n = cm->ar_n;
+  return WOQ_B200_OK;
+}
+
+int woq_b200_linear_allreduce(const woq_b200_ctx* c, const woq_b200_comm* cm, const void* x, int64_t m,
+                              int64_t ldx, int32_t fusion, const void* const* others,
+                              int32_t n_others, const float* bias, void* y, int64_t ldy,
+                              void* workspace, size_t workspace_bytes, void* stream_) {
+  woq::CommParams cp{};
+  if (m == 0) return WOQ_B200_OK;
+  if (int rc = comm_params(c, cm, m, &cp)) return rc;
+  cp.mode = woq::kCommAllReduce;
+  if (c->bias) return fail(WOQ_B200_ERR_INVALID_ARG, "a row-parallel context must be packed without bias (it is added after the reduction)");
+  if (c->desc.n > cm->ar_n) return fail(WOQ_B200_ERR_INVALID_ARG, "N exceeds the comm's max_n");
+  int need = fusion == WOQ_B200_FUSE_ADD || fusion == WOQ_B200_FUSE_MUL ? 1 : fusion == WOQ_B200_FUSE_ADD_ADD ? 2 : 0;
+  if (fusion == WOQ_B200_FUSE_SILU_MUL || fusion == WOQ_B200_FUSE_SCALED_SCATTER_ADD)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "fusion %#x cannot follow a reduction over K shards", fusion);
+  if (n_others != need || (need > 0 && !others)) return fail(WOQ_B200_ERR_INVALID_ARG, "fusion %#x takes %d extra tensors", fusion, need);
+  if (!x || !y || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "x, y and workspace must be non-null");
+  if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
+  if (ldy < c->desc.n) return fail(WOQ_B200_ERR_INVALID_ARG, "ldy smaller than the output width");
+  return run_decode(c, x, m, ldx, fusion, need > 0 ? others[0] : nullptr, need > 1 ? others[1] : nullptr,
+                    nullptr, nullptr, y, ldy, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_),
+                    &cp, bias);
+}
+
+int woq_b200_linear_allgather(const woq_b200_ctx* c, const woq_b200_comm* cm, const void* x, int64_t m,
+                              int64_t ldx, int32_t fusion, const void* const* others,
+                              int32_t n_others, size_t gather_offset, void* workspace,
+                              size_t workspace_bytes, void* stream_) {
+  woq::CommParams cp{};
+  if (m == 0) return WOQ_B200_OK;
+  if (int rc = comm_params(c, cm, m, &cp)) return rc;
+  cp.mode = woq::kCommAllGather;
+  if (fusion == WOQ_B200_FUSE_SCALED_SCATTER_ADD) return fail(WOQ_B200_ERR_INVALID_ARG, "scatter cannot be gathered");
+  if (fusion == WOQ_B200_FUSE_SILU_MUL && !c->gate_up)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "silu_mul needs a context created with the gate/up layout");
+  int need = fusion == WOQ_B200_FUSE_ADD || fusion == WOQ_B200_FUSE_MUL ? 1 : fusion == WOQ_B200_FUSE_ADD_ADD ? 2 : 0;
+  if (n_others != need || (need > 0 && !others)) return fail(WOQ_B200_ERR_INVALID_ARG, "fusion %#x takes %d extra tensors", fusion, need);
+  const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? c->desc.n / 2 : c->desc.n;
+  const size_t bytes = static_cast<size_t>(m) * n_out * cm->world * 2;
+  if ((gather_offset % 16) != 0 || gather_offset + bytes > cm->gather_bytes)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "gathered tensor [%lld, %lld] at offset %zu does not fit the gather area (%zu bytes)",
+                (long long)m, (long long)(n_out * cm->world), gather_offset, cm->gather_bytes);
+  if (!x || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "x and workspace must be non-null");
+  if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
+  if (c->desc.n > cm->ar_n) return fail(WOQ_B200_ERR_INVALID_ARG, "N exceeds the comm's max_n");
+  // y = this rank's column block of the gathered tensor; `others` are local [M, N_out] tensors
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(cm->local + cm->gather_off + gather_offset) +
+                     static_cast<int64_t>(cm->rank) * n_out;
+  return run_decode(c, x, m, ldx, fusion, need > 0 ? others[0] : nullptr, need > 1 ? others[1] : nullptr,
+                    nullptr, nullptr, y, n_out * cm->world, workspace, workspace_bytes,
+                    static_cast<cudaStream_t>(stream_), &cp, nullptr, n_out);
 }
 
 int woq_b200_linear_scatter(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx,

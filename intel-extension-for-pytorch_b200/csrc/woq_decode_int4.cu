@@ -59,6 +59,7 @@ struct SmemHeader {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   int abort_flag;
+  int finished_warps;  // of the two warps that run epilogues
 };
 
 // The k-block sequence is dealt out in units of `unit` k-blocks: CTA c owns units
@@ -67,19 +68,60 @@ __device__ __forceinline__ int owner_of(int64_t b, int unit, int64_t units, int6
   return static_cast<int>(((b / unit + 1) * ctas - 1) / units);
 }
 
-// bias, rounding and the fused post-op for one (row, token) of tile `tl`
-__device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tl, int row, int tok, float r) {
+__device__ __forceinline__ uint32_t* comm_ctl(uint8_t* base) { return reinterpret_cast<uint32_t*>(base); }
+// Exchange slots carry their own arrival mark: every 8-byte word is {two bf16 values, stamp},
+// written with one store, so data and mark arrive together and no fence is needed.
+// [epoch parity][source rank][tile][token][lane] words.
+__device__ __forceinline__ uint2* comm_ar_word(const CommParams& c, uint8_t* base, int parity, int src,
+                                               int tile, int tok, int lane) {
+  const size_t tiles = static_cast<size_t>(c.ar_n / kTileN);
+  return reinterpret_cast<uint2*>(base + kCommCtlBytes) +
+         (((static_cast<size_t>(parity) * kCommMaxRanks + src) * tiles + tile) * 16 + tok) * 32 + lane;
+}
+__device__ __forceinline__ void st_relaxed_sys_v2(uint2* p, uint2 v) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// Polls (bounded) until the word carries `stamp`; returns its data half.
+__device__ __forceinline__ uint32_t comm_wait_word(const uint2* w, uint32_t stamp, int* status) {
+  uint2 v = ld_relaxed_sys_v2(w);
+  if (v.y == stamp) return v.x;
+  if (*reinterpret_cast<volatile int*>(status) != 0) return 0u;
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    v = ld_relaxed_sys_v2(w);
+    if (v.y == stamp) return v.x;
+    if ((++spins & 255u) == 0) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
+        atomicCAS(status, 0, 3);
+        return 0u;
+      }
+    }
+  }
+}
+
+// Bias, rounding and the fused post-op for one (row, token) of tile `tl`; stores the result
+// (scatter epilogue: adds it into its row) and returns its bf16 bits, 0 where nothing is stored.
+__device__ __forceinline__ uint32_t decode_epilogue(const DecodeParams& p, int tl, int row, int tok, float r) {
   const int n = decode_row_to_n(p, tl, row);
-  if (tok >= p.m || n >= p.n) return;
+  if (tok >= p.m || n >= p.n) return 0u;
   if (p.bias) r += p.bias[n];
   r = bf16_round(r);
   if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
     const size_t o = static_cast<size_t>(p.row_idx[tok]) * p.ldy + n;
     const float w = __bfloat162float(p.row_w[tok]);
     p.y[o] = __float2bfloat16_rn(__bfloat162float(p.y[o]) + r * w);
-    return;
+    return 0u;
   }
-  const size_t o = static_cast<size_t>(tok) * p.ldy + n;
+  const size_t o = static_cast<size_t>(tok) * p.ldo + n;  // in the fused operands
   if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
     r = bf16_round(r + __bfloat162float(p.other0[o]));
     if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __bfloat162float(p.other1[o]));
@@ -88,7 +130,9 @@ __device__ __forceinline__ void decode_epilogue(const DecodeParams& p, int tl, i
   } else {
     r = unary_post_op(r, p.fusion);
   }
-  p.y[o] = __float2bfloat16_rn(r);
+  const __nv_bfloat16 v = __float2bfloat16_rn(r);
+  p.y[static_cast<size_t>(tok) * p.ldy + n] = v;
+  return __bfloat16_as_ushort(v);
 }
 
 // The stages a CTA walks: its share [b_begin, b_end) of the k-block sequence cut at tile
@@ -141,6 +185,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
       mbar_init(&hdr->empty[s], kConsumerWarps);
     }
     hdr->abort_flag = 0;
+    hdr->finished_warps = 0;
     mbar_fence_init();
   }
   __syncthreads();
@@ -159,28 +204,113 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
   // shared memory, so the consumers go straight on to the next tile; then it either runs the
   // fused epilogue or parks a partial tile and, if this CTA is the last contributor to
   // arrive, reduces the tile in a fixed order.
-  auto run_epilogue = [&](int tl, const float* a0, const float* a1) {
+  uint32_t epoch = 0;  // read by the warps that run epilogues, once the previous grid is done
+  auto run_epilogue = [&](int tl, float* a0, float* a1) {
+    if (p.comm.mode == kCommAllReduce) {
+      // Row-parallel linear: every rank's bf16 partial of this tile goes to every rank; each
+      // rank then adds them in rank order (fp32) and rounds once, so all ranks hold the same
+      // bits; bias and post-op follow the reduction.
+      const CommParams& c = p.comm;
+      const uint32_t stamp = epoch + 1;
+      const int parity = epoch & 1;
+      uint32_t mine[NTOK];
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < p.m) {
+          mine[tok] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a0[tok]))) |
+                      (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a1[tok]))) << 16);
+          for (int q = 0; q < c.world; ++q)
+            if (q != c.rank)
+              st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
+                                make_uint2(mine[tok], stamp));
+        }
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < p.m) {
+          float s0 = 0.f, s1 = 0.f;
+          for (int r = 0; r < c.world; ++r) {
+            const uint32_t w = r == c.rank ? mine[tok]
+                                           : comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane),
+                                                            stamp, p.status);
+            s0 += __uint_as_float(w << 16);
+            s1 += __uint_as_float(w & 0xffff0000u);
+          }
+          a0[tok] = bf16_round(s0);
+          a1[tok] = bf16_round(s1);
+        }
+    }
+    // words for the gather: the two results of this lane per token
+    uint32_t out[NTOK];
     if (p.fusion == FUSE_SILU_MUL) {
       // gate/up layout: row lane is a gate row, row lane + 32 its up row
       const int col = tl * 32 + lane;
       const int n_gate = decode_row_to_n(p, tl, lane);
       const int n_up = decode_row_to_n(p, tl, lane + 32);
 #pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
+      for (int tok = 0; tok < NTOK; ++tok) {
+        out[tok] = 0u;
         if (tok < p.m && col < p.n_out) {
           float gate = a0[tok], up = a1[tok];
           if (p.bias) {
             gate += p.bias[n_gate];
             up += p.bias[n_up];
           }
-          p.y[static_cast<size_t>(tok) * p.ldy + col] =
-              __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
+          const __nv_bfloat16 v = __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
+          p.y[static_cast<size_t>(tok) * p.ldy + col] = v;
+          out[tok] = __bfloat16_as_ushort(v);
         }
+      }
     } else {
 #pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok) {
-        decode_epilogue(p, tl, lane, tok, a0[tok]);
-        decode_epilogue(p, tl, lane + 32, tok, a1[tok]);
+      for (int tok = 0; tok < NTOK; ++tok)
+        out[tok] = decode_epilogue(p, tl, lane, tok, a0[tok]) |
+                   (decode_epilogue(p, tl, lane + 32, tok, a1[tok]) << 16);
+    }
+    if (p.comm.mode == kCommAllGather) {
+      // Column-parallel linear: p.y is this rank's column block of the gathered tensor.  The
+      // tile also goes to every other rank, and the same tile of every other rank is copied
+      // from this rank's slots into its column block here, so that the gathered tensor is
+      // written by local stores only and is complete when this kernel ends.
+      const CommParams& c = p.comm;
+      const uint32_t stamp = epoch + 1;
+      const int parity = epoch & 1;
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < p.m)
+          for (int q = 0; q < c.world; ++q)
+            if (q != c.rank)
+              st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
+                                make_uint2(out[tok], stamp));
+      const bool pair = p.fusion != FUSE_SILU_MUL;
+      const int c0 = pair ? decode_row_to_n(p, tl, lane) : tl * 32 + lane;
+      const int c1 = decode_row_to_n(p, tl, lane + 32);
+      for (int r = 0; r < c.world; ++r) {
+        if (r == c.rank) continue;
+        __nv_bfloat16* dst = p.y + (static_cast<int64_t>(r) - c.rank) * p.n_out;
+#pragma unroll
+        for (int tok = 0; tok < NTOK; ++tok)
+          if (tok < p.m) {
+            const uint32_t w = comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane), stamp, p.status);
+            if (c0 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w & 0xffffu));
+            if (pair && c1 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w >> 16));
+          }
+      }
+    }
+  };
+  // Both epilogue-running warps call this when they are done; the second one of the last CTA
+  // of the grid closes the epoch.
+  auto finish_comm = [&]() {
+    if (p.comm.mode == kCommNone) return;
+    int second = 0;
+    if (lane == 0) second = atomicAdd(&hdr->finished_warps, 1);
+    if (!__shfl_sync(0xffffffffu, second, 0)) return;
+    if (lane == 0) {
+      uint32_t* ctl = comm_ctl(p.comm.peer[p.comm.rank]);
+      __threadfence();
+      if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {
+        ctl[1] = 0;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(ctl) = epoch + 1;
       }
     }
   };
@@ -293,6 +423,8 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
           fill.next(fill.nkb());
         }
       grid_dependency_wait();
+      if (p.comm.mode != kCommNone)
+        epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
       __syncwarp();
       for (int s = 0; s < p.stages && !it.done(); ++s) {
         issue_x(it, s);
@@ -328,6 +460,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
                    nseg == 1, v0, v1, pend_tile, pend_old);
       if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
     }
+    finish_comm();
     return;
   }
 
@@ -337,11 +470,14 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
     int pend_tile = -1;
     unsigned pend_old = 0;
     grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
+    if (p.comm.mode != kCommNone)
+      epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
     for (int sg = 0; sg + 1 < nseg; ++sg) {
       take_segment(kBarRedFull, true, tile0 + sg, sg > 0 || kb00 == 0, sg == 0, v0, v1, pend_tile,
                    pend_old);
     }
     if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
+    finish_comm();
     return;
   }
 

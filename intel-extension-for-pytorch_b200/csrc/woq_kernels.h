@@ -6,6 +6,31 @@
 
 namespace woq {
 
+// ---- tensor-parallel exchange fused into the decode kernel's epilogue ---------------------
+// Every rank of one node owns a "symmetric" buffer with the same layout and maps all peers'
+// buffers (CUDA IPC).  Layout of one buffer:
+//   [0, 4096)               control words: epoch (u32 @0), finished CTAs of the running grid (u32 @4)
+//   [4096, +slot_n*1024)    exchange words {2 x bf16, stamp}, 8 bytes each:
+//                           [epoch parity][source rank][tile][token][lane]
+//   [gather_off, ..)        gather area (the caller places gathered tensors here)
+// A launch with a comm mode is one "epoch" (the same number on every rank, because all ranks
+// issue the same sequence of launches); its stamp is epoch + 1.  The warp that finishes a
+// tile stores each lane's two results and the stamp as one 8-byte word into every other
+// rank's slot (data and mark arrive together, no fence), then polls its own slots for the
+// other ranks' words of the same tile and adds them (all-reduce) or copies them into its
+// gathered tensor (all-gather).  Slots alternate with the epoch's parity: a rank can be at
+// most one epoch ahead of a peer, because finishing an epoch takes every peer's words.
+constexpr int kCommMaxRanks = 8;
+constexpr int kCommMaxTiles = 1024;
+constexpr int kCommCtlBytes = 4096;
+enum CommMode { kCommNone = 0, kCommAllReduce = 1, kCommAllGather = 2 };
+
+struct CommParams {
+  uint8_t* peer[kCommMaxRanks];  // base of every rank's buffer as mapped here (peer[rank]: own)
+  int mode, world, rank;
+  int64_t ar_n;        // 64 x the tiles a slot set holds
+};
+
 // ---- INT4 decode (M <= 16) -----------------------------------------------------------
 struct DecodeParams {
   const uint8_t* wq;       // tiled nibbles [tiles][kb_per_tile][2048]
@@ -21,6 +46,7 @@ struct DecodeParams {
   uint32_t* counters;      // [tiles], zero between calls
   int* status;             // 0, or the code of the wait that gave up
   int64_t ldx, ldy;
+  int64_t ldo;  // row length of other0 / other1
   int m, n, n_out, k;
   int tiles, kb_per_tile, kbpg_shift, groups, gps;  // gps = groups a full stage can touch
   int fusion, gate_up, stages;
@@ -30,6 +56,7 @@ struct DecodeParams {
   // experiment switches (timing only, results are wrong): 1 skip math, 2 skip x copies, 4 skip
   // scale copies, 8 copy only the first pipeline fill, 16 consumers never wait
   int debug;
+  CommParams comm;
 };
 
 struct DecodeShape {

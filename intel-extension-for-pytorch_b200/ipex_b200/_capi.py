@@ -44,6 +44,13 @@ EXPORTS = [
     "woq_b200_dump_dequant",
     "woq_b200_int8_internals",
     "woq_b200_workspace_status",
+    "woq_b200_comm_create",
+    "woq_b200_comm_export",
+    "woq_b200_comm_connect",
+    "woq_b200_comm_gather_ptr",
+    "woq_b200_comm_destroy",
+    "woq_b200_linear_allreduce",
+    "woq_b200_linear_allgather",
 ]
 
 
@@ -106,6 +113,15 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
     L.woq_b200_workspace_status.argtypes = [vp, vp]
+    L.woq_b200_comm_create.argtypes = [i32, i32, i64, sz, ctypes.POINTER(vp)]
+    L.woq_b200_comm_export.argtypes = [vp, vp]
+    L.woq_b200_comm_connect.argtypes = [vp, vp]
+    L.woq_b200_comm_gather_ptr.argtypes = [vp]
+    L.woq_b200_comm_gather_ptr.restype = vp
+    L.woq_b200_comm_destroy.argtypes = [vp]
+    L.woq_b200_linear_allreduce.argtypes = [vp, vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, vp, i64,
+                                            vp, sz, vp]
+    L.woq_b200_linear_allgather.argtypes = [vp, vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, sz, vp, sz, vp]
     _lib = L
     return L
 
@@ -145,6 +161,69 @@ class Workspace:
 
     def status(self) -> None:
         _check(lib().woq_b200_workspace_status(self.buf.data_ptr(), _stream()))
+
+
+class _DevicePointer:
+    """Wraps a raw device address for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+        }
+
+
+class Comm:
+    """Peer-mapped buffers of the tensor-parallel ranks of one node (woq_b200_comm).
+
+    `exchange(handle_bytes) -> list of every rank's handle bytes in rank order` is how the 64-byte
+    handles travel; by default torch.distributed.all_gather_object of the default group is used.
+    All ranks must issue the same sequence of fused calls on a Comm."""
+
+    HANDLE_BYTES = 64
+
+    def __init__(self, rank: int, world: int, max_n: int, gather_bytes: int, device, exchange=None):
+        self.rank, self.world = rank, world
+        self.device = torch.device(device)
+        self.gather_bytes = int(gather_bytes)
+        self._h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_comm_create(rank, world, max_n, self.gather_bytes, ctypes.byref(self._h)))
+            mine = ctypes.create_string_buffer(self.HANDLE_BYTES)
+            _check(lib().woq_b200_comm_export(self._h, mine))
+            if world > 1:
+                if exchange is None:
+                    import torch.distributed as dist
+
+                    def exchange(b):
+                        out = [None] * world
+                        dist.all_gather_object(out, b)
+                        return out
+
+                handles = exchange(mine.raw)
+                if len(handles) != world or any(len(h) != self.HANDLE_BYTES for h in handles):
+                    raise ValueError("exchange() must return one 64-byte handle per rank")
+                _check(lib().woq_b200_comm_connect(self._h, b"".join(handles)))
+            else:
+                _check(lib().woq_b200_comm_connect(self._h, mine.raw))
+            ptr = lib().woq_b200_comm_gather_ptr(self._h)
+            self._gather = torch.as_tensor(_DevicePointer(ptr, max(self.gather_bytes, 1)), device=self.device)
+
+    def gathered(self, offset: int, m: int, n_full: int) -> torch.Tensor:
+        """View of the [m, n_full] bf16 tensor at byte `offset` of this rank's gather area."""
+        nbytes = m * n_full * 2
+        return self._gather[offset:offset + nbytes].view(torch.bfloat16).view(m, n_full)
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            torch.cuda.synchronize(self.device)
+            lib().woq_b200_comm_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class WoqContext:
@@ -248,6 +327,44 @@ class WoqContext:
                 )
             )
         return out.reshape(*x.shape[:-1], n_out)
+
+    def linear_allreduce(self, comm: "Comm", x, fusion: int = FUSE_NONE, others: Sequence[torch.Tensor] = (),
+                         bias: Optional[torch.Tensor] = None, out=None, workspace=None) -> torch.Tensor:
+        """Row-parallel linear (this rank's K shard) fused with the all-reduce; 1..16 tokens."""
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty((m, self.n), dtype=torch.bfloat16, device=x.device)
+        ws = workspace or self.workspace(m)
+        oth = [o.reshape(m, self.n).contiguous() for o in others]
+        arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
+        if bias is not None and (bias.dtype != torch.float32 or not bias.is_cuda):
+            raise ValueError("bias must be an fp32 CUDA tensor")
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_linear_allreduce(
+                self._h, comm._h, x2.data_ptr(), m, x2.stride(0), fusion, arr, len(oth), _ptr(bias),
+                out.data_ptr(), out.stride(0), ws.buf.data_ptr(), ws.nbytes, _stream()))
+        return out
+
+    def linear_allgather(self, comm: "Comm", x, fusion: int = FUSE_NONE, others: Sequence[torch.Tensor] = (),
+                         gather_offset: int = 0, workspace=None) -> torch.Tensor:
+        """Column-parallel linear (this rank's N shard) fused with the all-gather; returns the
+        gathered [m, world * n_out] view inside the comm's gather area."""
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        n_out = self.n // 2 if fusion == FUSE_SILU_MUL else self.n
+        ws = workspace or self.workspace(m)
+        oth = [o.reshape(m, n_out).contiguous() for o in others]
+        arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_linear_allgather(
+                self._h, comm._h, x2.data_ptr(), m, x2.stride(0), fusion, arr, len(oth), gather_offset,
+                ws.buf.data_ptr(), ws.nbytes, _stream()))
+        return comm.gathered(gather_offset, m, n_out * comm.world)
 
     def linear_static_scratch(self, x, fusion=FUSE_NONE, others=(), out=None):
         """woq_b200_linear_static_scratch: at most 16 tokens, scratch inside the library, no

@@ -80,7 +80,7 @@ def _tp_worker(rank, world, port, ret):
 
 def test_row_parallel_reduce_two_ranks_gloo(ipex):
     world = 2
-    mgr = mp.Manager()
+    mgr = mp.get_context("spawn").Manager()  # no fork of this multi-threaded process
     ret = mgr.dict()
     port = 29500 + os.getpid() % 500
     mp.spawn(_tp_worker, args=(world, port, ret), nprocs=world, join=True)
