@@ -1,6 +1,7 @@
 """CPU-only checks of the Python surface: the extension loads, the operators exist with the
 reference's schemas, and the tensor-parallel helper reduces over a 2-rank gloo group."""
 import os
+import socket
 import sys
 
 import pytest
@@ -82,6 +83,8 @@ def test_row_parallel_reduce_two_ranks_gloo(ipex):
     world = 2
     mgr = mp.get_context("spawn").Manager()  # no fork of this multi-threaded process
     ret = mgr.dict()
-    port = 29500 + os.getpid() % 500
+    with socket.socket() as sock:  # a free port, not a guessed one
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     mp.spawn(_tp_worker, args=(world, port, ret), nprocs=world, join=True)
     assert all(ret[r] for r in range(world))
