@@ -5,13 +5,14 @@
 // activations are the B operand (N = tokens, 16..256), so one CTA tile is y^T[128 rows x
 // tokens] accumulated in fp32 in TMEM over the whole K of its share.
 //
-//   warp 16     producer: bulk copies of packed nibbles + group scales, TMA tile loads of x
-//               (128-byte swizzled K-major rows) - all completing on mbarriers;
+//   warp 16     producer: bulk copies of packed nibbles + group scales;
+//   warp 18     producer: TMA tile loads of x (128-byte swizzled K-major rows) - all copies
+//               complete on mbarriers;
 //   warps 0-15  dequantise: thread = output row.  Two 128-bit shared loads give the row's 64
 //               nibbles of a k-block; each becomes bf16((q - zp) * bf16(scale)) exactly (the
 //               reference's tile dequantiser) and the 32 packed registers go straight to
 //               TMEM with one tcgen05.st - the dequantised tile never touches shared memory.
-//               Consecutive k-blocks go round-robin to the four warpgroups;
+//               Consecutive stages go round-robin to the four warpgroups;
 //   warp 17     one thread issues tcgen05.mma (A from TMEM, B from shared memory) and
 //               releases A slots / x stages / the accumulator with tcgen05.commit;
 //   warps 0-15  epilogue at the end of a tile segment: tcgen05.ld the accumulators, then
@@ -30,8 +31,8 @@ namespace {
 
 constexpr int kDequantWarps = 16;
 constexpr int kWarpGroups = kDequantWarps / 4;
-constexpr int kTcThreads = (kDequantWarps + 2) * 32;
-constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1;
+constexpr int kTcThreads = (kDequantWarps + 3) * 32;
+constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1, kXProducerWarp = kDequantWarps + 2;
 constexpr int kASlots = 8;           // 32 TMEM columns each (one k-block of bf16 A)
 constexpr int kDCol0 = 0;            // accumulator columns [0, 256)
 constexpr int kDCols = 256;
@@ -113,12 +114,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->w_full[s], 1);
-      mbar_init(&hdr->w_empty[s], kDequantWarps);
+      mbar_init(&hdr->w_empty[s], 4);
       mbar_init(&hdr->x_full[s], 1);
       mbar_init(&hdr->x_empty[s], 1);
     }
     for (int s = 0; s < kASlots; ++s) {
-      mbar_init(&hdr->a_full[s], kDequantWarps);
+      mbar_init(&hdr->a_full[s], 4);
       mbar_init(&hdr->a_empty[s], 1);
     }
     mbar_init(&hdr->d_full, 1);
@@ -171,12 +172,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   };
 
   if (warp == kProducerWarp) {
+    // packed weights and their group scales
     if (lane == 0) {
       int pst = 0;
       while (b < b_end) {
         const int nkb = stage_len();
         uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
-        uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
         const int g0 = kb0 >> p.kbpg_shift;
         const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
         tc_stamp(p, 0, pst, 0);
@@ -188,8 +189,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         bulk_g2s(ws + p.kbs * kTcBlockBytes,
                  p.sz + (static_cast<size_t>(tile) * p.groups + g0) * kTcTileN, ng * 512,
                  &hdr->w_full[slot]);
-        mbar_wait(&hdr->x_empty[slot], phase ^ 1, abort_flag, p.status, 12);
         tc_stamp(p, 0, pst, 2);
+        ++pst;
+        advance(nkb);
+      }
+    }
+  } else if (warp == kXProducerWarp) {
+    // activation tiles (TMA, 128-byte swizzle), one per k-block
+    if (lane == 0) {
+      while (b < b_end) {
+        const int nkb = stage_len();
+        uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
+        mbar_wait(&hdr->x_empty[slot], phase ^ 1, abort_flag, p.status, 12);
         if (p.debug & 8) {
           mbar_arrive(&hdr->x_full[slot]);
         } else {
@@ -197,8 +208,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           for (int j = 0; j < nkb; ++j)
             tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->x_full[slot]);
         }
-        tc_stamp(p, 0, pst, 3);
-        ++pst;
         advance(nkb);
       }
     }
@@ -285,32 +294,47 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       const int c_first = tc_owner_of(tb0, total, gridDim.x);
       const int c_last = tc_owner_of(tb0 + p.kb_per_tile - 1, total, gridDim.x);
       for (int ch = wg; ch < n_chunks; ch += kWarpGroups) {
+        if (ch * 8 >= p.m) break;
+        // eight tokens at a time, all their loads in flight together
+        float v[8], v_up[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = v_up[e] = 0.f;
+        for (int cc = c_first; cc <= c_last; ++cc) {
+          const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
+          const int slot2 = whole ? own_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
+          const float* src = p.partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
+                             static_cast<size_t>(ch * 8) * kTcTileN + row;
+          float part[8], part_up[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            part[e] = __ldcg(src + e * kTcTileN);
+            part_up[e] = (p.fusion == FUSE_SILU_MUL && row < 64) ? __ldcg(src + e * kTcTileN + 64) : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[e] += part[e];
+            v_up[e] += part_up[e];
+          }
+        }
+#pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int tok = ch * 8 + e;
           if (tok >= p.m) break;
-          float v = 0.f, v_up = 0.f;
-          for (int cc = c_first; cc <= c_last; ++cc) {
-            const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
-            const int slot2 = whole ? own_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
-            const float* src = p.partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
-                               static_cast<size_t>(tok) * kTcTileN;
-            v += __ldcg(src + row);
-            if (p.fusion == FUSE_SILU_MUL && row < 64) v_up += __ldcg(src + row + 64);
-          }
           if (p.fusion == FUSE_SILU_MUL) {
             if (row < 64) {
               const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
+              float g = v[e], u = v_up[e];
               if (p.bias) {
-                v += p.bias[n_gate];
-                v_up += p.bias[n_up];
+                g += p.bias[n_gate];
+                u += p.bias[n_up];
               }
-              const float gate = bf16_round(v), up = bf16_round(v_up);
+              const float gate = bf16_round(g), up = bf16_round(u);
               if (n_gate < p.n_out)
                 p.y[static_cast<size_t>(tok) * p.ldy + n_gate] =
                     __float2bfloat16_rn(up * silu_bf16(gate));
             }
           } else {
-            tc_store(p, t, row, tok, v);
+            tc_store(p, t, row, tok, v[e]);
           }
         }
       }
@@ -321,41 +345,44 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       const int nkb = stage_len();
       const uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
       const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
-      if (tid == 0) tc_stamp(p, 2, stage_no, 0);
-      mbar_wait(&hdr->w_full[slot], phase, abort_flag, p.status, 16);
-      if (tid == 0) tc_stamp(p, 2, stage_no, 1);
-      // k-block j of this stage belongs to warpgroup (stage_no * kbs + j) % 4
-      const int j = (wg - stage_no * p.kbs) & (kWarpGroups - 1);
-      if (j < nkb) {
-        const uint4* wp = reinterpret_cast<const uint4*>(ws + j * kTcBlockBytes);
-        const uint4 v0 = wp[row], v1 = wp[kTcTileN + row];
+      // the stages go round-robin to the four warpgroups; the others only keep count
+      if ((stage_no & (kWarpGroups - 1)) == wg) {
+        if (tid == 0) tc_stamp(p, 2, stage_no, 0);
+        mbar_wait(&hdr->w_full[slot], phase, abort_flag, p.status, 16);
+        if (tid == 0) tc_stamp(p, 2, stage_no, 1);
         const int g0 = kb0 >> p.kbpg_shift;
-        const uint32_t szw = reinterpret_cast<const uint32_t*>(
-            ws + p.kbs * kTcBlockBytes)[(((kb0 + j) >> p.kbpg_shift) - g0) * kTcTileN + row];
-        const uint32_t z2 = __byte_perm(szw, 0, 0x1010), s2 = __byte_perm(szw, 0, 0x3232);
-        const uint32_t words[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        uint32_t r[32];
+        for (int j = 0; j < nkb; ++j) {
+          const uint4* wp = reinterpret_cast<const uint4*>(ws + j * kTcBlockBytes);
+          const uint4 v0 = wp[row], v1 = wp[kTcTileN + row];
+          const uint32_t szw = reinterpret_cast<const uint32_t*>(
+              ws + p.kbs * kTcBlockBytes)[(((kb0 + j) >> p.kbpg_shift) - g0) * kTcTileN + row];
+          const uint32_t z2 = __byte_perm(szw, 0, 0x1010), s2 = __byte_perm(szw, 0, 0x3232);
+          const uint32_t words[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+          uint32_t r[32];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) {
+          for (int jj = 0; jj < 8; ++jj) {
 #pragma unroll
-          for (int s = 0; s < 4; ++s)
-            r[jj * 4 + s] = bf16x2_mul(
-                bf16x2_sub(lop3_and_or(words[jj] >> (4 * s), 0x000f000fu, kBf16Magic), z2), s2);
+            for (int s = 0; s < 4; ++s)
+              r[jj * 4 + s] = bf16x2_mul(
+                  bf16x2_sub(lop3_and_or(words[jj] >> (4 * s), 0x000f000fu, kBf16Magic), z2), s2);
+          }
+          if (j == 0) {
+            mbar_wait(&hdr->a_empty[agrp], aphase ^ 1, abort_flag, p.status, 17);
+            tc_fence_after_sync();
+          }
+          if (!(p.debug & 4)) {
+            tmem_st_x32(lane_addr + kACol0 + agrp * (p.kbs * 32) + j * 32, r);
+          } else if (r[3] == 0x12345u) {
+            p.status[1] = 1;
+          }
         }
-        mbar_wait(&hdr->a_empty[agrp], aphase ^ 1, abort_flag, p.status, 17);
-        tc_fence_after_sync();
-        if (!(p.debug & 4)) {
-          tmem_st_x32(lane_addr + kACol0 + agrp * (p.kbs * 32) + j * 32, r);
-          tc_wait_st();
-        } else if (r[3] == 0x12345u) {
-          p.status[1] = 1;
-        }
+        if (!(p.debug & 4)) tc_wait_st();
         tc_fence_before_sync();
-      }
-      __syncwarp();
-      if (lane == 0) {
-        if (!(p.debug & 32)) mbar_arrive(&hdr->a_full[agrp]);
-        mbar_arrive(&hdr->w_empty[slot]);
+        __syncwarp();
+        if (lane == 0) {
+          if (!(p.debug & 32)) mbar_arrive(&hdr->a_full[agrp]);
+          mbar_arrive(&hdr->w_empty[slot]);
+        }
       }
       ++stage_no;
 
@@ -465,18 +492,23 @@ int tc_pick_grid(int tiles, int kb_per_tile, int num_sms) {
 }
 
 cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream) {
-  // k-blocks per stage: enough bytes in flight for small token counts, one x tile otherwise
-  p.kbs = p.n_tok <= 32 ? 4 : (p.n_tok <= 64 ? 2 : 1);
+  // k-blocks per stage: enough bytes in flight for small token counts, one x tile otherwise.
+  // The A groups in TMEM (8 / kbs of them) and the stages both go round-robin, groups over
+  // 4 or 8 and stages over the 4 warpgroups, so every A group has one owning warpgroup, which
+  // therefore sees every phase of that group's mbarriers (a parity wait cannot skip a phase).
+  p.kbs = p.n_tok <= 64 ? 2 : 1;
   const int x_stage = p.kbs * p.n_tok * 128;
   const int w_stage = p.kbs * kTcBlockBytes + (p.kbs + 1) * 512;
-  const int budget = 200 * 1024;
+  const int budget = 224 * 1024;
   int stages = (budget - kTcHeaderBytes) / (x_stage + w_stage);
   if (stages > kMaxTcStages) stages = kMaxTcStages;
   if (const char* e = getenv("WOQ_B200_TC_STAGES")) {
     const int want = atoi(e);
-    if (want >= 2 && want <= stages) stages = want;
+    if (want >= 4 && want <= stages) stages = want;
   }
-  if (stages < 2) return cudaErrorInvalidConfiguration;
+  // A warpgroup works on every fourth stage.  With fewer than four pipeline slots it could
+  // reach a slot two uses ahead of the producer, and a parity wait cannot tell those apart.
+  if (stages < 4) return cudaErrorInvalidConfiguration;
   p.stages = stages;
   if (const char* e = getenv("WOQ_B200_DEBUG")) p.debug = atoi(e);
   const size_t smem = kTcHeaderBytes + static_cast<size_t>(stages) * (x_stage + w_stage);

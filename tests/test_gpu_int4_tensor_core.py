@@ -61,6 +61,20 @@ def test_config1_single_linear(capi, m):
     check(y, oracle_y(layer, x))
 
 
+@pytest.mark.parametrize("m", [24, 64, 128, 256])
+def test_many_pipeline_stages_per_cta(capi, m):
+    """A long K and few tiles give every CTA dozens of pipeline stages, several tile segments and
+    partial tiles at both ends: every shared-memory slot and every TMEM operand group is
+    reused many times (mbarrier phases wrap)."""
+    layer = make_int4_layer(1152, 16384, 128, seed=4242)
+    ctx = make_ctx(capi, layer, flags=capi.LAYOUT_TC_ONLY)
+    x = make_acts(m, 16384, seed=m)
+    for _ in range(2):
+        y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda")))
+    ctx.workspace(m).status()
+    check(y, oracle_y(layer, x))
+
+
 @pytest.mark.parametrize("m", [2, 17, 64, 129])
 @pytest.mark.parametrize("n,k,g", [(64, 64, 64), (200, 320, 64), (768, 1536, 128), (96, 3584, 128),
                                    (1280, 1024, -1), (320, 2048, 512)])
