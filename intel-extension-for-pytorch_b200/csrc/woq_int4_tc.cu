@@ -13,8 +13,10 @@
 //               reference's tile dequantiser) and the 32 packed registers go straight to
 //               TMEM with one tcgen05.st - the dequantised tile never touches shared memory.
 //               Consecutive stages go round-robin to the four warpgroups;
-//   warp 17     one thread issues tcgen05.mma (A from TMEM, B from shared memory) and
-//               releases A slots / x stages / the accumulator with tcgen05.commit;
+//   warps 17,19 one thread each issues tcgen05.mma (A from TMEM, B from shared memory) for
+//               alternate stages: per stage one wait (the A group is written and the x
+//               tiles have landed) and one tcgen05.commit that frees the stage's buffers and
+//               its A group together;
 //   warps 0-15  epilogue at the end of a tile segment: tcgen05.ld the accumulators, then
 //               either the fused post-op and store, or - when the CTA saw only part of K -
 //               a partial tile in the workspace that the last contributor sums in a fixed
@@ -31,8 +33,9 @@ namespace {
 
 constexpr int kDequantWarps = 16;
 constexpr int kWarpGroups = kDequantWarps / 4;
-constexpr int kTcThreads = (kDequantWarps + 3) * 32;
-constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1, kXProducerWarp = kDequantWarps + 2;
+constexpr int kTcThreads = (kDequantWarps + 4) * 32;
+constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1, kXProducerWarp = kDequantWarps + 2,
+              kMmaWarp2 = kDequantWarps + 3;
 constexpr int kASlots = 8;           // 32 TMEM columns each (one k-block of bf16 A)
 constexpr int kDCol0 = 0;            // accumulator columns [0, 256)
 constexpr int kDCols = 256;
@@ -43,9 +46,10 @@ constexpr int kMaxTcStages = 8;
 constexpr int kTcHeaderBytes = 1024;
 
 struct TcHeader {
-  uint64_t w_full[kMaxTcStages], w_empty[kMaxTcStages];
-  uint64_t x_full[kMaxTcStages], x_empty[kMaxTcStages];
-  uint64_t a_full[kASlots], a_empty[kASlots];
+  uint64_t w_full[kMaxTcStages];  // packed weights + scales of the stage have landed
+  uint64_t full[kMaxTcStages];    // A group written (4 warps) and x tiles landed (1 + bytes)
+  uint64_t free_[kMaxTcStages];   // the stage's MMAs have completed: everything may be reused
+  uint64_t issued[2];             // MMA warp t has issued the MMAs of its latest stage
   uint64_t d_full, d_empty;
   uint32_t tmem_base;
   int abort_flag;
@@ -114,15 +118,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->w_full[s], 1);
-      mbar_init(&hdr->w_empty[s], 4);
-      mbar_init(&hdr->x_full[s], 1);
-      mbar_init(&hdr->x_empty[s], 1);
+      mbar_init(&hdr->full[s], 5);
+      mbar_init(&hdr->free_[s], 1);
     }
-    for (int s = 0; s < kASlots; ++s) {
-      mbar_init(&hdr->a_full[s], 4);
-      mbar_init(&hdr->a_empty[s], 1);
-    }
-    mbar_init(&hdr->d_full, 1);
+    mbar_init(&hdr->issued[0], 1);
+    mbar_init(&hdr->issued[1], 1);
+    mbar_init(&hdr->d_full, 2);
     mbar_init(&hdr->d_empty, kDequantWarps);
     hdr->abort_flag = 0;
     hdr->is_last = 0;
@@ -139,15 +140,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   volatile int* abort_flag = &hdr->abort_flag;
 
   // every role walks the same sequence of stages; a stage is up to `kbs` k-blocks of one tile.
-  // Stage `it` uses pipeline slot it % stages and A group it % a_groups (kbs * 32 TMEM columns).
+  // Stage `it` uses pipeline slot it % stages: its shared-memory buffers and the A group (kbs *
+  // 32 TMEM columns) of the same index.
   int tile = static_cast<int>(b_begin / p.kb_per_tile);
   int kb0 = static_cast<int>(b_begin % p.kb_per_tile);
   int64_t b = b_begin;
   int slot = 0;
   uint32_t phase = 0;       // parity of the current use of `slot`
-  int agrp = 0;
-  uint32_t aphase = 0;      // parity of the current use of `agrp`
-  const int a_groups = kASlots / p.kbs;  // 2, 4 or 8
   auto stage_len = [&]() {
     int nkb = p.kb_per_tile - kb0;
     if (nkb > p.kbs) nkb = p.kbs;
@@ -165,10 +164,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       slot = 0;
       phase ^= 1;
     }
-    if (++agrp == a_groups) {
-      agrp = 0;
-      aphase ^= 1;
-    }
   };
 
   if (warp == kProducerWarp) {
@@ -181,7 +176,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const int g0 = kb0 >> p.kbpg_shift;
         const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
         tc_stamp(p, 0, pst, 0);
-        mbar_wait(&hdr->w_empty[slot], phase ^ 1, abort_flag, p.status, 11);
+        mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 11);
         tc_stamp(p, 0, pst, 1);
         mbar_arrive_expect_tx(&hdr->w_full[slot], nkb * kTcBlockBytes + ng * 512);
         bulk_g2s(ws, p.wq + (static_cast<size_t>(tile) * p.kb_per_tile + kb0) * kTcBlockBytes,
@@ -200,21 +195,25 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       while (b < b_end) {
         const int nkb = stage_len();
         uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
-        mbar_wait(&hdr->x_empty[slot], phase ^ 1, abort_flag, p.status, 12);
+        mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 12);
         if (p.debug & 8) {
-          mbar_arrive(&hdr->x_full[slot]);
+          mbar_arrive(&hdr->full[slot]);
         } else {
-          mbar_arrive_expect_tx(&hdr->x_full[slot], nkb * p.n_tok * 128);
+          mbar_arrive_expect_tx(&hdr->full[slot], nkb * p.n_tok * 128);
           for (int j = 0; j < nkb; ++j)
-            tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->x_full[slot]);
+            tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->full[slot]);
         }
         advance(nkb);
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kMmaWarp || warp == kMmaWarp2) {
     if (lane == 0) {
-      // One thread issues every MMA of the CTA, so this loop is kept free of divisions and
-      // address recomputation: descriptors advance by constants.
+      // Two threads issue the MMAs, one the even stages and one the odd ones.  Issuing an MMA
+      // blocks the thread while the tensor core is busy, and the waits and commits around a
+      // stage cost about as much again; with two threads one of them has always finished its
+      // wait when the other has issued its last MMA.  A token (`issued`) keeps the stages in
+      // order, so the MMA that starts a tile's accumulator runs before any that adds to it.
+      const int me = warp == kMmaWarp ? 0 : 1;
       const uint32_t idesc = umma_idesc(p.n_tok, /*bf16*/ 1, /*f32*/ 1);
       const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
       const uint32_t x_base_lo = (smem_u32(x_stages) & 0x3FFFFu) >> 4;
@@ -222,43 +221,47 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       const uint32_t x_blk_lo = static_cast<uint32_t>(p.n_tok * 128) >> 4;
       const uint32_t d_addr = tmem_base + kDCol0;
       uint32_t seg = 0;
-      uint32_t accumulate = 0;
-      int mst = 0;
+      bool first_of_segment = true;
+      int mst = 0;  // stage number within this CTA
       while (b < b_end) {
         const int nkb = stage_len();
         const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
-        tc_stamp(p, 1, mst, 0);
-        mbar_wait(&hdr->x_full[slot], phase, abort_flag, p.status, 13);
-        tc_stamp(p, 1, mst, 1);
-        if (!(p.debug & 32)) mbar_wait(&hdr->a_full[agrp], aphase, abort_flag, p.status, 14);
-        tc_stamp(p, 1, mst, 2);
-        if (!accumulate) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 15);
-        tc_fence_after_sync();
-        uint32_t a_addr = tmem_base + kACol0 + agrp * (p.kbs * 32);
-        uint32_t b_lo = x_base_lo + slot * x_stage_lo;
-        for (int j = 0; j < nkb; ++j) {
+        if ((mst & 1) == me) {
+          if (me == 0) tc_stamp(p, 1, mst, 0);
+          mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 13);
+          if (me == 0) tc_stamp(p, 1, mst, 1);
+          if (first_of_segment) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 15);
+          // the previous stage's MMAs have been issued (by the other thread)
+          if (mst > 0) mbar_wait(&hdr->issued[me ^ 1], ((mst - 1) >> 1) & 1, abort_flag, p.status, 14);
+          if (me == 0) tc_stamp(p, 1, mst, 2);
+          tc_fence_after_sync();
+          uint32_t accumulate = first_of_segment ? 0u : 1u;
+          uint32_t a_addr = tmem_base + kACol0 + slot * (p.kbs * 32);
+          uint32_t b_lo = x_base_lo + slot * x_stage_lo;
+          for (int j = 0; j < nkb; ++j) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            if (!(p.debug & 2))
-              umma_f16_ts(d_addr, a_addr + ks * 8, desc_hi | (b_lo + ks * 2), idesc, accumulate);
-            accumulate = 1;
+            for (int ks = 0; ks < 4; ++ks) {
+              if (!(p.debug & 2))
+                umma_f16_ts(d_addr, a_addr + ks * 8, desc_hi | (b_lo + ks * 2), idesc, accumulate);
+              accumulate = 1;
+            }
+            a_addr += 32;
+            b_lo += x_blk_lo;
           }
-          a_addr += 32;
-          b_lo += x_blk_lo;
+          mbar_arrive(&hdr->issued[me]);
+          if (p.debug & 16)
+            mbar_arrive(&hdr->free_[slot]);
+          else
+            tc_commit(&hdr->free_[slot]);
+          if (me == 0) tc_stamp(p, 1, mst, 3);
         }
-        if (p.debug & 16) {
-          if (!(p.debug & 32)) mbar_arrive(&hdr->a_empty[agrp]);
-          mbar_arrive(&hdr->x_empty[slot]);
-        } else {
-          tc_commit(&hdr->a_empty[agrp]);
-          tc_commit(&hdr->x_empty[slot]);
-        }
+        first_of_segment = false;
         if (seg_end) {
+          // both threads: everything this thread issued for the segment is tracked
           tc_commit(&hdr->d_full);
           ++seg;
-          accumulate = 0;
+          first_of_segment = true;
         }
-        tc_stamp(p, 1, mst, 3);
         ++mst;
         advance(nkb);
       }
@@ -367,11 +370,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                   bf16x2_sub(lop3_and_or(words[jj] >> (4 * s), 0x000f000fu, kBf16Magic), z2), s2);
           }
           if (j == 0) {
-            mbar_wait(&hdr->a_empty[agrp], aphase ^ 1, abort_flag, p.status, 17);
+            if (tid == 0) tc_stamp(p, 2, stage_no, 2);
+            mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 17);
             tc_fence_after_sync();
+            if (tid == 0) tc_stamp(p, 2, stage_no, 3);
           }
           if (!(p.debug & 4)) {
-            tmem_st_x32(lane_addr + kACol0 + agrp * (p.kbs * 32) + j * 32, r);
+            tmem_st_x32(lane_addr + kACol0 + slot * (p.kbs * 32) + j * 32, r);
           } else if (r[3] == 0x12345u) {
             p.status[1] = 1;
           }
@@ -379,10 +384,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         if (!(p.debug & 4)) tc_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) {
-          if (!(p.debug & 32)) mbar_arrive(&hdr->a_full[agrp]);
-          mbar_arrive(&hdr->w_empty[slot]);
-        }
+        if (lane == 0) mbar_arrive(&hdr->full[slot]);
+        if (tid == 0) tc_stamp(p, 0, stage_no, 3);
       }
       ++stage_no;
 
@@ -492,22 +495,20 @@ int tc_pick_grid(int tiles, int kb_per_tile, int num_sms) {
 }
 
 cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream) {
-  // k-blocks per stage: enough bytes in flight for small token counts, one x tile otherwise.
-  // The A groups in TMEM (8 / kbs of them) and the stages both go round-robin, groups over
-  // 4 or 8 and stages over the 4 warpgroups, so every A group has one owning warpgroup, which
-  // therefore sees every phase of that group's mbarriers (a parity wait cannot skip a phase).
+  // k-blocks per stage: enough bytes in flight for small token counts, one x tile otherwise
   p.kbs = p.n_tok <= 64 ? 2 : 1;
   const int x_stage = p.kbs * p.n_tok * 128;
   const int w_stage = p.kbs * kTcBlockBytes + (p.kbs + 1) * 512;
   const int budget = 224 * 1024;
   int stages = (budget - kTcHeaderBytes) / (x_stage + w_stage);
-  if (stages > kMaxTcStages) stages = kMaxTcStages;
+  if (stages > kASlots / p.kbs) stages = kASlots / p.kbs;  // one A group in TMEM per slot
   if (const char* e = getenv("WOQ_B200_TC_STAGES")) {
     const int want = atoi(e);
     if (want >= 4 && want <= stages) stages = want;
   }
   // A warpgroup works on every fourth stage.  With fewer than four pipeline slots it could
-  // reach a slot two uses ahead of the producer, and a parity wait cannot tell those apart.
+  // reach a slot two uses ahead of the producer or of the MMA warp, and a parity wait cannot
+  // tell those apart.
   if (stages < 4) return cudaErrorInvalidConfiguration;
   p.stages = stages;
   if (const char* e = getenv("WOQ_B200_DEBUG")) p.debug = atoi(e);
