@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(256) quant_act_sym_kernel(const __nv_bfloat16*
 }
 
 // ---- tcgen05 int8 GEMM -------------------------------------------------------------------
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 16;  // four warpgroups; warp w reads TMEM lanes 32 * (w % 4) ...
 constexpr int kI8Threads = (kEpiWarps + 2) * 32;
 constexpr int kI8Producer = kEpiWarps, kI8Mma = kEpiWarps + 1;
 constexpr int kI8MaxStages = 8;
@@ -263,9 +263,11 @@ __global__ void __launch_bounds__(kI8Threads, 1)
     }
   } else {
     // ------------------------------- epilogue warps ----------------------------------------
-    const int row = warp * 32 + lane;
-    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const int n_chunks = p.n_tok / 8;
+    const int wg = warp >> 2, q = warp & 3;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const int n_chunks = p.n_tok / 8;  // 8-token column chunks, dealt round-robin to warpgroups
+    constexpr int kGroups = kEpiWarps / 4;
     int seg = 0, seg_kc0 = kc;
     bool first_segment = true;
     int pend_tile = -1;
@@ -276,32 +278,49 @@ __global__ void __launch_bounds__(kI8Threads, 1)
       const int64_t tb0 = static_cast<int64_t>(t) * p.kc_per_tile;
       const int c_first = i8_owner_of(tb0, total, gridDim.x);
       const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
-      for (int tok = 0; tok < p.m; ++tok) {
-        int v = 0, v_up = 0;
+      for (int ch = wg; ch < n_chunks && ch * 8 < p.m; ch += kGroups) {
+        // eight tokens at a time, all their loads in flight together
+        int v[8], v_up[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = v_up[e] = 0;
         for (int cc = c_first; cc <= c_last; ++cc) {
           const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
           const int slot2 = whole ? own_slot : cc * 2 + (cb >= tb0 ? 0 : 1);
           const int* src = partials + static_cast<size_t>(slot2) * p.n_tok * kTcTileN +
-                           static_cast<size_t>(tok) * kTcTileN;
-          v += __ldcg(src + row);
-          if (p.fusion == FUSE_SILU_MUL && row < 64) v_up += __ldcg(src + row + 64);
-        }
-        if (p.fusion == FUSE_SILU_MUL) {
-          if (row < 64) {
-            const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
-            if (n_gate < p.n_out) {
-              float g = (static_cast<float>(v) * p.sa[tok]) * p.sw[n_gate];
-              float u = (static_cast<float>(v_up) * p.sa[tok]) * p.sw[n_up];
-              if (p.bias) {
-                g = p.bias[n_gate] + g;
-                u = p.bias[n_up] + u;
-              }
-              p.y[static_cast<size_t>(tok) * p.ldy + n_gate] =
-                  __float2bfloat16_rn(bf16_round(u) * silu_bf16(bf16_round(g)));
-            }
+                           static_cast<size_t>(ch * 8) * kTcTileN + row;
+          int part[8], part_up[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            part[e] = __ldcg(src + e * kTcTileN);
+            part_up[e] = (p.fusion == FUSE_SILU_MUL && row < 64) ? __ldcg(src + e * kTcTileN + 64) : 0;
           }
-        } else {
-          i8_store(p, t, row, tok, v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            v[e] += part[e];
+            v_up[e] += part_up[e];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int tok = ch * 8 + e;
+          if (tok >= p.m) break;
+          if (p.fusion == FUSE_SILU_MUL) {
+            if (row < 64) {
+              const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
+              if (n_gate < p.n_out) {
+                float g = (static_cast<float>(v[e]) * p.sa[tok]) * p.sw[n_gate];
+                float u = (static_cast<float>(v_up[e]) * p.sa[tok]) * p.sw[n_up];
+                if (p.bias) {
+                  g = p.bias[n_gate] + g;
+                  u = p.bias[n_up] + u;
+                }
+                p.y[static_cast<size_t>(tok) * p.ldy + n_gate] =
+                    __float2bfloat16_rn(bf16_round(u) * silu_bf16(bf16_round(g)));
+              }
+            }
+          } else {
+            i8_store(p, t, row, tok, v[e]);
+          }
         }
       }
     };
@@ -313,7 +332,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
         mbar_wait(&hdr->d_full, seg & 1, abort_flag, p.status, 24);
         tc_fence_after_sync();
         if (whole && p.fusion != FUSE_SILU_MUL) {
-          for (int ch = 0; ch < n_chunks; ++ch) {
+          for (int ch = wg; ch < n_chunks; ch += kGroups) {
             uint32_t v[8];
             tmem_ld_x8(lane_addr + ch * 8, v);
             tc_wait_ld();
@@ -335,7 +354,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
         } else {
           const int my_slot = blockIdx.x * 2 + (first_segment ? 0 : 1);
           int* dst = partials + static_cast<size_t>(my_slot) * p.n_tok * kTcTileN;
-          for (int ch = 0; ch < n_chunks; ++ch) {
+          for (int ch = wg; ch < n_chunks; ch += kGroups) {
             uint32_t v[8];
             tmem_ld_x8(lane_addr + ch * 8, v);
             tc_wait_ld();
@@ -378,7 +397,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
                 const int c_first = i8_owner_of(tb0, total, gridDim.x);
                 const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
                 const int n = tc_tile_row_to_n(p.n, p.gate_up, tile, row);
-                for (int tok = 0; tok < p.m && n < p.n; ++tok) {
+                for (int tok = wg; tok < p.m && n < p.n; tok += kGroups) {
                   int v = 0;
                   for (int cc = c_first; cc <= c_last; ++cc) {
                     const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
@@ -417,7 +436,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
           const int c_first = i8_owner_of(tb0, total, gridDim.x);
           const int c_last = i8_owner_of(tb0 + p.kc_per_tile - 1, total, gridDim.x);
           const int n = tc_tile_row_to_n(p.n, p.gate_up, pend_tile, row);
-          for (int tok = 0; tok < p.m && n < p.n; ++tok) {
+          for (int tok = wg; tok < p.m && n < p.n; tok += kGroups) {
             int v = 0;
             for (int cc = c_first; cc <= c_last; ++cc) {
               const int64_t cb = (static_cast<int64_t>(cc) * total) / gridDim.x;
