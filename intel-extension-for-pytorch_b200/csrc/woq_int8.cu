@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(256) quant_act_sym_kernel(const __nv_bfloat16*
 
 // ---- tcgen05 int8 GEMM -------------------------------------------------------------------
 constexpr int kEpiWarps = 16;  // four warpgroups; warp w reads TMEM lanes 32 * (w % 4) ...
-constexpr int kI8Threads = (kEpiWarps + 2) * 32;
-constexpr int kI8Producer = kEpiWarps, kI8Mma = kEpiWarps + 1;
+constexpr int kI8Threads = (kEpiWarps + 3) * 32;
+constexpr int kI8Producer = kEpiWarps, kI8Mma = kEpiWarps + 1, kI8Mma2 = kEpiWarps + 2;
 constexpr int kI8MaxStages = 8;
 constexpr int kI8HeaderBytes = 1024;
 constexpr int kI8TmemCols = 256;
@@ -134,6 +134,7 @@ constexpr int kChunkBytes = 16384;  // 128 rows x 128 k
 
 struct I8Header {
   uint64_t full[kI8MaxStages], empty[kI8MaxStages];
+  uint64_t issued[2];  // MMA warp t has issued the MMAs of its latest k-chunk
   uint64_t d_full, d_empty;
   uint32_t tmem_base;
   int abort_flag;
@@ -185,7 +186,9 @@ __global__ void __launch_bounds__(kI8Threads, 1)
       mbar_init(&hdr->full[s], 1);
       mbar_init(&hdr->empty[s], 1);
     }
-    mbar_init(&hdr->d_full, 1);
+    mbar_init(&hdr->issued[0], 1);
+    mbar_init(&hdr->issued[1], 1);
+    mbar_init(&hdr->d_full, 2);
     mbar_init(&hdr->d_empty, kEpiWarps);
     hdr->abort_flag = 0;
     hdr->is_last = 0;
@@ -233,31 +236,45 @@ __global__ void __launch_bounds__(kI8Threads, 1)
         advance();
       }
     }
-  } else if (warp == kI8Mma) {
+  } else if (warp == kI8Mma || warp == kI8Mma2) {
     if (lane == 0) {
+      // Two threads issue the MMAs of alternate k-chunks: issuing blocks a thread while the
+      // tensor core is busy, and the wait and commit around a chunk cost about as much again.
+      // A token (`issued`) keeps the chunks in order, so the MMA that starts a tile's
+      // accumulator runs before any that adds to it.
+      const int me = warp == kI8Mma ? 0 : 1;
       const uint32_t idesc = umma_idesc(p.n_tok, /*s8*/ 1, /*s32*/ 2);
       const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
       const uint32_t base_lo = (smem_u32(stages) & 0x3FFFFu) >> 4;
       const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
-      uint32_t seg = 0, accumulate = 0;
+      uint32_t seg = 0;
+      bool first_of_segment = true;
+      int n = 0;  // chunk number within this CTA
       while (b < b_end) {
         const bool seg_end = (kc + 1 == p.kc_per_tile) || (b + 1 == b_end);
-        mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 22);
-        if (!accumulate) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 23);
-        tc_fence_after_sync();
-        const uint32_t a_lo = base_lo + slot * stage_lo;
-        const uint32_t b_lo = a_lo + (kChunkBytes >> 4);
+        if ((n & 1) == me) {
+          mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 22);
+          if (first_of_segment) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 23);
+          if (n > 0) mbar_wait(&hdr->issued[me ^ 1], ((n - 1) >> 1) & 1, abort_flag, p.status, 25);
+          tc_fence_after_sync();
+          uint32_t accumulate = first_of_segment ? 0u : 1u;
+          const uint32_t a_lo = base_lo + slot * stage_lo;
+          const uint32_t b_lo = a_lo + (kChunkBytes >> 4);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          umma_i8_ss(tmem_base, desc_hi | (a_lo + ks * 2), desc_hi | (b_lo + ks * 2), idesc, accumulate);
-          accumulate = 1;
+          for (int ks = 0; ks < 4; ++ks) {
+            umma_i8_ss(tmem_base, desc_hi | (a_lo + ks * 2), desc_hi | (b_lo + ks * 2), idesc, accumulate);
+            accumulate = 1;
+          }
+          mbar_arrive(&hdr->issued[me]);
+          tc_commit(&hdr->empty[slot]);
         }
-        tc_commit(&hdr->empty[slot]);
+        first_of_segment = false;
         if (seg_end) {
-          tc_commit(&hdr->d_full);
+          tc_commit(&hdr->d_full);  // both threads: all this thread issued for the segment
           ++seg;
-          accumulate = 0;
+          first_of_segment = true;
         }
+        ++n;
         advance();
       }
     }
