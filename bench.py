@@ -32,6 +32,11 @@ for _p in (ROOT, PKG_DIR):
 
 HIDDEN, QKV_N, FFN, LAYERS, GROUP = 8192, 10240, 28672, 80, 128
 METRIC = "int4_woq_linear_weight_GBps_decode"
+# DRAM bytes (read + write) per algorithmic byte of the decode kernel, from the ncu capture
+# summarised in profiles/decode_int4_57344x8192_m1.md (the device keeps 4 bytes of scale and
+# zero point per row and group against 3 algorithmic ones, and split-K partial tiles are
+# written and read back); the traffic of a launch grows in proportion to its bytes.
+TRAFFIC_RATIO = 1.032
 UNIT = "GB/s"
 
 
@@ -365,7 +370,8 @@ def run_ours(args):
     hbm_peak, _, peak_src = peaks()
     achieved = local_bytes / n_launch / (kernel_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak, "traffic": args.traffic,
+                "frac": achieved / hbm_peak,
+                "traffic": args.traffic if args.traffic is not None else TRAFFIC_RATIO * local_bytes / n_launch,
                 "kernel": "woq_int4_decode_kernel", "peak_source": peak_src,
                 "avg_launch_us": kernel_ms * 1e3,
                 "algorithmic_bytes_per_launch": local_bytes / n_launch}
@@ -395,6 +401,39 @@ def run_ours(args):
     e2e = {"value": total_w / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": m * HIDDEN * 2,
            "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": e2e_s * 1e3}
 
+    # ---- prefill side of the metric: the tcgen05 kernel on one gate_up-sized layer ----------
+    prefill = None
+    if p == 1 and not args.no_prefill:
+        pm = 512
+        g = torch.Generator(device=device).manual_seed(4242)
+        w = torch.randn((2 * FFN, HIDDEN), device=device, generator=g) * 0.02
+        qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
+        del w
+        pctx = [capi.WoqContext(qw, s.half(), z, None, 2 * FFN, HIDDEN, capi.DTYPE_INT4, GROUP, capi.LOWP_BF16,
+                                layout_flags=capi.LAYOUT_TC_ONLY) for _ in range(2)]
+        del qw, s, z
+        px = torch.randn((pm, HIDDEN), **bf)
+        py = torch.empty((pm, 2 * FFN), **bf)
+        pws = capi.Workspace(pctx[0].workspace_bytes(pm), device)
+        for c in pctx:
+            c.linear(px, out=py, workspace=pws)
+        torch.cuda.synchronize()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        preps = 6
+        p0.record()
+        for i in range(preps):
+            pctx[i % 2].linear(px, out=py, workspace=pws)
+        p1.record()
+        torch.cuda.synchronize()
+        pws.status()
+        pt = p0.elapsed_time(p1) * 1e-3 / preps
+        _, tf_peak, _ = peaks()
+        tflops = 2.0 * pm * 2 * FFN * HIDDEN / pt / 1e12
+        prefill = {"tflops": tflops, "m": pm, "shape": f"{2 * FFN}x{HIDDEN} INT4 g128", "us_per_linear": pt * 1e6,
+                   "kernel": "woq_int4_tc_kernel", "bound": "tensor", "peak": tf_peak, "unit": "TFLOP/s",
+                   "frac": tflops / tf_peak if tf_peak else None}
+        del pctx, px, py, pws
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": p, "steps": args.steps,
@@ -407,7 +446,7 @@ def run_ours(args):
                                       if fused else "nccl"),
                        "l2": "weights (35.8 GB per step over all ranks) exceed L2; no flush needed",
                        "cuda_graph": graph is not None},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": n_launch * args.steps,
+            "roofline": roofline, "prefill": prefill, "e2e": e2e, "gpu_launches": n_launch * args.steps,
             "clocks": clocks,
         }
         if p == 1 and not args.no_cpu_baseline:
@@ -478,11 +517,12 @@ def main():
     ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
                     help="N > 1: exchange inside the linear kernels, or NCCL after them")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (tensor-core kernel) side line")
     ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
     ap.add_argument("--int8", action="store_true", help="--single: INT8 weights with INT8 compute")
     ap.add_argument("--hint", type=int, default=0, help="--single: kernel hint (see include/woq_b200.h)")
     ap.add_argument("--traffic", type=float, default=None,
-                    help="DRAM bytes per launch from an ncu capture (profiles/)")
+                    help="DRAM bytes per launch from an ncu capture (default: TRAFFIC_RATIO x algorithmic bytes)")
     args = ap.parse_args()
     if args.single:
         run_single(args)
