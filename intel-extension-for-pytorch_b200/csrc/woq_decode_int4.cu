@@ -157,7 +157,9 @@ struct StageIter {
   }
 };
 
-template <int TB, int MODE, int KPW>
+// COMM: compiled with the tensor-parallel exchange in the epilogue (the plain variant carries
+// none of its code or registers).
+template <int TB, int MODE, int KPW, bool COMM>
 __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
     woq_int4_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -206,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
   // arrive, reduces the tile in a fixed order.
   uint32_t epoch = 0;  // read by the warps that run epilogues, once the previous grid is done
   auto run_epilogue = [&](int tl, float* a0, float* a1) {
-    if (p.comm.mode == kCommAllReduce) {
+    if (COMM && p.comm.mode == kCommAllReduce) {
       // Row-parallel linear: every rank's bf16 partial of this tile goes to every rank; each
       // rank then adds them in rank order (fp32) and rounds once, so all ranks hold the same
       // bits; bias and post-op follow the reduction.
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
         out[tok] = decode_epilogue(p, tl, lane, tok, a0[tok]) |
                    (decode_epilogue(p, tl, lane + 32, tok, a1[tok]) << 16);
     }
-    if (p.comm.mode == kCommAllGather) {
+    if (COMM && p.comm.mode == kCommAllGather) {
       // Column-parallel linear: p.y is this rank's column block of the gathered tensor.  The
       // tile also goes to every other rank, and the same tile of every other rank is copied
       // from this rank's slots into its column block here, so that the gathered tensor is
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
   // Both epilogue-running warps call this when they are done; the second one of the last CTA
   // of the grid closes the epoch.
   auto finish_comm = [&]() {
-    if (p.comm.mode == kCommNone) return;
+    if (!COMM || p.comm.mode == kCommNone) return;
     int second = 0;
     if (lane == 0) second = atomicAdd(&hdr->finished_warps, 1);
     if (!__shfl_sync(0xffffffffu, second, 0)) return;
@@ -423,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
           fill.next(fill.nkb());
         }
       grid_dependency_wait();
-      if (p.comm.mode != kCommNone)
+      if (COMM && p.comm.mode != kCommNone)
         epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
       __syncwarp();
       for (int s = 0; s < p.stages && !it.done(); ++s) {
@@ -470,7 +472,7 @@ __global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
     int pend_tile = -1;
     unsigned pend_old = 0;
     grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
-    if (p.comm.mode != kCommNone)
+    if (COMM && p.comm.mode != kCommNone)
       epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
     for (int sg = 0; sg + 1 < nseg; ++sg) {
       take_segment(kBarRedFull, true, tile0 + sg, sg > 0 || kb00 == 0, sg == 0, v0, v1, pend_tile,
@@ -693,13 +695,17 @@ int env_int(const char* name, int fallback) {
 // for three 32 KB stages
 int pick_kpw(int m) { return env_int("WOQ_B200_KPW", m <= 4 ? 2 : 1) == 2 && m <= 8 ? 2 : 1; }
 
-template <int TB, int KPW>
-void (*pick_kernel(int mode))(const DecodeParams) {
+template <int TB, int KPW, bool COMM>
+void (*pick_kernel_mode(int mode))(const DecodeParams) {
   switch (mode) {
-    case kScaleAfterSum: return woq_int4_decode_kernel<TB, kScaleAfterSum, KPW>;
-    case kExactShift: return woq_int4_decode_kernel<TB, kExactShift, KPW>;
-    default: return woq_int4_decode_kernel<TB, kExactInPlace, KPW>;
+    case kScaleAfterSum: return woq_int4_decode_kernel<TB, kScaleAfterSum, KPW, COMM>;
+    case kExactShift: return woq_int4_decode_kernel<TB, kExactShift, KPW, COMM>;
+    default: return woq_int4_decode_kernel<TB, kExactInPlace, KPW, COMM>;
   }
+}
+template <int TB, int KPW>
+void (*pick_kernel(int mode, bool comm))(const DecodeParams) {
+  return comm ? pick_kernel_mode<TB, KPW, true>(mode) : pick_kernel_mode<TB, KPW, false>(mode);
 }
 
 }  // namespace
@@ -729,8 +735,9 @@ cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
   p.stages = stages;
   const size_t smem = kHeaderBytes + static_cast<size_t>(stages) * stage_bytes + red_bytes;
   const int mode = env_int("WOQ_B200_DEQUANT_MODE", p.exact);
+  const bool comm = p.comm.mode != kCommNone;
   void (*kern)(const DecodeParams) =
-      tb == 2 ? pick_kernel<2, 1>(mode) : kpw == 2 ? pick_kernel<1, 2>(mode) : pick_kernel<1, 1>(mode);
+      tb == 2 ? pick_kernel<2, 1>(mode, comm) : kpw == 2 ? pick_kernel<1, 2>(mode, comm) : pick_kernel<1, 1>(mode, comm);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
