@@ -693,7 +693,20 @@ int env_int(const char* name, int fallback) {
 
 // consumer warps take two adjacent k-blocks per stage while x is small enough to leave room
 // for three 32 KB stages
-int pick_kpw(int m) { return env_int("WOQ_B200_KPW", m <= 4 ? 2 : 1) == 2 && m <= 8 ? 2 : 1; }
+// bytes of one pipeline stage / of the cross-warp reduction buffer
+int stage_bytes_for(int m, int kpw, int kbpg_shift) {
+  const int gps = (stage_kblocks(kpw) >> kbpg_shift) + 1;
+  return stage_kblocks(kpw) * kBlockBytes + (gps + 1) * 256 + m * x_row_bytes(kpw);
+}
+int red_bytes_for(int m) { return kConsumerWarps * ((m + 1) & ~1) * kRedTokStride * 4; }
+constexpr int kBudgetTwoCtas = 112 * 1024, kBudgetOneCta = 224 * 1024;
+
+// two k-blocks per warp and stage while two such stages fit beside the x rows (1..6 tokens)
+int pick_kpw(int m, int kbpg_shift) {
+  if (m > 8) return 1;
+  const int fits = (kBudgetTwoCtas - kHeaderBytes - red_bytes_for(m)) / stage_bytes_for(m, 2, kbpg_shift) >= 2;
+  return env_int("WOQ_B200_KPW", fits ? 2 : 1) == 2 && fits ? 2 : 1;
+}
 
 template <int TB, int KPW, bool COMM>
 void (*pick_kernel_mode(int mode))(const DecodeParams) {
@@ -713,19 +726,21 @@ void (*pick_kernel(int mode, bool comm))(const DecodeParams) {
 int decode_int4_unit(int m, int kb_per_group) {
   // shares are dealt in pairs of k-blocks when a warp takes two, so that a pair never
   // straddles two groups
-  return pick_kpw(m) == 2 && kb_per_group % 2 == 0 ? 2 : 1;
+  int shift = 0;
+  while ((1 << (shift + 1)) <= kb_per_group && shift < 30) ++shift;
+  return pick_kpw(m, shift) == 2 && kb_per_group % 2 == 0 ? 2 : 1;
 }
 
 cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
   const int tb = p.m <= 8 ? 1 : 2;
-  const int kpw = pick_kpw(p.m);
+  const int kpw = pick_kpw(p.m, p.kbpg_shift > 30 ? 30 : p.kbpg_shift);
   p.x_rows = p.m;
   p.red_tok = (p.m + 1) & ~1;
   const int skb = stage_kblocks(kpw);
   p.gps = (skb >> p.kbpg_shift) + 1;  // groups a stage can touch
   const int stage_bytes = skb * kBlockBytes + (p.gps + 1) * 256 + p.x_rows * x_row_bytes(kpw);
   const int red_bytes = kConsumerWarps * p.red_tok * kRedTokStride * 4;
-  const int budget = (tb == 1 ? 112 : 224) * 1024;
+  const int budget = tb == 1 ? kBudgetTwoCtas : kBudgetOneCta;
   int stages = (budget - kHeaderBytes - red_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   const int want = env_int("WOQ_B200_STAGES", 0);
