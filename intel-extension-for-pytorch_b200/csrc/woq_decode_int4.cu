@@ -1,7 +1,7 @@
 // INT4 weight-only-quantised skinny GEMM for M <= 16 tokens ("decode"): an HBM-bound stream
 // of packed weights.
 //
-// Persistent kernel, two CTAs per SM (one for 9..16 tokens), ten warps each.  The weight is a
+// Persistent kernel, two CTAs per SM, ten warps each.  The weight is a
 // linear sequence of k-blocks (64 rows x 64 k, 2 KB each, tile-major); CTA c owns an equal
 // contiguous share, cut at tile boundaries into "segments".
 //   * The producer warp moves 8 or 16 k-blocks of one tile per pipeline stage (weights, their
@@ -160,7 +160,7 @@ struct StageIter {
 // COMM: compiled with the tensor-parallel exchange in the epilogue (the plain variant carries
 // none of its code or registers).
 template <int TB, int MODE, int KPW, bool COMM>
-__global__ void __launch_bounds__(kThreads, TB == 1 ? 2 : 1)
+__global__ void __launch_bounds__(kThreads, 2)
     woq_int4_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
@@ -677,8 +677,8 @@ size_t decode_int4_partial_bytes(int grid) { return static_cast<size_t>(grid) * 
 
 int decode_int4_pick_grid(const DecodeShape& s, int num_sms) {
   const int64_t total = static_cast<int64_t>(s.tiles) * s.kb_per_tile / s.unit;
-  int per_sm = s.m <= 8 ? 2 : 1;
-  if (const char* e = getenv("WOQ_B200_GRID_PER_SM")) per_sm = atoi(e) > 1 && s.m <= 8 ? 2 : 1;
+  int per_sm = 2;
+  if (const char* e = getenv("WOQ_B200_GRID_PER_SM")) per_sm = atoi(e) > 1 ? 2 : 1;
   int64_t grid = static_cast<int64_t>(num_sms) * per_sm;
   if (grid > total) grid = total;
   return static_cast<int>(grid < 1 ? 1 : grid);
@@ -699,7 +699,7 @@ int stage_bytes_for(int m, int kpw, int kbpg_shift) {
   return stage_kblocks(kpw) * kBlockBytes + (gps + 1) * 256 + m * x_row_bytes(kpw);
 }
 int red_bytes_for(int m) { return kConsumerWarps * ((m + 1) & ~1) * kRedTokStride * 4; }
-constexpr int kBudgetTwoCtas = 112 * 1024, kBudgetOneCta = 224 * 1024;
+constexpr int kBudgetTwoCtas = 112 * 1024;  // shared memory of one CTA
 
 // two k-blocks per warp and stage while two such stages fit beside the x rows (1..6 tokens)
 int pick_kpw(int m, int kbpg_shift) {
@@ -740,7 +740,7 @@ cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
   p.gps = (skb >> p.kbpg_shift) + 1;  // groups a stage can touch
   const int stage_bytes = skb * kBlockBytes + (p.gps + 1) * 256 + p.x_rows * x_row_bytes(kpw);
   const int red_bytes = kConsumerWarps * p.red_tok * kRedTokStride * 4;
-  const int budget = tb == 1 ? kBudgetTwoCtas : kBudgetOneCta;
+  const int budget = kBudgetTwoCtas;
   int stages = (budget - kHeaderBytes - red_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   const int want = env_int("WOQ_B200_STAGES", 0);
