@@ -170,7 +170,7 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------
-def build_layers(torch, capi, quant, p, rank, n_layers, device):
+def build_layers(torch, capi, quant, p, rank, n_layers, device, m=1):
     """Random-init N(0, 0.02) weights, quantised on the GPU, packed into contexts."""
     layers = []
     for l in range(n_layers):
@@ -180,7 +180,9 @@ def build_layers(torch, capi, quant, p, rank, n_layers, device):
             w = torch.randn((n, k), device=device, generator=g) * 0.02
             qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
             del w
-            flags = capi.LAYOUT_STREAM_ONLY | (capi.LAYOUT_GATE_UP if name == "gate_up" else 0)
+            # one tiling is enough: the streaming one for decode sizes, the tensor-core one above
+            flags = (capi.LAYOUT_STREAM_ONLY if m <= 16 else capi.LAYOUT_TC_ONLY) | (
+                capi.LAYOUT_GATE_UP if name == "gate_up" else 0)
             row[name] = capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP,
                                         capi.LOWP_BF16, layout_flags=flags)
             del qw, s, z
@@ -215,7 +217,7 @@ def run_ours(args):
     log("process group up")
     m = args.m
     n_layers = args.layers
-    layers = build_layers(torch, capi, quant, p, rank, n_layers, device)
+    layers = build_layers(torch, capi, quant, p, rank, n_layers, device, m)
     log("layers built")
     ws = capi.Workspace(layers[0]["qkv"].workspace_bytes(m), device)
 
@@ -367,14 +369,23 @@ def run_ours(args):
     local_bytes = sum(weight_bytes(n, k) + 2 * m * k + 2 * m * (n // 2 if name == "gate_up" else n)
                       + (2 * m * n if (p == 1 and kind == "row") else 0)
                       for name, n, k, kind in layer_shapes(p)) * n_layers
-    hbm_peak, _, peak_src = peaks()
+    hbm_peak, tf_peak_r, peak_src = peaks()
     achieved = local_bytes / n_launch / (kernel_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak,
-                "traffic": args.traffic if args.traffic is not None else TRAFFIC_RATIO * local_bytes / n_launch,
-                "kernel": "woq_int4_decode_kernel", "peak_source": peak_src,
-                "avg_launch_us": kernel_ms * 1e3,
-                "algorithmic_bytes_per_launch": local_bytes / n_launch}
+    if m > 16:
+        # above decode sizes the linears are contractions on the tensor cores
+        flops = sum(2.0 * m * n * k for _, n, k, _ in layer_shapes(p)) * n_layers
+        tf = flops / n_launch / (kernel_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "achieved": tf, "peak": tf_peak_r, "unit": "TFLOP/s",
+                    "frac": tf / tf_peak_r if tf_peak_r else None, "traffic": None,
+                    "kernel": "woq_int4_tc_kernel", "peak_source": peak_src, "avg_launch_us": kernel_ms * 1e3,
+                    "algorithmic_flops_per_launch": flops / n_launch}
+    else:
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak,
+                    "traffic": args.traffic if args.traffic is not None else TRAFFIC_RATIO * local_bytes / n_launch,
+                    "kernel": "woq_int4_decode_kernel", "peak_source": peak_src,
+                    "avg_launch_us": kernel_ms * 1e3,
+                    "algorithmic_bytes_per_launch": local_bytes / n_launch}
 
     # ---- end to end: host activations in, host result out, through the module API ---------
     x_host = torch.randn((m, HIDDEN)).bfloat16().pin_memory()
