@@ -278,11 +278,14 @@ def run_ours(args):
         return d_out
 
     # eager warm-up (also initialises NCCL), then capture one step in a CUDA graph
+    launches_before = capi.kernel_launches()
     if p > 1:
         torch.cuda.synchronize()
         dist.barrier()  # the fused exchange waits about 2 s for a peer, not for its set-up
     step(hidden)
     torch.cuda.synchronize()
+    # kernels this library really launched for one step (a linear above 256 tokens is several)
+    launched_per_step = capi.kernel_launches() - launches_before
     log("eager step done")
     graph = None
     if not args.no_graph:
@@ -455,9 +458,9 @@ def run_ours(args):
                        "m": m, "layers": n_layers, "parallelism": f"tp{p}",
                        "collective": ("none" if p == 1 else "fused into the linear kernels (peer stores over NVLink)"
                                       if fused else "nccl"),
-                       "l2": "weights (35.8 GB per step over all ranks) exceed L2; no flush needed",
+                       "l2": f"weights ({total_w / 1e9:.1f} GB per step over all ranks) exceed L2; no flush needed",
                        "cuda_graph": graph is not None},
-            "roofline": roofline, "prefill": prefill, "e2e": e2e, "gpu_launches": n_launch * args.steps,
+            "roofline": roofline, "prefill": prefill, "e2e": e2e, "gpu_launches": launched_per_step * args.steps,
             "clocks": clocks,
         }
         if p == 1 and not args.no_cpu_baseline:

@@ -5,7 +5,7 @@
 //                woq_linear_silu, woq_linear_add, woq_linear_add_add, woq_linear_mul, woq_linear}
 //       (reference: csrc/cpu/aten/Linear.cpp:1025-1108)
 //   ipex_prepack::{weight_only_qlinear_prepack, weight_only_qlinear_prepack_int4,
-//                  woq_linear_unpack_weight} and the class ipex_prepack.WoqLinearOpContext
+//                  woq_linear_pack_weight, woq_linear_unpack_weight} and the class ipex_prepack.WoqLinearOpContext
 //       (reference: csrc/cpu/jit/cpu/kernels/RegisterOpContextClass.cpp:127-222)
 // plus torch_ipex::woq_linear_silu_mul (the reference's two-op gate/up composition as one op).
 // Everything numeric happens behind the C ABI of libwoq_b200.so; this file only converts
@@ -328,6 +328,31 @@ c10::intrusive_ptr<WoqLinearOpContext> prepack_gate_up(
                                     WOQ_B200_LAYOUT_GATE_UP);
 }
 
+// woq_linear_pack_weight of the reference returns the blocked weight and the {fp32, fp16, bf16}
+// copies of scales / zero points / bias for the context-free woq_linear op
+// (csrc/cpu/jit/cpu/kernels/OpContext.cpp packWoqLinearWeight, ContextLinearWoq.h:60-128).
+// Here the device repack belongs to a context, so the weight is handed on in its public plain
+// format (which woq_linear accepts) together with the same dtype copies.
+std::tuple<at::Tensor, std::vector<at::Tensor>, c10::optional<std::vector<at::Tensor>>,
+           c10::optional<std::vector<at::Tensor>>, c10::optional<at::Tensor>>
+pack_weight(const at::Tensor& W, const std::string& W_dtype, const std::vector<int64_t>& W_shape,
+            const at::Tensor& scales, const c10::optional<at::Tensor>& zero_points,
+            const c10::optional<at::Tensor>& B, const c10::optional<at::Tensor>& g_idx, int64_t group_size,
+            int64_t lowp_mode) {
+  (void)dtype_from_str(W_dtype);  // rejects unknown dtype names
+  (void)W_shape;
+  (void)group_size;
+  (void)lowp_mode;
+  auto copies = [](const at::Tensor& t) {
+    auto f = t.to(at::kFloat);
+    return std::vector<at::Tensor>{f, f.to(at::kHalf), f.to(at::kBFloat16)};
+  };
+  c10::optional<std::vector<at::Tensor>> z, b;
+  if (zero_points.has_value() && zero_points->defined()) z = copies(*zero_points);
+  if (B.has_value() && B->defined()) b = copies(*B);
+  return std::make_tuple(W.contiguous(), copies(scales), z, b, g_idx);
+}
+
 at::Tensor unpack_weight(const at::Tensor& weight, const std::string&, const std::vector<int64_t>&, int64_t) {
   return weight;  // weights handed out by get_weight() are already in the public plain format
 }
@@ -404,6 +429,10 @@ TORCH_LIBRARY(ipex_prepack, m) {
         "Tensor? zero_points, Tensor? B, int group_size, int lowp_mode, int act_quant_mode) -> "
         "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext",
         prepack_gate_up);
+  m.def("woq_linear_pack_weight(Tensor W, str W_dtype, int[] W_shape, Tensor scales, Tensor? zero_points, "
+        "Tensor? B, Tensor? g_idx, int group_size, int lowp_mode) -> "
+        "(Tensor, Tensor[], Tensor[]?, Tensor[]?, Tensor?)",
+        pack_weight);
   m.def("woq_linear_unpack_weight(Tensor W, str W_dtype, int[] W_shape, int lowp_mode) -> Tensor", unpack_weight);
 }
 

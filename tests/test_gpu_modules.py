@@ -93,6 +93,12 @@ def test_op_without_context_matches_module(ipex):
     y1 = mod(x)
     y2 = torch.ops.torch_ipex.woq_linear(x, qw, "int4", [256, 512], [s], [z], None, None, 128, 2, -1, None)
     assert torch.equal(y1, y2)
+    # the reference's pack op feeds the same context-free form
+    pw, ps, pz, pb, pg = torch.ops.ipex_prepack.woq_linear_pack_weight(qw, "int4", [256, 512], s, z, None, None, 128, 2)
+    assert [t.dtype for t in ps] == [torch.float32, torch.float16, torch.bfloat16] and pb is None and pg is None
+    y3 = torch.ops.torch_ipex.woq_linear(x, pw, "int4", [256, 512], ps, pz, pb, pg, 128, 2, -1, None)
+    assert torch.equal(y1, y3)
+    assert torch.equal(torch.ops.ipex_prepack.woq_linear_unpack_weight(pw, "int4", [256, 512], 2), qw)
 
 
 def test_fused_epilogue_modules(ipex):

@@ -38,6 +38,8 @@ def test_operator_schemas(ipex):
     s = str(torch.ops.ipex_prepack.weight_only_qlinear_prepack.default._schema)
     assert "int W_dtype, int[] W_shape, Tensor scales, Tensor? zero_points" in s
     assert "WoqLinearOpContext" in s
+    s = str(torch.ops.ipex_prepack.woq_linear_pack_weight.default._schema)
+    assert "-> (Tensor, Tensor[], Tensor[]?, Tensor[]?, Tensor?)" in s and "str W_dtype" in s
     s = str(torch.ops.ipex_prepack.weight_only_qlinear_prepack_int4.default._schema)
     assert "int weight_format=0" in s
 
