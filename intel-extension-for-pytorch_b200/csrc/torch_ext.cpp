@@ -58,6 +58,14 @@ at::Tensor& workspace_for(c10::DeviceIndex dev, cudaStream_t stream, size_t byte
   return t;
 }
 
+// plain INT4 weight [N, K/2] (k even in the low nibble) with its input channels re-ordered
+at::Tensor shuffle_int4_columns(const at::Tensor& w, const at::Tensor& order) {
+  auto q = at::stack({w.bitwise_and(15), w.bitwise_right_shift(4)}, 2).reshape({w.size(0), -1});
+  q = q.index_select(1, order);
+  auto pairs = q.reshape({w.size(0), -1, 2});
+  return pairs.select(2, 0).bitwise_or(pairs.select(2, 1).bitwise_left_shift(4)).contiguous();
+}
+
 struct WoqLinearOpContext : torch::CustomClassHolder {
   int64_t magic = kHandleMagic;
   woq_b200_ctx* ctx = nullptr;
@@ -66,6 +74,7 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
   bool cache_weight_for_large_batch;
   std::vector<int64_t> weight_shape;  // [N, K]
   at::Tensor scales, zero_points, bias, g_idx;
+  at::Tensor perm, inv_perm;  // act-order: input channels sorted by group / back (int64 on the device)
   c10::optional<int64_t> batch_size;
   c10::DeviceIndex device = 0;
   int layout_flags = 0;
@@ -80,9 +89,8 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
       c10::optional<at::Tensor> g_idx, c10::optional<int64_t> batch_size, int64_t group_size,
       int64_t lowp_mode, int64_t act_quant_mode, bool cache_weight_for_large_batch,
       int64_t weight_format, int64_t layout_flags) {
-    TORCH_CHECK(!(g_idx.has_value() && g_idx->defined()),
-                "WOQ: GPTQ act-order (g_idx) is not supported by this build");
     TORCH_CHECK(weight_shape.size() == 2, "WOQ: weight_shape must be [N, K]");
+    const bool act_order = g_idx.has_value() && g_idx->defined();
     auto self = c10::make_intrusive<WoqLinearOpContext>();
     // everything lives on the weight's CUDA device (CPU tensors are moved to the current one)
     at::Device dev = weight.is_cuda() ? weight.device()
@@ -90,6 +98,24 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
     c10::cuda::CUDAGuard guard(dev);
     auto to_dev = [&](const at::Tensor& t) { return t.to(dev).contiguous(); };
     at::Tensor w = to_dev(weight);
+    at::Tensor perm, inv_perm, gi;
+    if (act_order) {
+      // GPTQ act-order: g_idx[k] is the group of input channel k.  As in the reference
+      // (csrc/cpu/jit/cpu/kernels/LinearWoqPacked.cpp:755-870) the weight's input channels are
+      // shuffled once so that every group is contiguous, and the activations are shuffled the
+      // same way at run time.
+      TORCH_CHECK(weight_dtype == WOQ_B200_DTYPE_INT4 && weight_format == WOQ_B200_FMT_PLAIN && group_size > 0,
+                  "WOQ: g_idx needs a plain INT4 weight with a group size");
+      gi = g_idx->to(dev).to(at::kLong).contiguous();
+      TORCH_CHECK(gi.dim() == 1 && gi.numel() == weight_shape[1], "WOQ: g_idx size and weight shape mismatch");
+      perm = at::argsort(gi, /*stable=*/true, /*dim=*/0, /*descending=*/false);
+      auto sorted = gi.index_select(0, perm);
+      auto want = at::arange(weight_shape[1], sorted.options()).floor_divide(group_size);
+      TORCH_CHECK(at::equal(sorted, want), "WOQ: g_idx must assign exactly group_size input channels to every group");
+      inv_perm = at::empty_like(perm);
+      inv_perm.index_put_({perm}, at::arange(weight_shape[1], perm.options()));
+      w = shuffle_int4_columns(w, perm);
+    }
     at::Tensor s = to_dev(scales.dim() > 2 ? scales.squeeze() : scales);
     if (s.scalar_type() == at::kDouble) s = s.to(at::kFloat);
     at::Tensor z, b;
@@ -126,6 +152,11 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
     self->scales = s;
     self->zero_points = z;
     self->bias = b;
+    if (act_order) {
+      self->g_idx = gi;
+      self->perm = perm;
+      self->inv_perm = inv_perm;
+    }
     self->batch_size = batch_size;
     self->device = dev.index();
     self->layout_flags = static_cast<int>(layout_flags);
@@ -139,7 +170,7 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
     auto out = at::empty({weight_shape[0], int4 ? (weight_shape[1] + 1) / 2 : weight_shape[1]},
                          at::TensorOptions().dtype(int4 ? at::kByte : at::kChar).device(at::kCUDA, device));
     WOQ_CHECK(woq_b200_ctx_unpack(ctx, out.data_ptr(), at::cuda::getCurrentCUDAStream(device).stream()));
-    return out;
+    return inv_perm.defined() ? shuffle_int4_columns(out, inv_perm) : out;
   }
   at::Tensor to_public(const at::Tensor& w) { return w; }
   c10::optional<at::Tensor> get_bias() { return bias.defined() ? c10::make_optional(bias) : c10::nullopt; }
@@ -148,7 +179,7 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
     return zero_points.defined() ? c10::make_optional(zero_points) : c10::nullopt;
   }
   std::vector<int64_t> get_weight_shape() { return weight_shape; }
-  c10::optional<at::Tensor> get_g_idx() { return c10::nullopt; }
+  c10::optional<at::Tensor> get_g_idx() { return g_idx.defined() ? c10::make_optional(g_idx) : c10::nullopt; }
   c10::optional<at::Tensor> get_cached_weight() { return c10::nullopt; }
   c10::optional<at::Tensor> get_cached_compensation() { return c10::nullopt; }
   at::Tensor pack(const at::Tensor& w) { return w; }
@@ -178,6 +209,7 @@ at::Tensor run(WoqLinearOpContext* c, const at::Tensor& input, int32_t fusion,
               ") does not match the weight's in_features (", K, ")");
   c10::cuda::CUDAGuard guard(c->device);
   at::Tensor x = input.reshape({-1, K});
+  if (c->perm.defined()) x = x.index_select(1, c->perm);  // act-order: channels in group order
   const auto in_dtype = x.scalar_type();
   if (in_dtype != at::kBFloat16) x = x.to(at::kBFloat16);  // compute dtype of this path
   if (x.stride(-1) != 1 || (x.stride(0) % 8) != 0 || (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15))
@@ -404,7 +436,8 @@ TORCH_LIBRARY(ipex_prepack, m) {
                                    self->scales.cpu(),
                                    self->zero_points.defined() ? c10::make_optional(self->zero_points.cpu()) : c10::nullopt,
                                    self->bias.defined() ? c10::make_optional(self->bias.cpu()) : c10::nullopt,
-                                   c10::optional<at::Tensor>(), self->batch_size, self->group_size,
+                                   self->g_idx.defined() ? c10::make_optional(self->g_idx.cpu()) : c10::nullopt,
+                                   self->batch_size, self->group_size,
                                    self->lowp_mode, self->act_quant_mode, self->cache_weight_for_large_batch,
                                    static_cast<int64_t>(self->layout_flags));
           },

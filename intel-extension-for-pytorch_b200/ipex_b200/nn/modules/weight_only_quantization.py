@@ -33,6 +33,15 @@ def _cuda(t: Optional[torch.Tensor], device=None):
     return t.to(device if device is not None else torch.device("cuda", torch.cuda.current_device()))
 
 
+def _gptq_qweight_to_plain(qweight: torch.Tensor) -> torch.Tensor:
+    """AutoGPTQ qweight [K/8, N] int32 (nibble i of a word = input channel 8 r + i) -> plain [N, K/2]
+    uint8 with the even input channel in the low nibble."""
+    shifts = torch.arange(0, 32, 4, device=qweight.device, dtype=torch.int32)
+    q = (qweight.unsqueeze(1) >> shifts.view(1, 8, 1)) & 0xF          # [K/8, 8, N]
+    q = q.reshape(-1, qweight.shape[1]).t().contiguous().to(torch.uint8)  # [N, K]
+    return (q[:, 0::2] | (q[:, 1::2] << 4)).contiguous()
+
+
 class WeightOnlyQuantizedLinear(nn.Module):
     r"""A weight-only quantized (WOQ) linear module with floating point tensors as inputs and
     outputs.  The weight lives on the GPU in the kernels' tiled layout."""
@@ -157,7 +166,6 @@ class WeightOnlyQuantizedLinear(nn.Module):
                 WoqLowpMode.BF16, WoqLowpMode.INT8)
         assert qweight.dtype in (torch.int32, torch.uint8, torch.quint4x2), (
             "Data type of int4 weight should be in [int32, uint8, quint4x2], but got: {}".format(qweight.dtype))
-        assert g_idx is None, "GPTQ act-order (g_idx) is not supported by this build"
         qlinear = cls(in_features, out_features, dtype=WoqWeightDtype.INT4)
         weight_format = WoqWeightFormat.PLAIN_FORMAT
         if quant_method == QuantMethod.AWQ_GEMM:
@@ -166,10 +174,14 @@ class WeightOnlyQuantizedLinear(nn.Module):
         elif quant_method == QuantMethod.GPTQ_GEMM:
             scales, zero_points = _convert_gptq_scales_qzeros(scales, zero_points)
             weight_format = WoqWeightFormat.GPTQ_FORMAT
+            if g_idx is not None:
+                # act-order: the context shuffles the input channels of a plain weight
+                qweight = _gptq_qweight_to_plain(_cuda(qweight))
+                weight_format = WoqWeightFormat.PLAIN_FORMAT
         if bias is not None and torch.count_nonzero(bias) == 0:
             bias = None
         qlinear._op_context = torch.ops.ipex_prepack.weight_only_qlinear_prepack_int4(
-            _cuda(qweight), _cuda(scales), _cuda(zero_points), _cuda(bias), g_idx, None, group_size,
+            _cuda(qweight), _cuda(scales), _cuda(zero_points), _cuda(bias), _cuda(g_idx), None, group_size,
             int(lowp_mode), int(act_quant_mode), cache, int(weight_format))
         qlinear.weight = qlinear._op_context.get_weight()
         qlinear.bias = bias is not None

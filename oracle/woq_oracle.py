@@ -296,6 +296,29 @@ def _silu_bf16(y: np.ndarray) -> np.ndarray:
     return rne_bf16(y * sig)
 
 
+def dequantize_weight_act_order(qweight, scales, zps, g_idx, K: int) -> np.ndarray:
+    """GPTQ act-order: input channel k belongs to group g_idx[k], so
+    W[n][k] = RNE_bf16((q[n][k] - zp[n][g_idx[k]]) * RNE_bf16(scale[n][g_idx[k]])).
+    The reference reaches the same values by shuffling the weight's input channels so that
+    every group is contiguous and shuffling the activations alike
+    (csrc/cpu/jit/cpu/kernels/LinearWoqPacked.cpp:755-870, 405-420)."""
+    g = np.asarray(g_idx).astype(np.int64)
+    q = weight_integers(qweight, WOQ_DTYPE_INT4, K)
+    s = rne_bf16(np.asarray(scales, dtype=np.float32))[:, g]
+    z = np.float32(8.0) if zps is None else np.asarray(zps, dtype=np.float32)[:, g]
+    return rne_bf16(((q - z) * s).astype(np.float32))
+
+
+def woq_linear_bf16_act_order(x, qweight, scales, zps, bias, g_idx):
+    """y = bf16(x W^T + bias) with the act-order weight above, fp32 accumulation."""
+    x = np.asarray(x, dtype=np.float32)
+    w = dequantize_weight_act_order(qweight, scales, zps, g_idx, x.shape[1])
+    y = x.astype(np.float64) @ w.astype(np.float64).T
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64)[None, :]
+    return rne_bf16(y.astype(np.float32))
+
+
 def apply_post_op(y: np.ndarray, fusion: int, others: Sequence[np.ndarray] = ()) -> np.ndarray:
     """y is a float32 array of bf16 values [M,N]; returns the same kind of array."""
     if fusion == FUSE_NONE:

@@ -184,6 +184,53 @@ def test_gptq_checkpoint_layout(ipex):
     parity(y, O.woq_linear_bf16(x, qw, s.astype(np.float16), z, None, O.WOQ_DTYPE_INT4, g))
 
 
+def test_gptq_act_order_g_idx(ipex):
+    """GPTQ act-order: group membership of the input channels given by g_idx (a shuffled
+    assignment), through the checkpoint entry point and through the plain prepack op; the
+    context hands back the unshuffled weight and survives pickling."""
+    from ipex_b200.llm.quantization import IPEXWeightOnlyQuantizedLinear, QuantMethod
+
+    n, k, g = 192, 512, 128
+    rng = np.random.default_rng(3)
+    g_idx = rng.permutation(np.arange(k) // g).astype(np.int32)
+    q = rng.integers(0, 16, (n, k)).astype(np.uint32)
+    qw = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8)
+    s = (rng.random((n, k // g)) * 0.01 + 0.002).astype(np.float16)
+    z = rng.integers(1, 16, (n, k // g)).astype(np.float32)
+    x = make_acts(6, k, seed=4)
+    y_ref = O.woq_linear_bf16_act_order(x, qw, s, z, None, g_idx)
+
+    # plain prepack op
+    ctx = torch.ops.ipex_prepack.weight_only_qlinear_prepack(
+        torch.from_numpy(qw).cuda(), 2, [n, k], torch.from_numpy(s).cuda(), torch.from_numpy(z).cuda(), None,
+        torch.from_numpy(g_idx).cuda(), None, g, 2, -1)
+    y = torch.ops.torch_ipex.ipex_woq_linear(bf16_tensor(x, "cuda"), ctx.get_data_handle())
+    parity(bf16_numpy(y), y_ref)
+    np.testing.assert_array_equal(ctx.get_weight().cpu().numpy(), qw)
+    np.testing.assert_array_equal(ctx.get_g_idx().cpu().numpy(), g_idx)
+    buf = io.BytesIO()
+    torch.save(ctx, buf)
+    buf.seek(0)
+    ctx2 = torch.load(buf, weights_only=False)
+    y2 = torch.ops.torch_ipex.ipex_woq_linear(bf16_tensor(x, "cuda"), ctx2.get_data_handle())
+    assert torch.equal(y, y2)
+
+    # AutoGPTQ checkpoint tensors
+    qT = q.T.reshape(k // 8, 8, n)
+    gq = np.zeros((k // 8, n), dtype=np.uint32)
+    for j in range(8):
+        gq |= qT[:, j, :] << (4 * j)
+    zz = (z.T.astype(np.int64) - 1) % 16
+    gz = np.zeros((k // g, n // 8), dtype=np.uint32)
+    for j in range(8):
+        gz |= zz[:, j::8].astype(np.uint32) << (4 * j)
+    mod = IPEXWeightOnlyQuantizedLinear.from_weight(
+        torch.from_numpy(gq.view(np.int32)), torch.from_numpy(s.T.copy()), torch.from_numpy(gz.view(np.int32)),
+        k, n, None, None, g, torch.from_numpy(g_idx), QuantMethod.GPTQ_GEMM)
+    y3 = mod(bf16_tensor(x, "cuda"))
+    assert torch.equal(y3, y)
+
+
 def test_int8_lowp_module(ipex):
     q = ipex.quantization
     lin = make_linear(384, 1024, True, seed=9)

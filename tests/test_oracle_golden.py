@@ -123,3 +123,24 @@ def test_act_quant_against_reference_fakequant(golden_dir):
         fq = q.astype(np.float32) * s[:, None]
         np.testing.assert_array_equal(fq, fq_ref)  # value equality (-0.0 == 0.0)
         assert q.min() >= -128 and q.max() <= 127 and np.abs(q).max() == 127
+
+
+def test_act_order_dequant_matches_a_per_element_restatement():
+    """W[n][k] = bf16((q - zp[n][g_idx[k]]) * bf16(scale[n][g_idx[k]])), element by element."""
+    rng = np.random.default_rng(0)
+    n, k, g = 6, 256, 64
+    g_idx = rng.permutation(np.arange(k) // g)
+    q = rng.integers(0, 16, (n, k)).astype(np.uint8)
+    qw = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8)
+    s = (rng.random((n, k // g)) * 0.01 + 0.002).astype(np.float16)
+    z = rng.integers(0, 16, (n, k // g)).astype(np.float32)
+    w = O.dequantize_weight_act_order(qw, s, z, g_idx, k)
+    for i in range(n):
+        for j in range(0, k, 7):
+            sc = O.rne_bf16(np.float32(s[i, g_idx[j]]))
+            want = O.rne_bf16(np.float32((np.float32(q[i, j]) - z[i, g_idx[j]]) * sc))
+            assert w[i, j] == want
+    # identity g_idx = the grouped dequantiser
+    ident = np.arange(k) // g
+    np.testing.assert_array_equal(O.dequantize_weight_act_order(qw, s, z, ident, k),
+                                  O.dequantize_weight(qw, s, z, O.WOQ_DTYPE_INT4, k, g))
