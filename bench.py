@@ -518,6 +518,174 @@ def run_single(args):
                       "tflops": 2 * args.m * n * k / us / 1e6}))
 
 
+# ------------------------------------------------------------------------------------------
+# --configs: every benchmark configuration's linear shapes, one JSON line per case
+# ------------------------------------------------------------------------------------------
+# (config, name, N, K, weights, fused epilogue, token counts)
+CONFIG_CASES = [
+    ("c1-single-int4", "linear", 4096, 4096, "int4", "none", (1, 4, 32, 256)),
+    ("c2-llama3-8b-int8", "qkv", 6144, 4096, "int8", "none", (1, 8, 64, 512)),
+    ("c2-llama3-8b-int8", "o_proj", 4096, 4096, "int8", "none", (1, 8, 64, 512)),
+    ("c2-llama3-8b-int8", "gate_up", 28672, 4096, "int8", "silu_mul", (1, 8, 64, 512)),
+    ("c2-llama3-8b-int8", "down_proj", 4096, 14336, "int8", "add", (1, 8, 64, 512)),
+    ("c3-llama3-8b-int4", "qkv", 6144, 4096, "int4", "none", (1, 8, 32, 1024)),
+    ("c3-llama3-8b-int4", "o_proj", 4096, 4096, "int4", "add", (1, 8, 32, 1024)),
+    ("c3-llama3-8b-int4", "gate_up", 28672, 4096, "int4", "silu_mul", (1, 8, 32, 1024)),
+    ("c3-llama3-8b-int4", "down_proj", 4096, 14336, "int4", "add", (1, 8, 32, 1024)),
+    ("c5-llama3-70b-int4", "qkv", 10240, 8192, "int4", "none", (1, 16, 128)),
+    ("c5-llama3-70b-int4", "o_proj", 8192, 8192, "int4", "add", (1, 16, 128)),
+    ("c5-llama3-70b-int4", "gate_up", 57344, 8192, "int4", "silu_mul", (1, 16, 128)),
+    ("c5-llama3-70b-int4", "down_proj", 8192, 28672, "int4", "add", (1, 16, 128)),
+]
+MOE_TOKENS = (1, 16, 256, 4096)  # c4: 8 experts, top-2, w13 28672x4096 silu_mul, w2 4096x14336 scaled add
+ROTATE_BYTES = 300e6             # weight copies walked per pass: more than twice the L2
+
+
+def _time_graph(torch, fn, launches_per_pass, min_ms=40.0):
+    """Median over five timed blocks of graph replays of `fn`; returns microseconds per launch."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        for _ in range(3):
+            graph.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        reps = max(3, min(200, int(min_ms / 5 / max(e0.elapsed_time(e1), 1e-3))))
+        samples = []
+        for _ in range(5):
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            samples.append(e0.elapsed_time(e1) / reps)
+    return statistics.median(samples) * 1e3 / launches_per_pass
+
+
+def run_configs(args):
+    """Every configuration's linears at its token counts on one GPU: CUDA-graph replay over
+    rotating weight copies (more than twice the L2), CUDA events, median of five blocks.  One
+    JSON line per case: time, weight and total GB/s, TFLOP/s and the fraction of the bound that
+    applies (HBM below the ridge point, tensor above; INT8 against twice the bf16 peak)."""
+    import torch
+
+    from ipex_b200 import _capi as capi
+    from ipex_b200 import quantization as quant
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    hbm, tf, which = peaks()
+    only = args.configs if args.configs != "all" else None
+
+    def make_ctx(n, k, kind, fusion, m, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        w = torch.randn((n, k), device=dev, generator=g) * 0.02
+        gate_up = capi.LAYOUT_GATE_UP if fusion == "silu_mul" else 0
+        if kind == "int8":
+            qw, s, _ = quant.quantize_per_channel(w, quant.WoqWeightDtype.INT8, sym_quant=True)
+            return capi.WoqContext(qw, s, None, None, n, k, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
+                                   act_quant_mode=capi.ACT_PER_M_SYM, layout_flags=gate_up)
+        qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
+        tiling = capi.LAYOUT_STREAM_ONLY if m <= 16 else capi.LAYOUT_TC_ONLY
+        return capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP, capi.LOWP_BF16,
+                               layout_flags=tiling | gate_up)
+
+    def report(config, name, n, k, kind, fusion, m, us, wbytes, total, flops, note=None):
+        ai = flops / total
+        peak_tf = tf * (2.0 if kind == "int8" else 1.0)
+        bound = "tensor" if ai > peak_tf * 1e3 / hbm else "hbm"
+        frac = (flops / us / 1e6) / peak_tf if bound == "tensor" else (total / us / 1e3) / hbm
+        line = {"config": config, "linear": name, "n": n, "k": k, "weights": kind, "fusion": fusion, "m": m,
+                "us": round(us, 2), "weight_GBps": round(wbytes / us / 1e3, 1),
+                "total_GBps": round(total / us / 1e3, 1), "tflops": round(flops / us / 1e6, 2),
+                "bound": bound, "frac_of_" + which: round(frac, 3)}
+        if note:
+            line["note"] = note
+        print(json.dumps(line), flush=True)
+
+    for config, name, n, k, kind, fusion, ms in CONFIG_CASES:
+        if only and not config.startswith(only):
+            continue
+        wbytes = n * k + 4 * n if kind == "int8" else weight_bytes(n, k)
+        copies = max(2, min(40, int(ROTATE_BYTES // wbytes) + 1))
+        fuse = {"none": capi.FUSE_NONE, "silu_mul": capi.FUSE_SILU_MUL, "add": capi.FUSE_ADD}[fusion]
+        n_out = n // 2 if fusion == "silu_mul" else n
+        ctxs, tiling_m = [], None
+        for m in ms:
+            if kind == "int8" or tiling_m is None or (tiling_m <= 16) != (m <= 16):
+                for c in ctxs:
+                    c.close()
+                ctxs = [make_ctx(n, k, kind, fusion, m, 7 * i + 1) for i in range(copies)]
+                tiling_m = m
+            x = torch.randn((m, k), device=dev).bfloat16()
+            y = torch.empty((m, n_out), device=dev, dtype=torch.bfloat16)
+            others = [torch.randn((m, n_out), device=dev).bfloat16()] if fusion == "add" else []
+            ws = capi.Workspace(ctxs[0].workspace_bytes(m), dev)
+
+            def one_pass():
+                for c in ctxs:
+                    c.linear(x, fuse, others, out=y, workspace=ws)
+
+            us = _time_graph(torch, one_pass, copies)
+            ws.status()
+            total = wbytes + 2 * m * k + 2 * m * n_out * (1 + len(others))
+            report(config, name, n, k, kind, fusion, m, us, wbytes, total, 2.0 * m * n * k)
+        for c in ctxs:
+            c.close()
+        del ctxs
+        torch.cuda.empty_cache()
+
+    if only and not "c4-mixtral-moe".startswith(only):
+        return
+    # c4: one sparse-MoE layer, experts replicated on this GPU, top-2 routing from seeded logits
+    hid, ffn, n_exp = 4096, 14336, 8
+    experts = []
+    for e in range(n_exp):
+        experts.append((make_ctx(2 * ffn, hid, "int4", "silu_mul", 1, 100 + e), make_ctx(hid, ffn, "int4", "none", 1, 200 + e)))
+    for t in MOE_TOKENS:
+        if t > 16:  # the expert linears switch tiling with the token count
+            for a, b in experts:
+                a.close()
+                b.close()
+            experts = [(make_ctx(2 * ffn, hid, "int4", "silu_mul", t, 100 + e), make_ctx(hid, ffn, "int4", "none", t, 200 + e))
+                       for e in range(n_exp)]
+        g = torch.Generator(device=dev).manual_seed(4000 + t)
+        hidden = torch.randn((t, hid), device=dev, generator=g).bfloat16()
+        router = torch.randn((n_exp, hid), device=dev, generator=g) * 0.02
+        prob = torch.softmax(hidden.float() @ router.t(), dim=-1)
+        top_w, top_e = prob.topk(2, dim=-1)
+        top_w = (top_w / top_w.sum(-1, keepdim=True)).bfloat16()
+        plan = []
+        for e in range(n_exp):
+            tok, slot = (top_e == e).nonzero(as_tuple=True)
+            if tok.numel():
+                plan.append((e, tok.int().contiguous(), top_w[tok, slot].contiguous()))
+        out = torch.zeros((t, hid), device=dev, dtype=torch.bfloat16)
+        wss = {e: capi.moe_expert(experts[e][0], experts[e][1], hidden, idx, w, out) for e, idx, w in plan}
+
+        def one_layer():
+            for e, idx, w in plan:
+                capi.moe_expert(experts[e][0], experts[e][1], hidden, idx, w, out, workspace=wss[e])
+
+        us = _time_graph(torch, one_layer, 1)
+        for w_ in wss.values():
+            w_.status()
+        wbytes = len(plan) * (weight_bytes(2 * ffn, hid) + weight_bytes(hid, ffn))
+        assigned = sum(int(idx.numel()) for _, idx, _ in plan)
+        total = wbytes + assigned * (2 * hid + 2 * ffn * 2 + 2 * hid * 2)
+        flops = 2.0 * assigned * (2 * ffn * hid + hid * ffn)
+        report("c4-mixtral-moe", "layer (8 experts, top-2)", 2 * ffn, hid, "int4", "silu_mul + scaled add", t, us,
+               wbytes, total, flops, note=f"{len(plan)} experts active, {assigned} token assignments, one layer per pass "
+               f"(weights {'above' if wbytes > 2.5e8 else 'below'} twice the L2)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -537,8 +705,12 @@ def main():
     ap.add_argument("--hint", type=int, default=0, help="--single: kernel hint (see include/woq_b200.h)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture (default: TRAFFIC_RATIO x algorithmic bytes)")
+    ap.add_argument("--configs", default=None, nargs="?", const="all",
+                    help="time every benchmark configuration's linears (optionally a prefix: c1, c2, c3, c4, c5)")
     args = ap.parse_args()
-    if args.single:
+    if args.configs:
+        run_configs(args)
+    elif args.single:
         run_single(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -236,7 +236,9 @@ int woq_b200_linear_static_scratch(const woq_b200_ctx* ctx, const void* x, int64
  * out[row_idx[i], :] = bf16(out[row_idx[i], :] + y[i, :] * row_weight[i]) with
  * y = x[row_idx_in ? row_idx_in[i] : i, :] * W^T.  Replaces fuse_index_unsqueeze /
  * fuse_index_mul_index_add around the WOQ linears of mixtral_moe_woq
- * (csrc/cpu/aten/kernels/MoEKrnl.cpp:67-160,254-285).  row_weight is bf16 [m]. */
+ * (csrc/cpu/aten/kernels/MoEKrnl.cpp:67-160,254-285).  row_weight is bf16 [m].  The row_idx
+ * values of one call must be distinct (a token reaches an expert once); rows that repeat
+ * would lose all but one of their updates. */
 int woq_b200_linear_scatter(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
                             const int32_t* row_idx, const void* row_weight, void* out,
                             int64_t ld_out, void* workspace, size_t workspace_bytes,

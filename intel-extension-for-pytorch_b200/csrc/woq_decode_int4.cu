@@ -108,33 +108,6 @@ __device__ __forceinline__ uint32_t comm_wait_word(const uint2* w, uint32_t stam
   }
 }
 
-// Bias, rounding and the fused post-op for one (row, token) of tile `tl`; stores the result
-// (scatter epilogue: adds it into its row) and returns its bf16 bits, 0 where nothing is stored.
-__device__ __forceinline__ uint32_t decode_epilogue(const DecodeParams& p, int tl, int row, int tok, float r) {
-  const int n = decode_row_to_n(p, tl, row);
-  if (tok >= p.m || n >= p.n) return 0u;
-  if (p.bias) r += p.bias[n];
-  r = bf16_round(r);
-  if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
-    const size_t o = static_cast<size_t>(p.row_idx[tok]) * p.ldy + n;
-    const float w = __bfloat162float(p.row_w[tok]);
-    p.y[o] = __float2bfloat16_rn(__bfloat162float(p.y[o]) + r * w);
-    return 0u;
-  }
-  const size_t o = static_cast<size_t>(tok) * p.ldo + n;  // in the fused operands
-  if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
-    r = bf16_round(r + __bfloat162float(p.other0[o]));
-    if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __bfloat162float(p.other1[o]));
-  } else if (p.fusion == FUSE_MUL) {
-    r = bf16_round(r * __bfloat162float(p.other0[o]));
-  } else {
-    r = unary_post_op(r, p.fusion);
-  }
-  const __nv_bfloat16 v = __float2bfloat16_rn(r);
-  p.y[static_cast<size_t>(tok) * p.ldy + n] = v;
-  return __bfloat16_as_ushort(v);
-}
-
 // The stages a CTA walks: its share [b_begin, b_end) of the k-block sequence cut at tile
 // boundaries ("segments") and then into runs of up to kStageKBlocks k-blocks.  Producer and
 // consumers step through the same sequence.
@@ -157,11 +130,210 @@ struct StageIter {
   }
 };
 
+// Bias, rounding, fused post-op and store of one finished 64-row tile, by one warp: a0 / a1
+// hold rows lane and lane + 32 for every token.  A function of its own (not inlined) so that
+// its registers are allocated apart from the main loop's; with the tensor-parallel exchange
+// compiled in (COMM) it also swaps the tile with the other ranks.
+template <int NTOK, bool COMM>
+__device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl, int lane, uint32_t epoch,
+                                                  float* a0, float* a1) {
+  if (COMM && p.comm.mode == kCommAllReduce) {
+    // Row-parallel linear: every rank's bf16 partial of this tile goes to every rank; each
+    // rank then adds them in rank order (fp32) and rounds once, so all ranks hold the same
+    // bits; bias and post-op follow the reduction.
+    const CommParams& c = p.comm;
+    const uint32_t stamp = epoch + 1;
+    const int parity = epoch & 1;
+    uint32_t mine[NTOK];
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok)
+      if (tok < p.m) {
+        mine[tok] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a0[tok]))) |
+                    (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a1[tok]))) << 16);
+        for (int q = 0; q < c.world; ++q)
+          if (q != c.rank)
+            st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
+                              make_uint2(mine[tok], stamp));
+      }
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok)
+      if (tok < p.m) {
+        float s0 = 0.f, s1 = 0.f;
+        for (int r = 0; r < c.world; ++r) {
+          const uint32_t w = r == c.rank ? mine[tok]
+                                         : comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane),
+                                                          stamp, p.status);
+          s0 += __uint_as_float(w << 16);
+          s1 += __uint_as_float(w & 0xffff0000u);
+        }
+        a0[tok] = bf16_round(s0);
+        a1[tok] = bf16_round(s1);
+      }
+  }
+  // Words for the gather: the two results of this lane per token.  Everything the epilogue
+  // reads from global memory (bias, fused operands, scatter rows) is loaded for all tokens
+  // before the first value is used: one round trip instead of one per token.  Loads of
+  // tokens or rows that do not exist are clamped to ones that do and never stored.
+  uint32_t out[NTOK];
+  if (p.fusion == FUSE_SILU_MUL) {
+    // gate/up layout: row lane is a gate row, row lane + 32 its up row
+    const int col = tl * 32 + lane;
+    const bool ok = col < p.n_out;
+    float b_gate = 0.f, b_up = 0.f;
+    if (p.bias && ok) {
+      b_gate = p.bias[decode_row_to_n(p, tl, lane)];
+      b_up = p.bias[decode_row_to_n(p, tl, lane + 32)];
+    }
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok) {
+      out[tok] = 0u;
+      if (tok < p.m && ok) {
+        float gate = a0[tok], up = a1[tok];
+        if (p.bias) {
+          gate += b_gate;
+          up += b_up;
+        }
+        const __nv_bfloat16 v = __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
+        p.y[static_cast<size_t>(tok) * p.ldy + col] = v;
+        out[tok] = __bfloat16_as_ushort(v);
+      }
+    }
+  } else {
+    const int n0 = decode_row_to_n(p, tl, lane), n1 = decode_row_to_n(p, tl, lane + 32);
+    const bool ok0 = n0 < p.n, ok1 = n1 < p.n;
+    const int c0 = ok0 ? n0 : 0, c1 = ok1 ? n1 : 0;  // columns that always exist
+    float b0 = 0.f, b1 = 0.f;
+    if (p.bias) {
+      b0 = p.bias[c0];
+      b1 = p.bias[c1];
+    }
+    // Eight tokens at a time (register budget).  Loads sit in loops of their own, guarded per
+    // token, so that those of all existing tokens are in flight together; the arithmetic
+    // follows in a second guarded loop.
+#pragma unroll
+    for (int h = 0; h < NTOK; h += 8) {
+      if (h >= p.m) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[h + i] = 0u;
+        continue;
+      }
+      float r0[8], r1[8], f0[8], f1[8];
+      auto load_rows = [&](const __nv_bfloat16* src, int64_t ld) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            const size_t o = static_cast<size_t>(h + i) * ld;
+            f0[i] = __bfloat162float(src[o + c0]);
+            f1[i] = __bfloat162float(src[o + c1]);
+          }
+      };
+      int rows[8];
+      float w[8];
+      if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
+        // y[row_idx[tok]] += result * row_w[tok]; the rows of one call are distinct
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            rows[i] = p.row_idx[h + i];
+            w[i] = __bfloat162float(p.row_w[h + i]);
+          }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            const size_t o = static_cast<size_t>(rows[i]) * p.ldy;
+            f0[i] = __bfloat162float(p.y[o + c0]);
+            f1[i] = __bfloat162float(p.y[o + c1]);
+          }
+      } else if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD || p.fusion == FUSE_MUL) {
+        load_rows(p.other0, p.ldo);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (h + i < p.m) {
+          float v0 = a0[h + i], v1 = a1[h + i];
+          if (p.bias) {
+            v0 += b0;
+            v1 += b1;
+          }
+          v0 = bf16_round(v0);
+          v1 = bf16_round(v1);
+          if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
+            v0 = f0[i] + v0 * w[i];
+            v1 = f1[i] + v1 * w[i];
+          } else if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
+            v0 = bf16_round(v0 + f0[i]);
+            v1 = bf16_round(v1 + f1[i]);
+          } else if (p.fusion == FUSE_MUL) {
+            v0 = bf16_round(v0 * f0[i]);
+            v1 = bf16_round(v1 * f1[i]);
+          } else {
+            v0 = unary_post_op(v0, p.fusion);
+            v1 = unary_post_op(v1, p.fusion);
+          }
+          r0[i] = v0;
+          r1[i] = v1;
+        }
+      if (p.fusion == FUSE_ADD_ADD) {
+        load_rows(p.other1, p.ldo);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            r0[i] = bf16_round(r0[i] + f0[i]);
+            r1[i] = bf16_round(r1[i] + f1[i]);
+          }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        out[h + i] = 0u;
+        if (h + i < p.m) {
+          const __nv_bfloat16 v0 = __float2bfloat16_rn(r0[i]), v1 = __float2bfloat16_rn(r1[i]);
+          const size_t o = static_cast<size_t>(p.fusion == FUSE_SCALED_SCATTER_ADD ? rows[i] : h + i) * p.ldy;
+          if (ok0) p.y[o + n0] = v0;
+          if (ok1) p.y[o + n1] = v1;
+          if (p.fusion != FUSE_SCALED_SCATTER_ADD)
+            out[h + i] = (ok0 ? __bfloat16_as_ushort(v0) : 0u) |
+                         (ok1 ? static_cast<uint32_t>(__bfloat16_as_ushort(v1)) << 16 : 0u);
+        }
+      }
+    }
+  }
+  if (COMM && p.comm.mode == kCommAllGather) {
+    // Column-parallel linear: p.y is this rank's column block of the gathered tensor.  The
+    // tile also goes to every other rank, and the same tile of every other rank is copied
+    // from this rank's slots into its column block here, so that the gathered tensor is
+    // written by local stores only and is complete when this kernel ends.
+    const CommParams& c = p.comm;
+    const uint32_t stamp = epoch + 1;
+    const int parity = epoch & 1;
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok)
+      if (tok < p.m)
+        for (int q = 0; q < c.world; ++q)
+          if (q != c.rank)
+            st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
+                              make_uint2(out[tok], stamp));
+    const bool pair = p.fusion != FUSE_SILU_MUL;
+    const int c0 = pair ? decode_row_to_n(p, tl, lane) : tl * 32 + lane;
+    const int c1 = decode_row_to_n(p, tl, lane + 32);
+    for (int r = 0; r < c.world; ++r) {
+      if (r == c.rank) continue;
+      __nv_bfloat16* dst = p.y + (static_cast<int64_t>(r) - c.rank) * p.n_out;
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < p.m) {
+          const uint32_t w = comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane), stamp, p.status);
+          if (c0 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w & 0xffffu));
+          if (pair && c1 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w >> 16));
+        }
+    }
+  }
+}
+
 // COMM: compiled with the tensor-parallel exchange in the epilogue (the plain variant carries
 // none of its code or registers).
 template <int TB, int MODE, int KPW, bool COMM>
 __global__ void __launch_bounds__(kThreads, 2)
-    woq_int4_decode_kernel(const DecodeParams p) {
+    woq_int4_decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(smem);
   constexpr int NTOK = 8 * TB;
@@ -208,96 +380,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   // arrive, reduces the tile in a fixed order.
   uint32_t epoch = 0;  // read by the warps that run epilogues, once the previous grid is done
   auto run_epilogue = [&](int tl, float* a0, float* a1) {
-    if (COMM && p.comm.mode == kCommAllReduce) {
-      // Row-parallel linear: every rank's bf16 partial of this tile goes to every rank; each
-      // rank then adds them in rank order (fp32) and rounds once, so all ranks hold the same
-      // bits; bias and post-op follow the reduction.
-      const CommParams& c = p.comm;
-      const uint32_t stamp = epoch + 1;
-      const int parity = epoch & 1;
-      uint32_t mine[NTOK];
-#pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
-        if (tok < p.m) {
-          mine[tok] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a0[tok]))) |
-                      (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(a1[tok]))) << 16);
-          for (int q = 0; q < c.world; ++q)
-            if (q != c.rank)
-              st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
-                                make_uint2(mine[tok], stamp));
-        }
-#pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
-        if (tok < p.m) {
-          float s0 = 0.f, s1 = 0.f;
-          for (int r = 0; r < c.world; ++r) {
-            const uint32_t w = r == c.rank ? mine[tok]
-                                           : comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane),
-                                                            stamp, p.status);
-            s0 += __uint_as_float(w << 16);
-            s1 += __uint_as_float(w & 0xffff0000u);
-          }
-          a0[tok] = bf16_round(s0);
-          a1[tok] = bf16_round(s1);
-        }
-    }
-    // words for the gather: the two results of this lane per token
-    uint32_t out[NTOK];
-    if (p.fusion == FUSE_SILU_MUL) {
-      // gate/up layout: row lane is a gate row, row lane + 32 its up row
-      const int col = tl * 32 + lane;
-      const int n_gate = decode_row_to_n(p, tl, lane);
-      const int n_up = decode_row_to_n(p, tl, lane + 32);
-#pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok) {
-        out[tok] = 0u;
-        if (tok < p.m && col < p.n_out) {
-          float gate = a0[tok], up = a1[tok];
-          if (p.bias) {
-            gate += p.bias[n_gate];
-            up += p.bias[n_up];
-          }
-          const __nv_bfloat16 v = __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
-          p.y[static_cast<size_t>(tok) * p.ldy + col] = v;
-          out[tok] = __bfloat16_as_ushort(v);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
-        out[tok] = decode_epilogue(p, tl, lane, tok, a0[tok]) |
-                   (decode_epilogue(p, tl, lane + 32, tok, a1[tok]) << 16);
-    }
-    if (COMM && p.comm.mode == kCommAllGather) {
-      // Column-parallel linear: p.y is this rank's column block of the gathered tensor.  The
-      // tile also goes to every other rank, and the same tile of every other rank is copied
-      // from this rank's slots into its column block here, so that the gathered tensor is
-      // written by local stores only and is complete when this kernel ends.
-      const CommParams& c = p.comm;
-      const uint32_t stamp = epoch + 1;
-      const int parity = epoch & 1;
-#pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
-        if (tok < p.m)
-          for (int q = 0; q < c.world; ++q)
-            if (q != c.rank)
-              st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
-                                make_uint2(out[tok], stamp));
-      const bool pair = p.fusion != FUSE_SILU_MUL;
-      const int c0 = pair ? decode_row_to_n(p, tl, lane) : tl * 32 + lane;
-      const int c1 = decode_row_to_n(p, tl, lane + 32);
-      for (int r = 0; r < c.world; ++r) {
-        if (r == c.rank) continue;
-        __nv_bfloat16* dst = p.y + (static_cast<int64_t>(r) - c.rank) * p.n_out;
-#pragma unroll
-        for (int tok = 0; tok < NTOK; ++tok)
-          if (tok < p.m) {
-            const uint32_t w = comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane), stamp, p.status);
-            if (c0 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w & 0xffffu));
-            if (pair && c1 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w >> 16));
-          }
-      }
-    }
+    decode_tile_epilogue<NTOK, COMM>(p, tl, lane, epoch, a0, a1);
   };
   // Both epilogue-running warps call this when they are done; the second one of the last CTA
   // of the grid closes the epoch.
@@ -331,12 +414,25 @@ __global__ void __launch_bounds__(kThreads, 2)
       const int64_t cb = (static_cast<int64_t>(c) * units) / gridDim.x * p.unit;
       const float* src =
           p.partials + static_cast<size_t>(c * 2 + (cb >= tb0 ? 0 : 1)) * (16 * kTileN);
+      // The loads sit in a loop of their own so that those of all tokens are in flight
+      // together; the adds follow.
 #pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
-        if (tok < p.m) {
-          a0[tok] += __ldcg(src + tok * kTileN + lane);
-          a1[tok] += __ldcg(src + tok * kTileN + lane + 32);
-        }
+      for (int h = 0; h < NTOK; h += 8) {
+        if (h >= p.m) continue;
+        float t0[8], t1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            t0[i] = __ldcg(src + (h + i) * kTileN + lane);
+            t1[i] = __ldcg(src + (h + i) * kTileN + lane + 32);
+          }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            a0[h + i] += t0[i];
+            a1[h + i] += t1[i];
+          }
+      }
     }
     if (lane == 0) p.counters[tl] = 0;
     run_epilogue(tl, a0, a1);
