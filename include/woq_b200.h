@@ -45,8 +45,13 @@ extern "C" {
 #define WOQ_B200_LOWP_BF16 2
 #define WOQ_B200_LOWP_INT8 3
 
+/* Dynamic activation quantisation of the INT8 compute path (woq_defines.h:11-19): one range
+ * for the whole activation tensor or one per token; asymmetric u8 codes with a zero point, or
+ * symmetric s8 codes.  The per-K-block modes (1, 3, 5, 7) are not built. */
 #define WOQ_B200_ACT_NONE (-1)
+#define WOQ_B200_ACT_PER_TENSOR 0
 #define WOQ_B200_ACT_PER_M 2
+#define WOQ_B200_ACT_PER_TENSOR_SYM 4
 #define WOQ_B200_ACT_PER_M_SYM 6
 
 #define WOQ_B200_FMT_PLAIN 0 /* INT4: [N, K/2] u8, even k in the low nibble; INT8: [N, K] s8 */
@@ -259,13 +264,19 @@ int woq_b200_moe_expert(const woq_b200_ctx* w13, const woq_b200_ctx* w2, const v
  * uses for its tiles (the reference's Dequantize<bfloat16>, csrc/cpu/aten/utils/woq.h:1501-1581). */
 int woq_b200_dump_dequant(const woq_b200_ctx* ctx, void* w_bf16, void* stream);
 
-/* INT8-lowp internals for M tokens: quantised activations qa[M, K] s8, their scales sa[M] f32
- * (dynamic_quantize_per_block, csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750) and the
- * int32 accumulators acc[M, N] summed over the whole K (woq.h:2231-2354).  Any of the three
- * outputs may be null. */
+/* INT8-lowp internals for M tokens: quantised activations qa[M, K] (s8, or u8 in the
+ * asymmetric modes), their scales sa[M] f32 (dynamic_quantize_per_block,
+ * csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750) and the int32 accumulators acc[M, N]
+ * = sum over the whole K of qa * qw, before the zero-point compensation (woq.h:2231-2354).
+ * Any of the three outputs may be null. */
 int woq_b200_int8_internals(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
                             int8_t* qa, float* sa, int32_t* acc, void* workspace,
                             size_t workspace_bytes, void* stream);
+
+/* The activation zero points zp[M] (int32) that the latest INT8 call on `workspace` with M
+ * tokens left there; zeros for the symmetric modes. */
+int woq_b200_int8_zero_points(const woq_b200_ctx* ctx, int64_t m, int32_t* zp, const void* workspace,
+                              size_t workspace_bytes, void* stream);
 
 /* Reads the status word of a workspace (synchronises the stream).  WOQ_B200_OK, or
  * WOQ_B200_ERR_DEVICE_WAIT when a bounded wait inside a kernel gave up; the word is cleared. */

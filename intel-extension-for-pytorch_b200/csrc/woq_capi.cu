@@ -74,6 +74,7 @@ struct woq_b200_ctx {
   int tiles_tc, kbpg_shift;
   size_t wq_tc_bytes, sz_tc_bytes;
   float* scale_f32;  // INT8: per-channel fp32 scales [n_pad]
+  int32_t* comp;     // INT8 with asymmetric activations: per-row sums of the weight codes [n_pad]
   int is_int8;       // INT8 weights with INT8 compute
   int plain_scales;  // INT4: every scale is normal and below 0.5, every zero point below 16
   int kc_per_tile;   // INT8: K / 128
@@ -107,9 +108,11 @@ int create_int8(const woq_b200_desc* d, const void* qweight, const void* scales,
                 const void* zero_points, const void* bias, cudaStream_t stream, woq_b200_ctx** out) {
   if (d->lowp_mode != WOQ_B200_LOWP_INT8)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 weights are built for lowp_mode INT8 only (got %d)", d->lowp_mode);
-  if (d->act_quant_mode != WOQ_B200_ACT_PER_M_SYM)
-    return fail(WOQ_B200_ERR_UNSUPPORTED, "activation quantisation mode %d is not built (per-token symmetric = 6 is)",
-                d->act_quant_mode);
+  if (d->act_quant_mode != WOQ_B200_ACT_PER_M_SYM && d->act_quant_mode != WOQ_B200_ACT_PER_M &&
+      d->act_quant_mode != WOQ_B200_ACT_PER_TENSOR_SYM && d->act_quant_mode != WOQ_B200_ACT_PER_TENSOR)
+    return fail(WOQ_B200_ERR_UNSUPPORTED,
+                "activation quantisation mode %d is not built (per tensor 0 / 4 and per token 2 / 6 are; the "
+                "per-K-block modes 1, 3, 5, 7 are not)", d->act_quant_mode);
   if (zero_points) return fail(WOQ_B200_ERR_INVALID_ARG, "INT8 weights with INT8 compute are symmetric: no zero points");
   if (d->group_size > 0 && d->group_size < d->k)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 compute path takes per-channel weight scales (group_size -1)");
@@ -127,6 +130,7 @@ int create_int8(const woq_b200_desc* d, const void* qweight, const void* scales,
     if (c->wq) cudaFree(c->wq);
     if (c->scale_f32) cudaFree(c->scale_f32);
     if (c->bias) cudaFree(c->bias);
+    if (c->comp) cudaFree(c->comp);
     delete c;
     return rc;
   };
@@ -147,6 +151,14 @@ int create_int8(const woq_b200_desc* d, const void* qweight, const void* scales,
   CUDA_TRY_I(woq::launch_pack_int8(static_cast<const int8_t*>(qweight), reinterpret_cast<int8_t*>(c->wq),
                                    (int)d->n, (int)d->k, c->tiles_tc * 2, gate_up, stream));
   CUDA_TRY_I(woq::launch_pad_scale(scales, c->scale_f32, (int)d->n, c->tiles_tc * 128, d->scale_dtype, stream));
+  if (d->act_quant_mode == WOQ_B200_ACT_PER_M || d->act_quant_mode == WOQ_B200_ACT_PER_TENSOR) {
+    // asymmetric activations: the zero point's share of every accumulator is taken out with
+    // the per-row sums of the weight codes (the reference's cached compensation)
+    const size_t comp_bytes = static_cast<size_t>(c->tiles_tc) * 128 * sizeof(int32_t);
+    CUDA_TRY_I(cudaMalloc(&c->comp, comp_bytes));
+    CUDA_TRY_I(cudaMemsetAsync(c->comp, 0, comp_bytes, stream));
+    CUDA_TRY_I(woq::launch_weight_row_sum(static_cast<const int8_t*>(qweight), (int)d->n, (int)d->k, c->comp, stream));
+  }
   if (bias) {
     CUDA_TRY_I(cudaMalloc(&c->bias, static_cast<size_t>(d->n) * sizeof(float)));
     convert_bias_kernel<<<(unsigned)((d->n + 255) / 256), 256, 0, stream>>>(bias, c->bias, (int)d->n, d->bias_dtype);
@@ -161,7 +173,7 @@ int create_int8(const woq_b200_desc* d, const void* qweight, const void* scales,
 }
 
 struct Int8Workspace {
-  size_t partial_off, sa_off, qa_off, total;
+  size_t partial_off, sa_off, zpa_off, range_off, qa_off, total;
 };
 Int8Workspace int8_ws_layout(const woq_b200_ctx* c, int64_t m) {
   Int8Workspace w;
@@ -171,7 +183,10 @@ Int8Workspace int8_ws_layout(const woq_b200_ctx* c, int64_t m) {
   w.partial_off = kWsHeaderBytes;
   size_t off = w.partial_off + woq::int8_partial_bytes(c->num_sms, n_tok);
   w.sa_off = (off + 255) / 256 * 256;
-  off = w.sa_off + static_cast<size_t>((m + 63) / 64 * 64) * sizeof(float);
+  const size_t m_pad = static_cast<size_t>((m + 63) / 64 * 64);
+  w.zpa_off = w.sa_off + m_pad * sizeof(float);
+  w.range_off = w.zpa_off + m_pad * sizeof(int32_t);
+  off = w.range_off + 2 * m_pad * sizeof(float);
   w.qa_off = (off + 1023) / 1024 * 1024;
   w.total = w.qa_off + static_cast<size_t>(m) * c->desc.k;
   return w;
@@ -376,6 +391,7 @@ int woq_b200_ctx_destroy(woq_b200_ctx* c) {
   cudaFree(c->wq_tc);
   cudaFree(c->sz_tc);
   cudaFree(c->scale_f32);
+  cudaFree(c->comp);
   cudaFree(c->bias);
   delete c;
   return WOQ_B200_OK;
@@ -568,7 +584,12 @@ static int run_int8(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
   float* sa = reinterpret_cast<float*>(w8 + L.sa_off);
   int8_t* qa = reinterpret_cast<int8_t*>(w8 + L.qa_off);
   const int64_t k = c->desc.k;
-  CUDA_TRY(woq::launch_quant_act_sym(static_cast<const __nv_bfloat16*>(x), ldx, (int)m, (int)k, qa, sa, stream));
+  int32_t* zpa = reinterpret_cast<int32_t*>(w8 + L.zpa_off);
+  const int mode = c->desc.act_quant_mode;
+  const int asym = mode == WOQ_B200_ACT_PER_M || mode == WOQ_B200_ACT_PER_TENSOR;
+  const int per_tensor = mode == WOQ_B200_ACT_PER_TENSOR || mode == WOQ_B200_ACT_PER_TENSOR_SYM;
+  CUDA_TRY(woq::launch_quant_act(static_cast<const __nv_bfloat16*>(x), ldx, (int)m, (int)k, asym, per_tensor, qa, sa,
+                                 zpa, reinterpret_cast<float*>(w8 + L.range_off), stream));
   if (qa_out) CUDA_TRY(cudaMemcpyAsync(qa_out, qa, static_cast<size_t>(m) * k, cudaMemcpyDeviceToDevice, stream));
   if (sa_out) CUDA_TRY(cudaMemcpyAsync(sa_out, sa, static_cast<size_t>(m) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
   if (!y && !acc_out) return WOQ_B200_OK;
@@ -582,6 +603,8 @@ static int run_int8(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
     p.wq = reinterpret_cast<const int8_t*>(c->wq);
     p.sw = c->scale_f32;
     p.sa = sa + m0;
+    p.zpa = asym ? zpa + m0 : nullptr;
+    p.comp = c->comp;
     p.bias = c->bias;
     p.y = y ? static_cast<__nv_bfloat16*>(y) + m0 * ldy : nullptr;
     p.other0 = o0 ? static_cast<const __nv_bfloat16*>(o0) + m0 * ldy : nullptr;
@@ -921,6 +944,25 @@ int woq_b200_int8_internals(const woq_b200_ctx* c, const void* x, int64_t m, int
     return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
   return run_int8(c, x, m, ldx, WOQ_B200_FUSE_NONE, nullptr, nullptr, nullptr, c->desc.n, qa, sa, acc,
                   workspace, workspace_bytes, static_cast<cudaStream_t>(stream_));
+}
+
+int woq_b200_int8_zero_points(const woq_b200_ctx* c, int64_t m, int32_t* zp, const void* workspace,
+                              size_t workspace_bytes, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!c->is_int8) return fail(WOQ_B200_ERR_INVALID_ARG, "context does not use INT8 compute");
+  if (!zp || !workspace || m < 1) return fail(WOQ_B200_ERR_INVALID_ARG, "null pointer or no tokens");
+  const Int8Workspace L = int8_ws_layout(c, m);
+  if (workspace_bytes < L.total)
+    return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", workspace_bytes, L.total);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int mode = c->desc.act_quant_mode;
+  if (mode == WOQ_B200_ACT_PER_M || mode == WOQ_B200_ACT_PER_TENSOR) {
+    CUDA_TRY(cudaMemcpyAsync(zp, static_cast<const uint8_t*>(workspace) + L.zpa_off,
+                             static_cast<size_t>(m) * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream));
+  } else {
+    CUDA_TRY(cudaMemsetAsync(zp, 0, static_cast<size_t>(m) * sizeof(int32_t), stream));
+  }
+  return WOQ_B200_OK;
 }
 
 int woq_b200_workspace_status(void* workspace, void* stream_) {

@@ -410,27 +410,38 @@ __global__ void __launch_bounds__(kThreads, 2)
     __threadfence();
 #pragma unroll
     for (int tok = 0; tok < NTOK; ++tok) a0[tok] = a1[tok] = 0.f;
-    for (int c = c_first; c <= c_last; ++c) {
-      const int64_t cb = (static_cast<int64_t>(c) * units) / gridDim.x * p.unit;
-      const float* src =
-          p.partials + static_cast<size_t>(c * 2 + (cb >= tb0 ? 0 : 1)) * (16 * kTileN);
-      // The loads sit in a loop of their own so that those of all tokens are in flight
-      // together; the adds follow.
+    // The first contributor's share began before this tile unless it begins exactly with it
+    // (its partial is then its first segment's); every later contributor begins inside the
+    // tile, so this is its first segment.  Two contributors and eight tokens at a time; the
+    // loads sit in a loop of their own so that all of them are in flight together, the adds
+    // follow in CTA order.
+    const int64_t cb_first = (static_cast<int64_t>(c_first) * units) / gridDim.x * p.unit;
+    const float* slot0 = p.partials + static_cast<size_t>(c_first * 2 + (cb_first >= tb0 ? 0 : 1)) * (16 * kTileN) + lane;
+    for (int c = c_first; c <= c_last; c += 2) {
+      const float* src0 = c == c_first ? slot0 : p.partials + static_cast<size_t>(c * 2) * (16 * kTileN) + lane;
+      const bool two = c + 1 <= c_last;
+      const float* src1 = p.partials + static_cast<size_t>((two ? c + 1 : c) * 2) * (16 * kTileN) + lane;
 #pragma unroll
       for (int h = 0; h < NTOK; h += 8) {
         if (h >= p.m) continue;
-        float t0[8], t1[8];
+        float t0[8], t1[8], u0[8], u1[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
-            t0[i] = __ldcg(src + (h + i) * kTileN + lane);
-            t1[i] = __ldcg(src + (h + i) * kTileN + lane + 32);
+            t0[i] = __ldcg(src0 + (h + i) * kTileN);
+            t1[i] = __ldcg(src0 + (h + i) * kTileN + 32);
+            u0[i] = __ldcg(src1 + (h + i) * kTileN);
+            u1[i] = __ldcg(src1 + (h + i) * kTileN + 32);
           }
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
             a0[h + i] += t0[i];
             a1[h + i] += t1[i];
+            if (two) {
+              a0[h + i] += u0[i];
+              a1[h + i] += u1[i];
+            }
           }
       }
     }

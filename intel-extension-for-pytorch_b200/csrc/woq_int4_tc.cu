@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       // wait when the other has issued its last MMA.  A token (`issued`) keeps the stages in
       // order, so the MMA that starts a tile's accumulator runs before any that adds to it.
       const int me = warp == kMmaWarp ? 0 : 1;
-      const uint32_t idesc = umma_idesc(p.n_tok, /*bf16*/ 1, /*f32*/ 1);
+      const uint32_t idesc = umma_idesc(p.n_tok, /*bf16*/ 1, /*bf16*/ 1, /*f32*/ 1);
       const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
       const uint32_t x_base_lo = (smem_u32(x_stages) & 0x3FFFFu) >> 4;
       const uint32_t x_stage_lo = static_cast<uint32_t>(x_stage_bytes) >> 4;

@@ -75,33 +75,94 @@ __global__ void pad_scale_kernel(const void* src, float* dst, int n, int n_pad, 
   dst[i] = v;
 }
 
-// ---- per-token symmetric activation quantisation --------------------------------------
-// scale = max(|max|, |min|) / 127 ; q = clamp(nearbyint(x / scale), -128, 127); a row of zeros
-// gets codes 0.  One CTA per token row.
-__global__ void __launch_bounds__(256) quant_act_sym_kernel(const __nv_bfloat16* x, int64_t ldx, int k,
-                                                            int8_t* qa, float* sa) {
-  __shared__ float red[8];
-  const int m = blockIdx.x, tid = threadIdx.x;
-  const __nv_bfloat16* xr = x + static_cast<int64_t>(m) * ldx;
-  float amax = 0.f;
-  for (int i = tid * 8; i < k; i += 256 * 8) {
+// ---- dynamic activation quantisation ------------------------------------------------------
+// Follows dynamic_quantize_per_block (csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750).
+// Symmetric: scale = max(|max|, |min|) / 127, q = clamp(nearbyint(x / scale), -128, 127) as s8.
+// Asymmetric: scale = (max - min) / 255, zp = -nearbyint(min / scale),
+// q = clamp(nearbyint(x / scale + zp), 0, 255) as u8.  True division, round-half-even; no
+// clamping of the range to zero and no epsilon; a constant row of zeros gets codes 0.
+// Per token: one range per row.  Per tensor: one range over all rows (act_row_range_kernel
+// first, then every CTA folds the row ranges).  One CTA per token row.
+__device__ __forceinline__ void block_min_max(float& lo, float& hi, float* red) {
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if ((tid & 31) == 0) {
+    red[tid >> 5] = lo;
+    red[8 + (tid >> 5)] = hi;
+  }
+  __syncthreads();
+  lo = red[0];
+  hi = red[8];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) {
+    lo = fminf(lo, red[i]);
+    hi = fmaxf(hi, red[8 + i]);
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void row_min_max(const __nv_bfloat16* xr, int k, float& lo, float& hi) {
+  lo = INFINITY;
+  hi = -INFINITY;
+  for (int i = threadIdx.x * 8; i < k; i += 256 * 8) {
     const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      amax = fmaxf(amax, fabsf(__uint_as_float(w[j] << 16)));
-      amax = fmaxf(amax, fabsf(__uint_as_float(w[j] & 0xffff0000u)));
+      const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
+      lo = fminf(lo, fminf(a, b));
+      hi = fmaxf(hi, fmaxf(a, b));
     }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  if ((tid & 31) == 0) red[tid >> 5] = amax;
-  __syncthreads();
-  amax = red[0];
-#pragma unroll
-  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
-  const float scale = __fdiv_rn(amax, 127.0f);
+}
+
+__global__ void __launch_bounds__(256) act_row_range_kernel(const __nv_bfloat16* x, int64_t ldx, int k,
+                                                            float* range) {
+  __shared__ float red[16];
+  float lo, hi;
+  row_min_max(x + static_cast<int64_t>(blockIdx.x) * ldx, k, lo, hi);
+  block_min_max(lo, hi, red);
+  if (threadIdx.x == 0) {
+    range[2 * blockIdx.x] = lo;
+    range[2 * blockIdx.x + 1] = hi;
+  }
+}
+
+// range: null (per token) or the [m_total][2] row ranges of the whole tensor (per tensor)
+template <bool ASYM>
+__global__ void __launch_bounds__(256) quant_act_kernel(const __nv_bfloat16* x, int64_t ldx, int k,
+                                                        int8_t* qa, float* sa, int32_t* zpa,
+                                                        const float* range, int m_total) {
+  __shared__ float red[16];
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* xr = x + static_cast<int64_t>(m) * ldx;
+  float lo, hi;
+  if (range) {
+    lo = INFINITY;
+    hi = -INFINITY;
+    for (int i = tid; i < m_total; i += 256) {
+      lo = fminf(lo, range[2 * i]);
+      hi = fmaxf(hi, range[2 * i + 1]);
+    }
+  } else {
+    row_min_max(xr, k, lo, hi);
+  }
+  block_min_max(lo, hi, red);
+  float scale, zp = 0.f;
+  if (ASYM) {
+    scale = __fdiv_rn(hi - lo, 255.0f);
+    const float z = -rintf(__fdiv_rn(lo, scale));
+    zp = z;
+    if (tid == 0) zpa[m] = scale > 0.f ? static_cast<int32_t>(z) : 0;
+  } else {
+    scale = __fdiv_rn(fmaxf(fabsf(hi), fabsf(lo)), 127.0f);
+  }
   if (tid == 0) sa[m] = scale;
+  const float q_lo = ASYM ? 0.f : -128.f, q_hi = ASYM ? 255.f : 127.f;
   int8_t* qr = qa + static_cast<int64_t>(m) * k;
   for (int i = tid * 8; i < k; i += 256 * 8) {
     const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
@@ -109,18 +170,36 @@ __global__ void __launch_bounds__(256) quant_act_sym_kernel(const __nv_bfloat16*
     uint32_t out[2] = {0u, 0u};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+      const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
       float ql = 0.f, qh = 0.f;
       if (scale > 0.f) {
-        ql = fminf(fmaxf(rintf(__fdiv_rn(lo, scale)), -128.f), 127.f);
-        qh = fminf(fmaxf(rintf(__fdiv_rn(hi, scale)), -128.f), 127.f);
+        ql = fminf(fmaxf(rintf(__fdiv_rn(a, scale) + zp), q_lo), q_hi);
+        qh = fminf(fmaxf(rintf(__fdiv_rn(b, scale) + zp), q_lo), q_hi);
       }
-      const uint32_t b = (static_cast<uint32_t>(static_cast<int>(ql)) & 0xffu) |
+      const uint32_t c = (static_cast<uint32_t>(static_cast<int>(ql)) & 0xffu) |
                          ((static_cast<uint32_t>(static_cast<int>(qh)) & 0xffu) << 8);
-      out[j >> 1] |= b << ((j & 1) * 16);
+      out[j >> 1] |= c << ((j & 1) * 16);
     }
     *reinterpret_cast<uint2*>(qr + i) = make_uint2(out[0], out[1]);
   }
+}
+
+// compensation[n] = sum over k of the weight codes of row n (plain [n][k] int8): what an
+// activation zero point contributes to every accumulator of that row.  One warp per row.
+__global__ void __launch_bounds__(256) weight_row_sum_kernel(const int8_t* w, int n, int k, int32_t* comp) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const int8_t* wr = w + static_cast<int64_t>(row) * k;
+  int sum = 0;
+  for (int i = lane * 16; i < k; i += 32 * 16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(wr + i);
+    const uint32_t q[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sum = __dp4a(static_cast<int>(q[j]), 0x01010101, sum);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) comp[row] = sum;
 }
 
 // ---- tcgen05 int8 GEMM -------------------------------------------------------------------
@@ -145,11 +224,18 @@ __device__ __forceinline__ int i8_owner_of(int64_t b, int64_t total, int64_t cta
   return static_cast<int>(((b + 1) * ctas - 1) / total);
 }
 
+// (acc - compensation[n] * zp_a[tok]) * scale_a[tok] * scale_w[n]: the integer part is exact
+// (csrc/cpu/aten/utils/woq.h:2310-2321)
+__device__ __forceinline__ float i8_scaled(const I8Params& p, int acc, int tok, int n) {
+  if (p.zpa) acc -= p.comp[n] * p.zpa[tok];
+  return (static_cast<float>(acc) * p.sa[tok]) * p.sw[n];
+}
+
 __device__ __forceinline__ void i8_store(const I8Params& p, int tile, int row, int tok, int acc) {
   const int n = tc_tile_row_to_n(p.n, p.gate_up, tile, row);
   if (tok >= p.m || n >= p.n) return;
   // C = bias + (float(acc) * scale_a) * scale_w   (fp32), then bf16 and the post-op
-  float v = (static_cast<float>(acc) * p.sa[tok]) * p.sw[n];
+  float v = i8_scaled(p, acc, tok, n);
   if (p.bias) v = p.bias[n] + v;
   float r = bf16_round(v);
   const size_t o = static_cast<size_t>(tok) * p.ldy + n;
@@ -243,7 +329,8 @@ __global__ void __launch_bounds__(kI8Threads, 1)
       // A token (`issued`) keeps the chunks in order, so the MMA that starts a tile's
       // accumulator runs before any that adds to it.
       const int me = warp == kI8Mma ? 0 : 1;
-      const uint32_t idesc = umma_idesc(p.n_tok, /*s8*/ 1, /*s32*/ 2);
+      // A = weights (s8), B = activations (s8, or u8 when quantised asymmetrically)
+      const uint32_t idesc = umma_idesc(p.n_tok, /*s8*/ 1, p.zpa ? /*u8*/ 0 : /*s8*/ 1, /*s32*/ 2);
       const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
       const uint32_t base_lo = (smem_u32(stages) & 0x3FFFFu) >> 4;
       const uint32_t stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
@@ -325,8 +412,8 @@ __global__ void __launch_bounds__(kI8Threads, 1)
             if (row < 64) {
               const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
               if (n_gate < p.n_out) {
-                float g = (static_cast<float>(v[e]) * p.sa[tok]) * p.sw[n_gate];
-                float u = (static_cast<float>(v_up[e]) * p.sa[tok]) * p.sw[n_up];
+                float g = i8_scaled(p, static_cast<int>(v[e]), tok, n_gate);
+                float u = i8_scaled(p, static_cast<int>(v_up[e]), tok, n_up);
                 if (p.bias) {
                   g = p.bias[n_gate] + g;
                   u = p.bias[n_up] + u;
@@ -506,9 +593,23 @@ cudaError_t launch_pad_scale(const void* src, float* dst, int n, int n_pad, int 
   return cudaGetLastError();
 }
 
-cudaError_t launch_quant_act_sym(const __nv_bfloat16* x, int64_t ldx, int m, int k, int8_t* qa,
-                                 float* sa, cudaStream_t stream) {
-  quant_act_sym_kernel<<<m, 256, 0, stream>>>(x, ldx, k, qa, sa);
+cudaError_t launch_quant_act(const __nv_bfloat16* x, int64_t ldx, int m, int k, int asym, int per_tensor,
+                             int8_t* qa, float* sa, int32_t* zpa, float* range, cudaStream_t stream) {
+  if (per_tensor) {
+    act_row_range_kernel<<<m, 256, 0, stream>>>(x, ldx, k, range);
+    count_launch();
+  }
+  const float* r = per_tensor ? range : nullptr;
+  if (asym)
+    quant_act_kernel<true><<<m, 256, 0, stream>>>(x, ldx, k, qa, sa, zpa, r, m);
+  else
+    quant_act_kernel<false><<<m, 256, 0, stream>>>(x, ldx, k, qa, sa, zpa, r, m);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_weight_row_sum(const int8_t* plain, int n, int k, int32_t* comp, cudaStream_t stream) {
+  weight_row_sum_kernel<<<(n + 7) / 8, 256, 0, stream>>>(plain, n, k, comp);
   count_launch();
   return cudaGetLastError();
 }

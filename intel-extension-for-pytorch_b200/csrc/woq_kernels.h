@@ -117,6 +117,8 @@ struct I8Params {
   const int8_t* wq;     // operand images [tiles64][kc_per_tile][8192]
   const float* sw;      // per-channel weight scales [n_pad]
   const float* sa;      // per-token activation scales [m]
+  const int32_t* zpa;   // per-token activation zero points [m] (asymmetric codes are u8), or null
+  const int32_t* comp;  // with zpa: per-row sums of the weight codes [n_pad]
   const float* bias;
   __nv_bfloat16* y;     // may be null when only the accumulators are wanted
   const __nv_bfloat16* other0;
@@ -137,8 +139,9 @@ cudaError_t launch_unpack_int8(const int8_t* tiled, int8_t* plain, int n, int k,
                                cudaStream_t stream);
 cudaError_t launch_pad_scale(const void* src, float* dst, int n, int n_pad, int dtype,
                              cudaStream_t stream);
-cudaError_t launch_quant_act_sym(const __nv_bfloat16* x, int64_t ldx, int m, int k, int8_t* qa,
-                                 float* sa, cudaStream_t stream);
+cudaError_t launch_quant_act(const __nv_bfloat16* x, int64_t ldx, int m, int k, int asym, int per_tensor,
+                             int8_t* qa, float* sa, int32_t* zpa, float* range, cudaStream_t stream);
+cudaError_t launch_weight_row_sum(const int8_t* plain, int n, int k, int32_t* comp, cudaStream_t stream);
 size_t int8_partial_bytes(int grid, int n_tok);
 cudaError_t launch_int8_tc(I8Params p, const CUtensorMap& qamap, int grid, cudaStream_t stream);
 

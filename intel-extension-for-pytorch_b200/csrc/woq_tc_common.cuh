@@ -99,9 +99,9 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
 
 // Instruction descriptor: dense, M = 128, N = n, K-major A and B.
 // a/b formats: kind::f16 -> 0 f16, 1 bf16; kind::i8 -> 0 u8, 1 s8.  c format: 1 f32, 2 s32.
-__host__ __device__ inline uint32_t umma_idesc(int n, int ab_format, int c_format) {
-  return (static_cast<uint32_t>(c_format) << 4) | (static_cast<uint32_t>(ab_format) << 7) |
-         (static_cast<uint32_t>(ab_format) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+__host__ __device__ inline uint32_t umma_idesc(int n, int a_format, int b_format, int c_format) {
+  return (static_cast<uint32_t>(c_format) << 4) | (static_cast<uint32_t>(a_format) << 7) |
+         (static_cast<uint32_t>(b_format) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(128 >> 4) << 24);
 }
 

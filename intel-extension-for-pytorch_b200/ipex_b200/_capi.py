@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libwoq_b200.so")
 # constants of include/woq_b200.h
 DTYPE_INT8, DTYPE_INT4, DTYPE_NF4, DTYPE_FP8 = 1, 2, 3, 4
 LOWP_NONE, LOWP_FP16, LOWP_BF16, LOWP_INT8 = 0, 1, 2, 3
-ACT_NONE, ACT_PER_M, ACT_PER_M_SYM = -1, 2, 6
+ACT_NONE, ACT_PER_TENSOR, ACT_PER_M, ACT_PER_TENSOR_SYM, ACT_PER_M_SYM = -1, 0, 2, 4, 6
 FMT_PLAIN, FMT_GPTQ, FMT_AWQ = 0, 1, 2
 FUSE_NONE, FUSE_GELU_ERF, FUSE_GELU_TANH, FUSE_RELU, FUSE_SILU = 0, 1, 2, 3, 4
 FUSE_ADD, FUSE_ADD_ADD, FUSE_MUL, FUSE_SILU_MUL = 0x10, 0x20, 0x30, 0x100
@@ -43,6 +43,7 @@ EXPORTS = [
     "woq_b200_moe_expert",
     "woq_b200_dump_dequant",
     "woq_b200_int8_internals",
+    "woq_b200_int8_zero_points",
     "woq_b200_workspace_status",
     "woq_b200_comm_create",
     "woq_b200_comm_export",
@@ -112,6 +113,7 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_moe_expert.argtypes = [vp, vp, vp, i64, vp, vp, i64, vp, i64, vp, sz, vp]
     L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
+    L.woq_b200_int8_zero_points.argtypes = [vp, i64, vp, vp, sz, vp]
     L.woq_b200_workspace_status.argtypes = [vp, vp]
     L.woq_b200_comm_create.argtypes = [i32, i32, i64, sz, ctypes.POINTER(vp)]
     L.woq_b200_comm_export.argtypes = [vp, vp]
@@ -429,6 +431,14 @@ class WoqContext:
                 )
             )
         return qa, sa, acc
+
+    def int8_zero_points(self, m: int) -> torch.Tensor:
+        """Activation zero points the latest INT8 call with m tokens left in this context's workspace."""
+        zp = torch.empty((m,), dtype=torch.int32, device=self.device)
+        ws = self.workspace(m)
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_int8_zero_points(self._h, m, zp.data_ptr(), ws.buf.data_ptr(), ws.nbytes, _stream()))
+        return zp
 
 
 def moe_expert(w13: "WoqContext", w2: "WoqContext", hidden, token_idx, token_weight, out, workspace=None):

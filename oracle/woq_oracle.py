@@ -422,6 +422,23 @@ def dynamic_quant_per_token(
     return q.astype(np.uint8), scale, zp
 
 
+ACT_PER_TENSOR, ACT_PER_M, ACT_PER_TENSOR_SYM, ACT_PER_M_SYM = 0, 2, 4, 6  # woq_defines.h:11-19
+
+
+def dynamic_quant(x: np.ndarray, act_mode: int = ACT_PER_M_SYM):
+    """Activation codes, scales [M] and zero points [M] (None when symmetric) for the
+    per-token modes (2, 6) and the per-tensor modes (0, 4): the per-tensor ones take one range
+    over the whole activation tensor and every row carries the same scale and zero point."""
+    sym = act_mode in (ACT_PER_TENSOR_SYM, ACT_PER_M_SYM)
+    if act_mode in (ACT_PER_M, ACT_PER_M_SYM):
+        return dynamic_quant_per_token(x, sym=sym)
+    assert act_mode in (ACT_PER_TENSOR, ACT_PER_TENSOR_SYM), act_mode
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    q, scale, zp = dynamic_quant_per_token(x.reshape(1, -1), sym=sym)
+    m = x.shape[0]
+    return q.reshape(x.shape), np.repeat(scale, m), None if zp is None else np.repeat(zp, m)
+
+
 # ---------------------------------------------------------------------------------------
 # a9. INT8 x INT8 -> INT32 WOQ linear (WoqLowpMode.INT8, INT8 symmetric per-channel weights)
 # ---------------------------------------------------------------------------------------
@@ -445,19 +462,23 @@ def woq_linear_int8(
     others: Sequence[np.ndarray] = (),
     block_k: int = INT8_BLOCK_K,
     return_acc: bool = False,
+    act_mode: int = ACT_PER_M_SYM,
 ):
-    """INT8 weights (symmetric, per channel), per-token symmetric activation quantisation.
+    """INT8 weights (symmetric, per channel), dynamically quantised activations (per token or
+    per tensor, symmetric or asymmetric).
 
-    Per K block of 128: qC = sum_k qa*qw (int32, exact); C += (float(qC) * scale_a[m]) *
-    scale_w[n] in fp32, blocks taken in k order after the fp32 bias
+    Per K block of 128: qC = sum_k qa*qw (int32, exact); C += (float(qC - comp[n] * zp_a[m]) *
+    scale_a[m]) * scale_w[n] in fp32 with comp[n] the block's sum of weight codes (the term
+    is absent for symmetric activations), blocks taken in k order after the fp32 bias
     (csrc/cpu/aten/utils/woq.h:2231-2354; driver loop :3312-3448), then fp32 -> bf16 and the
-    post-op.
+    post-op.  With return_acc also the whole-K accumulators before compensation, the codes,
+    scales and zero points.
     """
     x = np.ascontiguousarray(x, dtype=np.float32)
     M, K = x.shape
     qw = np.ascontiguousarray(qweight).view(np.int8)
     N = qw.shape[0]
-    qa, sa, _ = dynamic_quant_per_token(x, sym=True)
+    qa, sa, zpa = dynamic_quant(x, act_mode)
     sw = np.asarray(scales, dtype=np.float32).reshape(N)
     C = np.zeros((M, N), dtype=np.float32)
     if bias is not None:
@@ -465,7 +486,11 @@ def woq_linear_int8(
     qa64 = qa.astype(np.float64)  # float64 products and sums of int8 codes are exact
     qw64 = qw.astype(np.float64)
     for k0 in range(0, K, block_k):
-        qc = (qa64[:, k0 : k0 + block_k] @ qw64[:, k0 : k0 + block_k].T).astype(np.float32)
+        qc = qa64[:, k0 : k0 + block_k] @ qw64[:, k0 : k0 + block_k].T
+        if zpa is not None:
+            comp = qw64[:, k0 : k0 + block_k].sum(axis=1)
+            qc = qc - zpa.astype(np.float64)[:, None] * comp[None, :]
+        qc = qc.astype(np.float32)
         C = (C + ((qc * sa[:, None]).astype(np.float32) * sw[None, :]).astype(np.float32)).astype(
             np.float32
         )
@@ -476,6 +501,8 @@ def woq_linear_int8(
     else:
         y = apply_post_op(y, fusion, others)
     if return_acc:
+        if zpa is not None:
+            return y, int8_accumulators(qa, qw), qa, sa, zpa
         return y, int8_accumulators(qa, qw), qa, sa
     return y
 

@@ -31,11 +31,11 @@ def make_layer(n, k, seed, bias=False):
     return dict(qw=qw, s=s, bias=b, n=n, k=k)
 
 
-def make_ctx(capi, layer, flags=0):
+def make_ctx(capi, layer, flags=0, act_mode=None):
     return capi.WoqContext(torch.from_numpy(layer["qw"]).cuda(), torch.from_numpy(layer["s"]).cuda(),
                            None, None if layer["bias"] is None else torch.from_numpy(layer["bias"]).cuda(),
                            layer["n"], layer["k"], capi.DTYPE_INT8, -1, capi.LOWP_INT8,
-                           act_quant_mode=capi.ACT_PER_M_SYM, layout_flags=flags)
+                           act_quant_mode=capi.ACT_PER_M_SYM if act_mode is None else act_mode, layout_flags=flags)
 
 
 def check(y, y_ref):
@@ -114,6 +114,55 @@ def test_fused_post_ops(capi, fusion, n_others):
     assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)
 
 
+# The other activation quantisation modes of the reference that share the whole-K accumulators:
+# per tensor (0 asymmetric, 4 symmetric) and per token asymmetric (2).  Asymmetric codes are
+# unsigned with a zero point, taken out again with the per-row sums of the weight codes.
+@pytest.mark.parametrize("act_mode", [0, 2, 4])
+@pytest.mark.parametrize("m,n,k", [(1, 96, 256), (8, 640, 1024), (64, 1536, 4096), (300, 640, 1024)])
+def test_activation_modes_internals_bit_exact(capi, act_mode, m, n, k):
+    layer = make_layer(n, k, seed=5 * n + m + act_mode)
+    ctx = make_ctx(capi, layer, act_mode=act_mode)
+    x = make_acts(m, k, seed=m + n + act_mode)
+    x += 0.37  # a range that is not centred on zero, so the zero points matter
+    x = O.rne_bf16(x)
+    qa, sa, acc = ctx.int8_internals(bf16_tensor(x, "cuda"))
+    zp = ctx.int8_zero_points(m)
+    ctx.workspace(m).status()
+    qa_ref, sa_ref, zp_ref = O.dynamic_quant(x, act_mode)
+    codes = qa.cpu().numpy()
+    np.testing.assert_array_equal(codes.view(qa_ref.dtype), qa_ref)
+    np.testing.assert_array_equal(sa.cpu().numpy(), sa_ref)
+    if zp_ref is None:
+        assert not zp.any()
+    else:
+        np.testing.assert_array_equal(zp.cpu().numpy(), zp_ref)
+    np.testing.assert_array_equal(acc.cpu().numpy(), O.int8_accumulators(qa_ref, layer["qw"]))
+
+
+@pytest.mark.parametrize("act_mode", [0, 2, 4])
+@pytest.mark.parametrize("m", [1, 8, 64, 512])
+def test_activation_modes_outputs(capi, act_mode, m):
+    layer = make_layer(1024, 2048, seed=17 + act_mode, bias=True)
+    ctx = make_ctx(capi, layer, act_mode=act_mode)
+    x = O.rne_bf16(make_acts(m, 2048, seed=40 + m) + 0.25)
+    resid = make_acts(m, 1024, seed=41 + m)
+    y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda"), capi.FUSE_ADD, [bf16_tensor(resid, "cuda")]))
+    ctx.workspace(m).status()
+    check_tol = O.parity_metrics(y, O.woq_linear_int8(x, layer["qw"], layer["s"], layer["bias"], O.FUSE_ADD, [resid],
+                                                      act_mode=act_mode))
+    assert check_tol[0] <= O.MAX_ABS_TOL and check_tol[1] <= O.MEAN_REL_TOL, check_tol
+
+
+def test_asymmetric_gate_up_silu_mul(capi):
+    layer = make_layer(1024, 1024, seed=23)
+    ctx = make_ctx(capi, layer, flags=capi.LAYOUT_GATE_UP, act_mode=capi.ACT_PER_M)
+    x = O.rne_bf16(make_acts(24, 1024, seed=24) - 0.3)
+    y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda"), capi.FUSE_SILU_MUL))
+    mx, mr = O.parity_metrics(y, O.woq_linear_int8(x, layer["qw"], layer["s"], None, O.FUSE_SILU_MUL,
+                                                   act_mode=O.ACT_PER_M))
+    assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)
+
+
 def test_unsupported_modes_are_reported(capi):
     layer = make_layer(64, 128, seed=1)
     qw, s = torch.from_numpy(layer["qw"]).cuda(), torch.from_numpy(layer["s"]).cuda()
@@ -121,5 +170,5 @@ def test_unsupported_modes_are_reported(capi):
         capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_BF16)
     assert e.value.code == 2
     with pytest.raises(capi.WoqError) as e:
-        capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_INT8, act_quant_mode=2)
-    assert e.value.code == 2
+        capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_INT8, act_quant_mode=7)
+    assert e.value.code == 2  # the per-K-block modes are not built

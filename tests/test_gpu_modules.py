@@ -231,18 +231,19 @@ def test_gptq_act_order_g_idx(ipex):
     assert torch.equal(y3, y)
 
 
-def test_int8_lowp_module(ipex):
+@pytest.mark.parametrize("act_mode", ["PER_BATCH_SYM", "PER_BATCH", "PER_TENSOR_SYM", "PER_TENSOR"])
+def test_int8_lowp_module(ipex, act_mode):
     q = ipex.quantization
     lin = make_linear(384, 1024, True, seed=9)
     ref = copy.deepcopy(lin)
+    mode = getattr(q.WoqActQuantMode, act_mode)
     lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
-        weight_dtype=q.WoqWeightDtype.INT8, lowp_mode=q.WoqLowpMode.INT8,
-        act_quant_mode=q.WoqActQuantMode.PER_BATCH_SYM).global_qconfig
+        weight_dtype=q.WoqWeightDtype.INT8, lowp_mode=q.WoqLowpMode.INT8, act_quant_mode=mode).global_qconfig
     mod = ipex.nn.modules.WeightOnlyQuantizedLinear.from_float(lin)
-    x = make_acts(33, 1024, seed=3)
+    x = O.rne_bf16(make_acts(33, 1024, seed=3) + 0.2)
     y = bf16_numpy(mod(bf16_tensor(x, "cuda")))
     qw, s, _ = O.quantize_per_channel(ref.weight.detach().numpy(), O.WOQ_DTYPE_INT8, sym=True)
-    parity(y, O.woq_linear_int8(x, qw, s, ref.bias.detach().numpy()))
+    parity(y, O.woq_linear_int8(x, qw, s, ref.bias.detach().numpy(), act_mode=int(mode)))
 
 
 def test_op_context_pickles_in_plain_format(ipex):

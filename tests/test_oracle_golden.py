@@ -144,3 +144,23 @@ def test_act_order_dequant_matches_a_per_element_restatement():
     ident = np.arange(k) // g
     np.testing.assert_array_equal(O.dequantize_weight_act_order(qw, s, z, ident, k),
                                   O.dequantize_weight(qw, s, z, O.WOQ_DTYPE_INT4, k, g))
+
+
+@pytest.mark.parametrize("act_mode", [O.ACT_PER_TENSOR, O.ACT_PER_M, O.ACT_PER_TENSOR_SYM, O.ACT_PER_M_SYM])
+def test_int8_activation_modes_of_the_oracle(act_mode):
+    """Codes, scales and zero points of every activation mode reproduce x to half a step, the
+    per-tensor modes carry one scale, and the compensated INT8 linear tracks the float one."""
+    rng = np.random.default_rng(act_mode)
+    x = O.rne_bf16((rng.standard_normal((6, 512)) + 0.4).astype(np.float32))
+    q, s, zp = O.dynamic_quant(x, act_mode)
+    sym = act_mode in (O.ACT_PER_TENSOR_SYM, O.ACT_PER_M_SYM)
+    assert q.dtype == (np.int8 if sym else np.uint8) and (zp is None) == sym
+    if act_mode in (O.ACT_PER_TENSOR, O.ACT_PER_TENSOR_SYM):
+        assert np.unique(s).size == 1 and (zp is None or np.unique(zp).size == 1)
+    back = (q.astype(np.float32) - (0 if zp is None else zp[:, None])) * s[:, None]
+    assert np.abs(back - x).max() <= 0.5001 * s.max()
+    w = (rng.standard_normal((64, 512)) * 0.02).astype(np.float32)
+    qw, sw, _ = O.quantize_per_channel(w, O.WOQ_DTYPE_INT8, sym=True)
+    y = O.woq_linear_int8(x, qw, sw, None, act_mode=act_mode)
+    ref = x @ (qw.view(np.int8).astype(np.float32) * sw.reshape(-1, 1)).T
+    assert np.abs(y - ref).max() <= 0.03 * np.abs(ref).max()
