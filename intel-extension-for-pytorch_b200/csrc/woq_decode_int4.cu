@@ -217,32 +217,38 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
         for (int i = 0; i < 8; ++i) out[h + i] = 0u;
         continue;
       }
-      float r0[8], r1[8], f0[8], f1[8];
+      // raw bf16 bits here, converted where they are used: a conversion inside the guarded
+      // load loop would wait for its load before the next one is issued
+      float r0[8], r1[8];
+      uint32_t f0[8], f1[8], wr[8];  // one register each: packed halves would tie a load to its neighbour
+      const auto bf = [](uint32_t b) { return __uint_as_float(b << 16); };
       auto load_rows = [&](const __nv_bfloat16* src, int64_t ld) {
+        const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
             const size_t o = static_cast<size_t>(h + i) * ld;
-            f0[i] = __bfloat162float(src[o + c0]);
-            f1[i] = __bfloat162float(src[o + c1]);
+            f0[i] = s16[o + c0];
+            f1[i] = s16[o + c1];
           }
       };
       int rows[8];
-      float w[8];
       if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
         // y[row_idx[tok]] += result * row_w[tok]; the rows of one call are distinct
+        const unsigned short* y16 = reinterpret_cast<const unsigned short*>(p.y);
+        const unsigned short* w16 = reinterpret_cast<const unsigned short*>(p.row_w);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
             rows[i] = p.row_idx[h + i];
-            w[i] = __bfloat162float(p.row_w[h + i]);
+            wr[i] = w16[h + i];
           }
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
             const size_t o = static_cast<size_t>(rows[i]) * p.ldy;
-            f0[i] = __bfloat162float(p.y[o + c0]);
-            f1[i] = __bfloat162float(p.y[o + c1]);
+            f0[i] = y16[o + c0];
+            f1[i] = y16[o + c1];
           }
       } else if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD || p.fusion == FUSE_MUL) {
         load_rows(p.other0, p.ldo);
@@ -258,14 +264,14 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
           v0 = bf16_round(v0);
           v1 = bf16_round(v1);
           if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
-            v0 = f0[i] + v0 * w[i];
-            v1 = f1[i] + v1 * w[i];
+            v0 = bf(f0[i]) + v0 * bf(wr[i]);
+            v1 = bf(f1[i]) + v1 * bf(wr[i]);
           } else if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
-            v0 = bf16_round(v0 + f0[i]);
-            v1 = bf16_round(v1 + f1[i]);
+            v0 = bf16_round(v0 + bf(f0[i]));
+            v1 = bf16_round(v1 + bf(f1[i]));
           } else if (p.fusion == FUSE_MUL) {
-            v0 = bf16_round(v0 * f0[i]);
-            v1 = bf16_round(v1 * f1[i]);
+            v0 = bf16_round(v0 * bf(f0[i]));
+            v1 = bf16_round(v1 * bf(f1[i]));
           } else {
             v0 = unary_post_op(v0, p.fusion);
             v1 = unary_post_op(v1, p.fusion);
@@ -278,8 +284,8 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
-            r0[i] = bf16_round(r0[i] + f0[i]);
-            r1[i] = bf16_round(r1[i] + f1[i]);
+            r0[i] = bf16_round(r0[i] + bf(f0[i]));
+            r1[i] = bf16_round(r1[i] + bf(f1[i]));
           }
       }
 #pragma unroll
