@@ -692,7 +692,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--m", type=int, default=1, help="decode batch (tokens per step)")
+    ap.add_argument("--m", "--tokens", dest="m", type=int, default=1,
+                    help="decode batch (tokens per step); spell it --tokens under torch.distributed.run")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="phase messages on stderr")

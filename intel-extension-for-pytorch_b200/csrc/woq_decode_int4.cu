@@ -108,6 +108,20 @@ __device__ __forceinline__ uint32_t comm_wait_word(const uint2* w, uint32_t stam
   }
 }
 
+// The words of tokens h .. h+7 from source rank r: one load each, all in flight together,
+// then the bounded wait only for those that had not arrived.
+template <typename WordAt>
+__device__ __forceinline__ void comm_wait_words8(WordAt word_at, int h, int m, uint32_t stamp, int* status,
+                                                 uint32_t* data) {
+  uint2 v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (h + i < m) v[i] = ld_relaxed_sys_v2(word_at(h + i));
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (h + i < m) data[i] = v[i].y == stamp ? v[i].x : comm_wait_word(word_at(h + i), stamp, status);
+}
+
 // The stages a CTA walks: its share [b_begin, b_end) of the k-block sequence cut at tile
 // boundaries ("segments") and then into runs of up to kStageKBlocks k-blocks.  Producer and
 // consumers step through the same sequence.
@@ -156,24 +170,38 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
                               make_uint2(mine[tok], stamp));
       }
 #pragma unroll
-    for (int tok = 0; tok < NTOK; ++tok)
-      if (tok < p.m) {
-        float s0 = 0.f, s1 = 0.f;
-        for (int r = 0; r < c.world; ++r) {
-          const uint32_t w = r == c.rank ? mine[tok]
-                                         : comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane),
-                                                          stamp, p.status);
-          s0 += __uint_as_float(w << 16);
-          s1 += __uint_as_float(w & 0xffff0000u);
+    for (int h = 0; h < NTOK; h += 8) {
+      if (h >= p.m) continue;
+      float s0[8], s1[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s0[i] = s1[i] = 0.f;
+      for (int r = 0; r < c.world; ++r) {
+        uint32_t w[8];
+        if (r == c.rank) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = mine[h + i];
+        } else {
+          comm_wait_words8([&](int tok) { return comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane); }, h,
+                           p.m, stamp, p.status, w);
         }
-        a0[tok] = bf16_round(s0);
-        a1[tok] = bf16_round(s1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            s0[i] += __uint_as_float(w[i] << 16);
+            s1[i] += __uint_as_float(w[i] & 0xffff0000u);
+          }
       }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (h + i < p.m) {
+          a0[h + i] = bf16_round(s0[i]);
+          a1[h + i] = bf16_round(s1[i]);
+        }
+    }
   }
   // Words for the gather: the two results of this lane per token.  Everything the epilogue
-  // reads from global memory (bias, fused operands, scatter rows) is loaded for all tokens
-  // before the first value is used: one round trip instead of one per token.  Loads of
-  // tokens or rows that do not exist are clamped to ones that do and never stored.
+  // reads from global memory (bias, fused operands, scatter rows) is loaded for up to eight
+  // tokens before the first value is used: one round trip instead of one per token.
   uint32_t out[NTOK];
   if (p.fusion == FUSE_SILU_MUL) {
     // gate/up layout: row lane is a gate row, row lane + 32 its up row
@@ -325,12 +353,19 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
       if (r == c.rank) continue;
       __nv_bfloat16* dst = p.y + (static_cast<int64_t>(r) - c.rank) * p.n_out;
 #pragma unroll
-      for (int tok = 0; tok < NTOK; ++tok)
-        if (tok < p.m) {
-          const uint32_t w = comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane), stamp, p.status);
-          if (c0 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w & 0xffffu));
-          if (pair && c1 < p.n_out) dst[static_cast<size_t>(tok) * p.ldy + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w >> 16));
-        }
+      for (int h = 0; h < NTOK; h += 8) {
+        if (h >= p.m) continue;
+        uint32_t w[8];
+        comm_wait_words8([&](int tok) { return comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane); }, h, p.m,
+                         stamp, p.status, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (h + i < p.m) {
+            const size_t o = static_cast<size_t>(h + i) * p.ldy;
+            if (c0 < p.n_out) dst[o + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w[i] & 0xffffu));
+            if (pair && c1 < p.n_out) dst[o + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w[i] >> 16));
+          }
+      }
     }
   }
 }
