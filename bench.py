@@ -37,6 +37,7 @@ METRIC = "int4_woq_linear_weight_GBps_decode"
 # zero point per row and group against 3 algorithmic ones, and split-K partial tiles are
 # written and read back); the traffic of a launch grows in proportion to its bytes.
 TRAFFIC_RATIO = 1.041
+FUSED_MAX_TOKENS = 8  # --collective auto: largest decode batch that takes the fused exchange
 UNIT = "GB/s"
 
 
@@ -237,7 +238,12 @@ def run_ours(args):
     # With more than one GPU the exchange is part of the linear kernels' epilogue (stores into the
     # peers' buffers over NVLink); `--collective nccl` runs the NCCL collectives after the
     # kernels instead, for comparison.
-    fused = p > 1 and args.collective == "fused" and m <= 16
+    # "auto": the fused exchange up to FUSED_MAX_TOKENS tokens, NCCL above (measured at two GPUs:
+    # the fused step wins by 28 % at one token and by 8 % at eight, and loses by 13 % at sixteen,
+    # where the epilogue warp's per-tile wait for the peer outweighs the saved collective
+    # launches).
+    want_fused = args.collective == "fused" or (args.collective == "auto" and m <= FUSED_MAX_TOKENS)
+    fused = p > 1 and want_fused and m <= 16
     comm = None
     if fused:
         act_off = (m * QKV_N * 2 + 255) // 256 * 256
@@ -697,8 +703,9 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="phase messages on stderr")
-    ap.add_argument("--collective", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: exchange inside the linear kernels, or NCCL after them")
+    ap.add_argument("--collective", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N > 1: exchange inside the linear kernels, NCCL after them, or (auto) the "
+                         "fused exchange up to %d tokens" % FUSED_MAX_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (tensor-core kernel) side line")
     ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
