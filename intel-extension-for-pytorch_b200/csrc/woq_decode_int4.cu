@@ -839,8 +839,6 @@ int env_int(const char* name, int fallback) {
   return e ? atoi(e) : fallback;
 }
 
-// consumer warps take two adjacent k-blocks per stage while x is small enough to leave room
-// for three 32 KB stages
 // bytes of one pipeline stage / of the cross-warp reduction buffer
 int stage_bytes_for(int m, int kpw, int kbpg_shift) {
   const int gps = (stage_kblocks(kpw) >> kbpg_shift) + 1;
