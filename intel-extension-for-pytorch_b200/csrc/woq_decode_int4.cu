@@ -237,7 +237,10 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
     }
     // Eight tokens at a time (register budget).  Loads sit in loops of their own, guarded per
     // token, so that those of all existing tokens are in flight together; the arithmetic
-    // follows in a second guarded loop.
+    // follows in guarded loops.  Raw bf16 bits here, converted where they are used: a
+    // conversion inside the guarded load loop would wait for its load before the next one is
+    // issued.
+    const auto bf = [](uint32_t b) { return __uint_as_float(b << 16); };
 #pragma unroll
     for (int h = 0; h < NTOK; h += 8) {
       if (h >= p.m) {
@@ -245,11 +248,8 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
         for (int i = 0; i < 8; ++i) out[h + i] = 0u;
         continue;
       }
-      // raw bf16 bits here, converted where they are used: a conversion inside the guarded
-      // load loop would wait for its load before the next one is issued
-      float r0[8], r1[8];
       uint32_t f0[8], f1[8], wr[8];  // one register each: packed halves would tie a load to its neighbour
-      const auto bf = [](uint32_t b) { return __uint_as_float(b << 16); };
+      int rows[8];
       auto load_rows = [&](const __nv_bfloat16* src, int64_t ld) {
         const unsigned short* s16 = reinterpret_cast<const unsigned short*>(src);
 #pragma unroll
@@ -260,7 +260,6 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
             f1[i] = s16[o + c1];
           }
       };
-      int rows[8];
       if (p.fusion == FUSE_SCALED_SCATTER_ADD) {
         // y[row_idx[tok]] += result * row_w[tok]; the rows of one call are distinct
         const unsigned short* y16 = reinterpret_cast<const unsigned short*>(p.y);
@@ -304,23 +303,23 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
             v0 = unary_post_op(v0, p.fusion);
             v1 = unary_post_op(v1, p.fusion);
           }
-          r0[i] = v0;
-          r1[i] = v1;
+          a0[h + i] = v0;
+          a1[h + i] = v1;
         }
       if (p.fusion == FUSE_ADD_ADD) {
         load_rows(p.other1, p.ldo);
 #pragma unroll
         for (int i = 0; i < 8; ++i)
           if (h + i < p.m) {
-            r0[i] = bf16_round(r0[i] + bf(f0[i]));
-            r1[i] = bf16_round(r1[i] + bf(f1[i]));
+            a0[h + i] = bf16_round(a0[h + i] + bf(f0[i]));
+            a1[h + i] = bf16_round(a1[h + i] + bf(f1[i]));
           }
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         out[h + i] = 0u;
         if (h + i < p.m) {
-          const __nv_bfloat16 v0 = __float2bfloat16_rn(r0[i]), v1 = __float2bfloat16_rn(r1[i]);
+          const __nv_bfloat16 v0 = __float2bfloat16_rn(a0[h + i]), v1 = __float2bfloat16_rn(a1[h + i]);
           const size_t o = static_cast<size_t>(p.fusion == FUSE_SCALED_SCATTER_ADD ? rows[i] : h + i) * p.ldy;
           if (ok0) p.y[o + n0] = v0;
           if (ok1) p.y[o + n1] = v1;
