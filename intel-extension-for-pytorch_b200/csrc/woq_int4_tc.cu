@@ -90,6 +90,45 @@ __device__ __forceinline__ void tc_store(const TcParams& p, int tile, int row, i
   p.y[o] = __float2bfloat16_rn(r);
 }
 
+// Eight tokens (chunk ch) of one row: the fused operands of all eight are loaded before the
+// first is used (raw bits, converted at use), so the chunk costs one global round trip, not
+// one per token.  The scatter epilogue keeps the per-token routine (its rows come from a table).
+__device__ __forceinline__ void tc_store8(const TcParams& p, int tile, int row, int ch, const float* v) {
+  const bool binary = p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD || p.fusion == FUSE_MUL;
+  const int n = tc_row_to_n(p, tile, row);
+  if (!binary || n >= p.n) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) tc_store(p, tile, row, ch * 8 + e, v[e]);
+    return;
+  }
+  const unsigned short* o0 = reinterpret_cast<const unsigned short*>(p.other0);
+  const unsigned short* o1 = reinterpret_cast<const unsigned short*>(p.other1);
+  uint32_t f[8], g[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    if (ch * 8 + e < p.m) {
+      const size_t o = static_cast<size_t>(ch * 8 + e) * p.ldy + n;
+      f[e] = o0[o];
+      if (p.fusion == FUSE_ADD_ADD) g[e] = o1[o];
+    }
+  const float b = p.bias ? p.bias[n] : 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    if (ch * 8 + e < p.m) {
+      float r = v[e];
+      if (p.bias) r += b;
+      r = bf16_round(r);
+      const float a = __uint_as_float(f[e] << 16);
+      if (p.fusion == FUSE_MUL) {
+        r = bf16_round(r * a);
+      } else {
+        r = bf16_round(r + a);
+        if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __uint_as_float(g[e] << 16));
+      }
+      p.y[static_cast<size_t>(ch * 8 + e) * p.ldy + n] = __float2bfloat16_rn(r);
+    }
+}
+
 // Timeline probe for experiments (debug bit 64): CTA 0 writes cycle stamps of its first 64
 // stages into the partial-tile area, [role][stage][4].
 __device__ __forceinline__ void tc_stamp(const TcParams& p, int role, int stage, int k) {
@@ -319,11 +358,15 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             v_up[e] += part_up[e];
           }
         }
+        if (p.fusion != FUSE_SILU_MUL) {
+          tc_store8(p, t, row, ch, v);
+          continue;
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int tok = ch * 8 + e;
           if (tok >= p.m) break;
-          if (p.fusion == FUSE_SILU_MUL) {
+          {
             if (row < 64) {
               const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
               float g = v[e], u = v_up[e];
@@ -336,8 +379,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                 p.y[static_cast<size_t>(tok) * p.ldy + n_gate] =
                     __float2bfloat16_rn(up * silu_bf16(gate));
             }
-          } else {
-            tc_store(p, t, row, tok, v[e]);
           }
         }
       }
@@ -398,8 +439,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           for (int ch = wg; ch < n_chunks; ch += kWarpGroups) {
             float v[8];
             load_acc(ch, n_used, v);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) tc_store(p, tile, row, ch * 8 + e, v[e]);
+            tc_store8(p, tile, row, ch, v);
           }
           tc_fence_before_sync();
           __syncwarp();

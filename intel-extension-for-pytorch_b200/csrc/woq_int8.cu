@@ -250,6 +250,49 @@ __device__ __forceinline__ void i8_store(const I8Params& p, int tile, int row, i
   p.y[o] = __float2bfloat16_rn(r);
 }
 
+// Eight tokens (chunk ch) of one row, four at a time: the fused operands of four tokens are
+// loaded before the first is used (raw bits, converted at use), so they cost one global round
+// trip, not one per token (four, not eight: the kernel has no registers to spare).
+__device__ __forceinline__ void i8_store8(const I8Params& p, int tile, int row, int ch, const int* acc) {
+  const bool binary = p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD || p.fusion == FUSE_MUL;
+  const int n = tc_tile_row_to_n(p.n, p.gate_up, tile, row);
+  if (!binary || n >= p.n || p.m <= 16) {  // few tokens: the plain routine is as fast
+#pragma unroll
+    for (int e = 0; e < 8; ++e) i8_store(p, tile, row, ch * 8 + e, acc[e]);
+    return;
+  }
+  const unsigned short* o0 = reinterpret_cast<const unsigned short*>(p.other0);
+  const unsigned short* o1 = reinterpret_cast<const unsigned short*>(p.other1);
+#pragma unroll
+  for (int h = 0; h < 8; h += 4) {
+    uint32_t f[4];
+    float r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (ch * 8 + h + e < p.m) f[e] = o0[static_cast<size_t>(ch * 8 + h + e) * p.ldy + n];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (ch * 8 + h + e < p.m) {
+        float v = i8_scaled(p, acc[h + e], ch * 8 + h + e, n);
+        if (p.bias) v = p.bias[n] + v;
+        const float a = __uint_as_float(f[e] << 16);
+        r[e] = p.fusion == FUSE_MUL ? bf16_round(bf16_round(v) * a) : bf16_round(bf16_round(v) + a);
+      }
+    if (p.fusion == FUSE_ADD_ADD) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (ch * 8 + h + e < p.m) f[e] = o1[static_cast<size_t>(ch * 8 + h + e) * p.ldy + n];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (ch * 8 + h + e < p.m) r[e] = bf16_round(r[e] + __uint_as_float(f[e] << 16));
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (ch * 8 + h + e < p.m)
+        p.y[static_cast<size_t>(ch * 8 + h + e) * p.ldy + n] = __float2bfloat16_rn(r[e]);
+  }
+}
+
 __global__ void __launch_bounds__(kI8Threads, 1)
     woq_int8_tc_kernel(const I8Params p, const __grid_constant__ CUtensorMap qamap) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -404,11 +447,15 @@ __global__ void __launch_bounds__(kI8Threads, 1)
             v_up[e] += part_up[e];
           }
         }
+        if (p.fusion != FUSE_SILU_MUL) {
+          i8_store8(p, t, row, ch, v);
+          continue;
+        }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int tok = ch * 8 + e;
           if (tok >= p.m) break;
-          if (p.fusion == FUSE_SILU_MUL) {
+          {
             if (row < 64) {
               const int n_gate = t * 64 + row, n_up = p.n / 2 + n_gate;
               if (n_gate < p.n_out) {
@@ -422,8 +469,6 @@ __global__ void __launch_bounds__(kI8Threads, 1)
                     __float2bfloat16_rn(bf16_round(u) * silu_bf16(bf16_round(g)));
               }
             }
-          } else {
-            i8_store(p, t, row, tok, v[e]);
           }
         }
       }
@@ -448,8 +493,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
               }
             }
             if (p.y) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) i8_store(p, tile, row, ch * 8 + e, static_cast<int>(v[e]));
+              i8_store8(p, tile, row, ch, reinterpret_cast<const int*>(v));
             }
           }
           tc_fence_before_sync();
