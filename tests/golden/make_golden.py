@@ -150,4 +150,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of intel-extension-for-pytorch>")
+    main(sys.argv[1])
