@@ -601,7 +601,7 @@ def run_configs(args):
         qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
         tiling = capi.LAYOUT_STREAM_ONLY if m <= 16 else capi.LAYOUT_TC_ONLY
         return capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP, capi.LOWP_BF16,
-                               layout_flags=tiling | gate_up)
+                               layout_flags=tiling | gate_up, kernel_hint=args.hint if m <= 16 else 0)
 
     def report(config, name, n, k, kind, fusion, m, us, wbytes, total, flops, note=None):
         ai = flops / total
@@ -609,6 +609,7 @@ def run_configs(args):
         bound = "tensor" if ai > peak_tf * 1e3 / hbm else "hbm"
         frac = (flops / us / 1e6) / peak_tf if bound == "tensor" else (total / us / 1e3) / hbm
         line = {"config": config, "linear": name, "n": n, "k": k, "weights": kind, "fusion": fusion, "m": m,
+                "hint": args.hint, "split": args.split,
                 "us": round(us, 2), "weight_GBps": round(wbytes / us / 1e3, 1),
                 "total_GBps": round(total / us / 1e3, 1), "tflops": round(flops / us / 1e6, 2),
                 "bound": bound, "frac_of_" + which: round(frac, 3)}
@@ -625,6 +626,8 @@ def run_configs(args):
         n_out = n // 2 if fusion == "silu_mul" else n
         ctxs, tiling_m = [], None
         for m in ms:
+            if m > args.max_m:
+                continue
             if kind == "int8" or tiling_m is None or (tiling_m <= 16) != (m <= 16):
                 for c in ctxs:
                     c.close()
@@ -656,6 +659,8 @@ def run_configs(args):
     for e in range(n_exp):
         experts.append((make_ctx(2 * ffn, hid, "int4", "silu_mul", 1, 100 + e), make_ctx(hid, ffn, "int4", "none", 1, 200 + e)))
     for t in MOE_TOKENS:
+        if t > args.max_m:
+            continue
         if t > 16:  # the expert linears switch tiling with the token count
             for a, b in experts:
                 a.close()
@@ -711,11 +716,18 @@ def main():
     ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
     ap.add_argument("--int8", action="store_true", help="--single: INT8 weights with INT8 compute")
     ap.add_argument("--hint", type=int, default=0, help="--single: kernel hint (see include/woq_b200.h)")
+    ap.add_argument("--max-m", type=int, default=1 << 30, help="--configs: skip token counts above this")
+    ap.add_argument("--split", type=int, default=None, choices=[0, 1, 2],
+                    help="decode kernel's K split: 0 per layer, 1 stream-K, 2 clusters (woq_b200_set_option)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per launch from an ncu capture (default: TRAFFIC_RATIO x algorithmic bytes)")
     ap.add_argument("--configs", default=None, nargs="?", const="all",
                     help="time every benchmark configuration's linears (optionally a prefix: c1, c2, c3, c4, c5)")
     args = ap.parse_args()
+    if args.split is not None:
+        from ipex_b200 import _capi
+
+        _capi.set_option(_capi.OPT_DECODE_SPLIT, args.split)
     if args.configs:
         run_configs(args)
     elif args.single:

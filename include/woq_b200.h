@@ -135,6 +135,17 @@ const char* woq_b200_last_error(void);
 /* Number of kernels this library has launched in this process (all threads). */
 int64_t woq_b200_kernel_launches(void);
 
+/* Process-wide tuning switches.  No reference counterpart (the reference reads its tuning from
+ * environment variables, e.g. csrc/cpu/aten/utils/woq.h block-size getters).  Set them while no
+ * call of this library is in flight on another host thread.
+ *   WOQ_B200_OPT_DECODE_SPLIT: how the M <= 16 INT4 kernel cuts a layer whose K range is
+ *     shared by several thread blocks.  0 (default, or WOQ_B200_DECODE_SPLIT in the
+ *     environment at load time): chosen per layer; 1: always the stream-K grid that reduces
+ *     split tiles through the workspace; 2: thread-block clusters that reduce through
+ *     distributed shared memory whenever the layer has at most two tiles per SM. */
+#define WOQ_B200_OPT_DECODE_SPLIT 1
+int woq_b200_set_option(int32_t option, int32_t value);
+
 /* Repack a plain quantised weight into the tiled device layout and keep bf16 scales,
  * zero points and fp32 bias beside it.  Replaces woq_linear_pack_weight + qlinear_woq_pack
  * (csrc/cpu/aten/Linear.cpp:379-438, csrc/cpu/aten/kernels/WoqUtilKrnl.cpp:32-249) and the
@@ -277,6 +288,12 @@ int woq_b200_int8_internals(const woq_b200_ctx* ctx, const void* x, int64_t m, i
  * tokens left there; zeros for the symmetric modes. */
 int woq_b200_int8_zero_points(const woq_b200_ctx* ctx, int64_t m, int32_t* zp, const void* workspace,
                               size_t workspace_bytes, void* stream);
+
+/* How woq_b200_linear would launch the M <= 16 INT4 kernel for this context on the current
+ * device (no reference counterpart; a diagnostic): out[0] thread blocks, out[1] thread blocks
+ * per cluster (0: the stream-K grid), out[2] k-blocks per warp and pipeline stage, out[3] the
+ * shared-memory budget per thread block in bytes. */
+int woq_b200_decode_plan(const woq_b200_ctx* ctx, int64_t m, int32_t* out);
 
 /* Reads the status word of a workspace (synchronises the stream).  WOQ_B200_OK, or
  * WOQ_B200_ERR_DEVICE_WAIT when a bounded wait inside a kernel gave up; the word is cleared. */

@@ -204,6 +204,15 @@ int64_t woq_b200_kernel_launches(void) { return woq::g_launches.load(); }
 
 size_t woq_b200_workspace_header_bytes(void) { return kWsHeaderBytes; }
 
+int woq_b200_set_option(int32_t option, int32_t value) {
+  if (option == WOQ_B200_OPT_DECODE_SPLIT) {
+    if (value < 0 || value > 2) return fail(WOQ_B200_ERR_INVALID_ARG, "decode split must be 0, 1 or 2, got %d", value);
+    woq::decode_int4_set_split(value);
+    return WOQ_B200_OK;
+  }
+  return fail(WOQ_B200_ERR_INVALID_ARG, "unknown option %d", option);
+}
+
 int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void* scales,
                         const void* zero_points, const void* bias, void* stream_,
                         woq_b200_ctx** out) {
@@ -475,13 +484,17 @@ static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t l
   p.fusion = fusion;
   p.gate_up = c->gate_up;
   p.exact = c->desc.kernel_hint == WOQ_B200_HINT_STREAM_FAST ? 0 : c->plain_scales ? 2 : 1;
-  p.unit = woq::decode_int4_unit((int)m, c->kb_per_group);
+#ifdef WOQ_B200_TIMELINE
+  {
+    const size_t need = woq_b200_workspace_bytes(c, m), extra = 8 * 1024 * 8 * sizeof(unsigned long long);
+    p.stamps = ws_bytes >= need + extra ? reinterpret_cast<unsigned long long*>(w8 + (need + 255) / 256 * 256) : nullptr;
+  }
+#endif
   if (comm) p.comm = *comm;
   if (ldo_override) p.ldo = ldo_override;
   if (bias_override) p.bias = bias_override;
-  woq::DecodeShape shape{(int)m, c->tiles, c->kb_per_tile, p.unit};
-  const int grid = woq::decode_int4_pick_grid(shape, c->num_sms);
-  CUDA_TRY(woq::launch_decode_int4(p, grid, stream));
+  const woq::DecodePlan plan = woq::decode_int4_plan((int)m, c->tiles, c->kb_per_tile, c->kb_per_group, c->num_sms);
+  CUDA_TRY(woq::launch_decode_int4(p, plan, stream));
   woq::count_launch();
   return WOQ_B200_OK;
 }
@@ -962,6 +975,18 @@ int woq_b200_int8_zero_points(const woq_b200_ctx* c, int64_t m, int32_t* zp, con
   } else {
     CUDA_TRY(cudaMemsetAsync(zp, 0, static_cast<size_t>(m) * sizeof(int32_t), stream));
   }
+  return WOQ_B200_OK;
+}
+
+int woq_b200_decode_plan(const woq_b200_ctx* c, int64_t m, int32_t* out) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!out || m < 1 || m > 16 || c->is_int8 || !c->wq)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "decode plan: INT4 context with the streaming layout, 1..16 tokens");
+  const woq::DecodePlan plan = woq::decode_int4_plan((int)m, c->tiles, c->kb_per_tile, c->kb_per_group, c->num_sms);
+  out[0] = plan.grid;
+  out[1] = plan.cluster;
+  out[2] = plan.kpw;
+  out[3] = plan.smem_budget;
   return WOQ_B200_OK;
 }
 

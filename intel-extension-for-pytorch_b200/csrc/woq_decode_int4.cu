@@ -26,6 +26,13 @@
 //     segment is taken by the producer warp, idle by then.
 // The memory system needs about 2.5 us x 44 GB/s = 110+ KB in flight per SM to stay busy,
 // which sets the number of pipeline stages.
+//
+// Cluster variant (layers with at most two tiles' worth of CTAs per SM): the grid is
+// tiles x C CTAs in thread-block clusters of C; the C CTAs of a cluster split the K range of
+// one tile, one segment each.  Ranks 1..C-1 push their partial tile into the shared memory
+// of rank 0 (st.shared::cluster), one cluster barrier orders the pushes, and rank 0 adds the
+// partials in rank order and runs the epilogue: no global partial tiles, no atomics, no
+// fences, and nothing to clear in the workspace.
 #include <cstdlib>
 
 #include "woq_kernels.h"
@@ -55,17 +62,60 @@ constexpr int kRedTokStride = 68;                             // floats; conflic
 constexpr int kHeaderBytes = 1024;
 constexpr int kMaxStages = 8;
 
+// What the tile epilogue reads of the launch parameters, copied into shared memory when the
+// CTA starts.  The epilogue is a function of its own; handed the kernel parameter by
+// reference it would fetch every field through a generic pointer into the parameter bank,
+// and the first touch of those lines costs a round trip to device memory (about 2 us per
+// epilogue call when measured), on the serial tail of every launch.
+struct EpiParams {
+  const float* bias;
+  __nv_bfloat16* y;
+  const __nv_bfloat16* other0;
+  const __nv_bfloat16* other1;
+  const int32_t* row_idx;
+  const __nv_bfloat16* row_w;
+  int* status;
+  int64_t ldy, ldo;
+  int m, n, n_out, fusion, gate_up;
+  CommParams comm;
+};
+
 struct SmemHeader {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   int abort_flag;
   int finished_warps;  // of the two warps that run epilogues
+  EpiParams epi;
 };
+static_assert(sizeof(SmemHeader) <= kHeaderBytes, "shared-memory header");
 
 // The k-block sequence is dealt out in units of `unit` k-blocks: CTA c owns units
 // [c*units/ctas, (c+1)*units/ctas).
 __device__ __forceinline__ int owner_of(int64_t b, int unit, int64_t units, int64_t ctas) {
   return static_cast<int>(((b / unit + 1) * ctas - 1) / units);
+}
+
+// ---- thread-block cluster helpers (plain distributed-shared-memory stores, no multicast) ----
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_num_ctas() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// Hardware barrier over all threads of the cluster (threads that have exited count as
+// arrived); release / acquire makes shared-memory stores of any CTA visible to the others.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Store into the shared memory of CTA `rank` of this cluster at the offset `local` has here.
+__device__ __forceinline__ void st_cluster_f32(float* local, uint32_t rank, float v) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
 }
 
 __device__ __forceinline__ uint32_t* comm_ctl(uint8_t* base) { return reinterpret_cast<uint32_t*>(base); }
@@ -122,6 +172,16 @@ __device__ __forceinline__ void comm_wait_words8(WordAt word_at, int h, int m, u
     if (h + i < m) data[i] = v[i].y == stamp ? v[i].x : comm_wait_word(word_at(h + i), stamp, status);
 }
 
+// Timeline probe, compiled in only with -DWOQ_B200_TIMELINE (a measuring build, never the
+// shipped library): CTA c of launch q writes global-timer stamps to p.stamps[q % 8][c][idx].
+#ifdef WOQ_B200_TIMELINE
+__device__ __forceinline__ void decode_stamp(const DecodeParams& p, int idx) {
+  if (p.stamps) p.stamps[(static_cast<size_t>(p.launch_seq & 7) * 1024 + blockIdx.x) * 8 + idx] = global_timer_ns();
+}
+#else
+__device__ __forceinline__ void decode_stamp(const DecodeParams&, int) {}
+#endif
+
 // The stages a CTA walks: its share [b_begin, b_end) of the k-block sequence cut at tile
 // boundaries ("segments") and then into runs of up to kStageKBlocks k-blocks.  Producer and
 // consumers step through the same sequence.
@@ -149,7 +209,7 @@ struct StageIter {
 // its registers are allocated apart from the main loop's; with the tensor-parallel exchange
 // compiled in (COMM) it also swaps the tile with the other ranks.
 template <int NTOK, bool COMM>
-__device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl, int lane, uint32_t epoch,
+__device__ __noinline__ void decode_tile_epilogue(const EpiParams& p, int tl, int lane, uint32_t epoch,
                                                   float* a0, float* a1) {
   if (COMM && p.comm.mode == kCommAllReduce) {
     // Row-parallel linear: every rank's bf16 partial of this tile goes to every rank; each
@@ -371,7 +431,7 @@ __device__ __noinline__ void decode_tile_epilogue(const DecodeParams& p, int tl,
 
 // COMM: compiled with the tensor-parallel exchange in the epilogue (the plain variant carries
 // none of its code or registers).
-template <int TB, int MODE, int KPW, bool COMM>
+template <int TB, int MODE, int KPW, bool COMM, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 2)
     woq_int4_decode_kernel(const __grid_constant__ DecodeParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -384,22 +444,53 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int red_tok = p.red_tok;  // tokens kept in the cross-warp reduction buffer
   uint8_t* stages = smem + kHeaderBytes;
   float* red = reinterpret_cast<float*>(stages + static_cast<size_t>(p.stages) * stage_bytes);
+  // cluster variant, rank 0: the partial tiles pushed by ranks 1 .. C-1, [rank][token][row]
+  float* parts = red + kConsumerWarps * red_tok * kRedTokStride;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t units = static_cast<int64_t>(p.tiles) * p.kb_per_tile / p.unit;
-  const int64_t b_begin = (static_cast<int64_t>(blockIdx.x) * units) / gridDim.x * p.unit;
-  const int64_t b_end = (static_cast<int64_t>(blockIdx.x + 1) * units) / gridDim.x * p.unit;
+  int64_t b_begin, b_end;
+  uint32_t crank = 0, csize = 1;
+  if constexpr (CLUSTER) {
+    // CTA r of a cluster owns units [r * u / C, (r + 1) * u / C) of its tile's u units
+    csize = cluster_num_ctas();
+    crank = cluster_cta_rank();
+    const int64_t tile = blockIdx.x / csize;
+    const int units_t = p.kb_per_tile / p.unit;
+    b_begin = tile * p.kb_per_tile + static_cast<int64_t>(crank * units_t / csize) * p.unit;
+    b_end = tile * p.kb_per_tile + static_cast<int64_t>((crank + 1) * units_t / csize) * p.unit;
+  } else {
+    b_begin = (static_cast<int64_t>(blockIdx.x) * units) / gridDim.x * p.unit;
+    b_end = (static_cast<int64_t>(blockIdx.x + 1) * units) / gridDim.x * p.unit;
+  }
   const int tile0 = static_cast<int>(b_begin / p.kb_per_tile);
   const int kb00 = static_cast<int>(b_begin - static_cast<int64_t>(tile0) * p.kb_per_tile);
   const int share = static_cast<int>(b_end - b_begin);
 
   if (tid == 0) {
+    decode_stamp(p, 0);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&hdr->full[s], 1);
       mbar_init(&hdr->empty[s], kConsumerWarps);
     }
     hdr->abort_flag = 0;
     hdr->finished_warps = 0;
+    EpiParams& e = hdr->epi;
+    e.bias = p.bias;
+    e.y = p.y;
+    e.other0 = p.other0;
+    e.other1 = p.other1;
+    e.row_idx = p.row_idx;
+    e.row_w = p.row_w;
+    e.status = p.status;
+    e.ldy = p.ldy;
+    e.ldo = p.ldo;
+    e.m = p.m;
+    e.n = p.n;
+    e.n_out = p.n_out;
+    e.fusion = p.fusion;
+    e.gate_up = p.gate_up;
+    if constexpr (COMM) e.comm = p.comm;
     mbar_fence_init();
   }
   __syncthreads();
@@ -419,8 +510,84 @@ __global__ void __launch_bounds__(kThreads, 2)
   // fused epilogue or parks a partial tile and, if this CTA is the last contributor to
   // arrive, reduces the tile in a fixed order.
   uint32_t epoch = 0;  // read by the warps that run epilogues, once the previous grid is done
+  // The three epilogues decode steps use most (plain, residual add, silu(gate) * up; no
+  // exchange) are written out here: a handful of instructions per token on the serial tail of
+  // the launch, the partial sums stay in registers.  Everything else goes through the general
+  // routine, on copies of the sums so that the arrays here never have their address taken.
   auto run_epilogue = [&](int tl, float* a0, float* a1) {
-    decode_tile_epilogue<NTOK, COMM>(p, tl, lane, epoch, a0, a1);
+    const int fusion = p.fusion;
+    const bool plain = (!COMM || p.comm.mode == kCommNone) &&
+                       (fusion == FUSE_NONE || fusion == FUSE_ADD || fusion == FUSE_SILU_MUL);
+    if (!plain) {
+      float w0[NTOK], w1[NTOK];
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok) {
+        w0[tok] = a0[tok];
+        w1[tok] = a1[tok];
+      }
+      decode_tile_epilogue<NTOK, COMM>(hdr->epi, tl, lane, epoch, w0, w1);
+      return;
+    }
+    const int n0 = decode_row_to_n(p, tl, lane), n1 = decode_row_to_n(p, tl, lane + 32);
+    const int m = p.m;
+    const int64_t ldy = p.ldy;
+    float b0 = 0.f, b1 = 0.f;
+    if (fusion == FUSE_SILU_MUL) {
+      // gate/up layout: row lane is a gate row, row lane + 32 its up row
+      const int col = tl * 32 + lane;
+      if (col >= p.n_out) return;
+      if (p.bias) {
+        b0 = p.bias[n0];
+        b1 = p.bias[n1];
+      }
+      __nv_bfloat16* yc = p.y + col;
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < m) {
+          float gate = a0[tok], up = a1[tok];
+          if (p.bias) {
+            gate += b0;
+            up += b1;
+          }
+          yc[tok * ldy] = __float2bfloat16_rn(bf16_round(up) * silu_bf16(bf16_round(gate)));
+        }
+      return;
+    }
+    const bool ok0 = n0 < p.n, ok1 = n1 < p.n;
+    const int c0 = ok0 ? n0 : 0, c1 = ok1 ? n1 : 0;  // columns that always exist
+    if (p.bias) {
+      b0 = p.bias[c0];
+      b1 = p.bias[c1];
+    }
+    uint32_t f0[NTOK], f1[NTOK];
+    if (fusion == FUSE_ADD) {
+      // all loads first (raw bf16 bits, converted where they are used): one round trip
+      const unsigned short* o16 = reinterpret_cast<const unsigned short*>(p.other0);
+      const int64_t ldo = p.ldo;
+#pragma unroll
+      for (int tok = 0; tok < NTOK; ++tok)
+        if (tok < m) {
+          f0[tok] = o16[tok * ldo + c0];
+          f1[tok] = o16[tok * ldo + c1];
+        }
+    }
+#pragma unroll
+    for (int tok = 0; tok < NTOK; ++tok)
+      if (tok < m) {
+        float v0 = a0[tok], v1 = a1[tok];
+        if (p.bias) {
+          v0 += b0;
+          v1 += b1;
+        }
+        v0 = bf16_round(v0);
+        v1 = bf16_round(v1);
+        if (fusion == FUSE_ADD) {
+          v0 = bf16_round(v0 + __uint_as_float(f0[tok] << 16));
+          v1 = bf16_round(v1 + __uint_as_float(f1[tok] << 16));
+        }
+        if (ok0) p.y[tok * ldy + n0] = __float2bfloat16_rn(v0);
+        if (ok1) p.y[tok * ldy + n1] = __float2bfloat16_rn(v1);
+      }
   };
   // Both epilogue-running warps call this when they are done; the second one of the last CTA
   // of the grid closes the epoch.
@@ -506,10 +673,9 @@ __global__ void __launch_bounds__(kThreads, 2)
       v0[tok] = s0;
       v1[tok] = s1;
     }
-    if (signal_free) {
-      __threadfence_block();
-      named_bar_arrive(kBarRedFree, kConsumerThreads + 32);
-    }
+    // (a named barrier orders the shared-memory accesses made before it among its
+    // participants; a fence on top of it cost about 0.6 us per call when measured)
+    if (signal_free) named_bar_arrive(kBarRedFree, kConsumerThreads + 32);
     if (whole) {
       run_epilogue(seg_tile, v0, v1);
       return;
@@ -544,19 +710,16 @@ __global__ void __launch_bounds__(kThreads, 2)
       uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
       const int g0 = it.kb >> p.kbpg_shift;
       const int ng = ((it.kb + nkb - 1) >> p.kbpg_shift) - g0 + 1;
-      uint32_t bytes = nkb * kBlockBytes;
-      if (!(p.debug & 4)) bytes += ng * 256;
-      if (!(p.debug & 2)) bytes += p.m * nkb * (kBlockK * 2);
+      const uint32_t bytes = nkb * kBlockBytes + ng * 256 + p.m * nkb * (kBlockK * 2);
       mbar_arrive_expect_tx(&hdr->full[slot], bytes);
       bulk_g2s(st, p.wq + (static_cast<size_t>(it.tile) * p.kb_per_tile + it.kb) * kBlockBytes,
                nkb * kBlockBytes, &hdr->full[slot]);
-      if (!(p.debug & 4))
-        bulk_g2s(st + kStageKBlocks * kBlockBytes,
-                 p.sz + (static_cast<size_t>(it.tile) * p.groups + g0) * 64, ng * 256,
-                 &hdr->full[slot]);
+      bulk_g2s(st + kStageKBlocks * kBlockBytes,
+               p.sz + (static_cast<size_t>(it.tile) * p.groups + g0) * 64, ng * 256,
+               &hdr->full[slot]);
     };
     auto issue_x = [&](const StageIter& it, int slot) {  // lane = token
-      if (lane < p.m && !(p.debug & 2)) {
+      if (lane < p.m) {
         uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
         bulk_g2s(st + kStageKBlocks * kBlockBytes + sz_stage_bytes + lane * kXRowBytes,
                  p.x + static_cast<size_t>(lane) * p.ldx + static_cast<size_t>(it.kb) * kBlockK,
@@ -571,7 +734,9 @@ __global__ void __launch_bounds__(kThreads, 2)
           issue_weights(fill, s);
           fill.next(fill.nkb());
         }
+      if (lane == 0) decode_stamp(p, 1);
       grid_dependency_wait();
+      if (lane == 0) decode_stamp(p, 2);
       if (COMM && p.comm.mode != kCommNone)
         epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
       __syncwarp();
@@ -582,23 +747,72 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     int slot = 0;
     uint32_t phase = 1;  // the slots are on their second use from here on
-    while (!it.done() && !(p.debug & 16)) {
+    while (!it.done()) {
       if (lane == 0) {
         mbar_wait(&hdr->empty[slot], phase ^ 1, abort_flag, p.status, 1);
-        if (p.debug & 8)
-          mbar_arrive(&hdr->full[slot]);  // experiment: consumers re-read the stale stage
-        else
-          issue_weights(it, slot);
+        issue_weights(it, slot);
       }
       __syncwarp();
-      if (!(p.debug & 8)) issue_x(it, slot);
+      issue_x(it, slot);
       it.next(it.nkb());
       if (++slot == p.stages) {
         slot = 0;
         phase ^= 1;
       }
     }
-    if (nseg > 0) {
+    if constexpr (CLUSTER) {
+      // The CTA's only segment.  Ranks 1 .. C-1 push their partial tile into rank 0's shared
+      // memory; after the cluster barrier rank 0 adds them in rank order and finishes the tile.
+      float v0[NTOK], v1[NTOK];
+      if (nseg > 0) {
+        named_bar_sync(kBarRedFullLast, kConsumerThreads + 32);
+#pragma unroll
+        for (int tok = 0; tok < NTOK; ++tok) {
+          float s0 = 0.f, s1 = 0.f;
+          if (tok < red_tok) {
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+              const float* r = red + w * (red_tok * kRedTokStride) + tok * kRedTokStride;
+              s0 += r[lane];
+              s1 += r[lane + 32];
+            }
+          }
+          v0[tok] = s0;
+          v1[tok] = s1;
+        }
+      } else {
+#pragma unroll
+        for (int tok = 0; tok < NTOK; ++tok) v0[tok] = v1[tok] = 0.f;
+      }
+      if (lane == 0) decode_stamp(p, 5);
+      if (csize > 1) {
+        if (crank != 0) {
+          float* mine = parts + crank * (red_tok * kRedTokStride);
+#pragma unroll
+          for (int tok = 0; tok < NTOK; ++tok)
+            if (tok < p.m) {
+              st_cluster_f32(mine + tok * kRedTokStride + lane, 0, v0[tok]);
+              st_cluster_f32(mine + tok * kRedTokStride + lane + 32, 0, v1[tok]);
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();
+        if (crank == 0) {
+          for (uint32_t c = 1; c < csize; ++c) {
+            const float* src = parts + c * (red_tok * kRedTokStride);
+#pragma unroll
+            for (int tok = 0; tok < NTOK; ++tok)
+              if (tok < p.m) {
+                v0[tok] += src[tok * kRedTokStride + lane];
+                v1[tok] += src[tok * kRedTokStride + lane + 32];
+              }
+          }
+        }
+      }
+      if (lane == 0) decode_stamp(p, 6);
+      if (crank == 0) run_epilogue(tile0, v0, v1);
+      if (lane == 0) decode_stamp(p, 7);
+    } else if (nseg > 0) {
       // the CTA's last segment
       float v0[NTOK], v1[NTOK];
       int pend_tile = -1;
@@ -608,6 +822,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       take_segment(kBarRedFullLast, false, tile0 + nseg - 1, k0 == 0 && len == p.kb_per_tile,
                    nseg == 1, v0, v1, pend_tile, pend_old);
       if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
+      if (lane == 0) decode_stamp(p, 7);
     }
     finish_comm();
     return;
@@ -621,12 +836,15 @@ __global__ void __launch_bounds__(kThreads, 2)
     grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
     if (COMM && p.comm.mode != kCommNone)
       epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
-    for (int sg = 0; sg + 1 < nseg; ++sg) {
-      take_segment(kBarRedFull, true, tile0 + sg, sg > 0 || kb00 == 0, sg == 0, v0, v1, pend_tile,
-                   pend_old);
+    if constexpr (!CLUSTER) {
+      for (int sg = 0; sg + 1 < nseg; ++sg) {
+        take_segment(kBarRedFull, true, tile0 + sg, sg > 0 || kb00 == 0, sg == 0, v0, v1, pend_tile,
+                     pend_old);
+      }
+      if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
     }
-    if (pend_tile >= 0) resolve(pend_tile, pend_old, v0, v1);
     finish_comm();
+    if (CLUSTER && csize > 1) cluster_sync_all();
     return;
   }
 
@@ -657,7 +875,6 @@ __global__ void __launch_bounds__(kThreads, 2)
           if (tok < red_tok) my[tok * kRedTokStride + row] = acc[rt][tb][i];
           acc[rt][tb][i] = 0.f;
         }
-    __threadfence_block();
     ++seg;
     named_bar_arrive(seg == nseg ? kBarRedFullLast : kBarRedFull, kConsumerThreads + 32);
   };
@@ -679,7 +896,8 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int nkb = it.nkb();
     const int kb0 = it.kb;
     const uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
-    if (!(p.debug & 16)) mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 2);
+    mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 2);
+    if (warp == 0 && lane == 0 && kb0 == kb00) decode_stamp(p, 3);
 
     // one k-block (64 rows x 64 k) of the stage: index idx, constants reloaded if `prep`
     auto do_kblock = [&](const int idx, const bool prep) {
@@ -796,8 +1014,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           }
       }
     };
-    const int nkb_do = (p.debug & 1) ? 0 : nkb;
-    if (nkb_do == kStageKBlocks) {
+    if (nkb == kStageKBlocks) {
       // full stage: straight-line code, the second k-block's loads overlap the first's math
       // (a warp's two k-blocks share their group unless a group is a single k-block)
 #pragma unroll
@@ -805,16 +1022,23 @@ __global__ void __launch_bounds__(kThreads, 2)
     } else {
 #pragma unroll 1
       for (int kk = 0; kk < KPW; ++kk)
-        if (KPW * warp + kk < nkb_do) do_kblock(KPW * warp + kk, true);
+        if (KPW * warp + kk < nkb) do_kblock(KPW * warp + kk, true);
     }
     __syncwarp();
-    if (lane == 0 && !(p.debug & 16)) mbar_arrive(&hdr->empty[slot]);
-    if (kb0 + nkb == it.k1) flush();
+    if (lane == 0) mbar_arrive(&hdr->empty[slot]);
+    if (kb0 + nkb == it.k1) {
+      if (warp == 0 && lane == 0) decode_stamp(p, 4);
+      flush();
+    }
     it.next(nkb);
     if (++slot == p.stages) {
       slot = 0;
       phase ^= 1;
     }
+  }
+  if (CLUSTER && csize > 1) {
+    __syncwarp();
+    cluster_sync_all();
   }
 }
 
@@ -822,20 +1046,27 @@ __global__ void __launch_bounds__(kThreads, 2)
 
 size_t decode_int4_partial_bytes(int grid) { return static_cast<size_t>(grid) * 2 * 16 * kTileN * 4; }
 
-int decode_int4_pick_grid(const DecodeShape& s, int num_sms) {
-  const int64_t total = static_cast<int64_t>(s.tiles) * s.kb_per_tile / s.unit;
-  int per_sm = 2;
-  if (const char* e = getenv("WOQ_B200_GRID_PER_SM")) per_sm = atoi(e) > 1 ? 2 : 1;
-  int64_t grid = static_cast<int64_t>(num_sms) * per_sm;
-  if (grid > total) grid = total;
-  return static_cast<int>(grid < 1 ? 1 : grid);
-}
-
 namespace {
 
-int env_int(const char* name, int fallback) {
-  const char* e = getenv(name);
-  return e ? atoi(e) : fallback;
+// Tuning variables, read once when the library is first used (never per launch):
+//   WOQ_B200_DECODE_SPLIT  0 choose per layer (default), 1 always the stream-K grid,
+//                          2 the cluster grid whenever the layer has few enough tiles
+//   WOQ_B200_PDL           0 switches programmatic dependent launch off
+struct DecodeTuning {
+  int split, pdl;
+};
+DecodeTuning& tuning() {
+  static DecodeTuning t = [] {
+    auto env_int = [](const char* name, int fallback) {
+      const char* e = getenv(name);
+      return e ? atoi(e) : fallback;
+    };
+    DecodeTuning v;
+    v.split = env_int("WOQ_B200_DECODE_SPLIT", 0);
+    v.pdl = env_int("WOQ_B200_PDL", 1);
+    return v;
+  }();
+  return t;
 }
 
 // bytes of one pipeline stage / of the cross-warp reduction buffer
@@ -843,81 +1074,189 @@ int stage_bytes_for(int m, int kpw, int kbpg_shift) {
   const int gps = (stage_kblocks(kpw) >> kbpg_shift) + 1;
   return stage_kblocks(kpw) * kBlockBytes + (gps + 1) * 256 + m * x_row_bytes(kpw);
 }
-int red_bytes_for(int m) { return kConsumerWarps * ((m + 1) & ~1) * kRedTokStride * 4; }
+int red_tok_for(int m) { return (m + 1) & ~1; }
+int red_bytes_for(int m) { return kConsumerWarps * red_tok_for(m) * kRedTokStride * 4; }
 constexpr int kBudgetTwoCtas = 112 * 1024;  // shared memory of one CTA
 
 // two k-blocks per warp and stage while two such stages fit beside the x rows (1..6 tokens)
 int pick_kpw(int m, int kbpg_shift) {
   if (m > 8) return 1;
   const int fits = (kBudgetTwoCtas - kHeaderBytes - red_bytes_for(m)) / stage_bytes_for(m, 2, kbpg_shift) >= 2;
-  return env_int("WOQ_B200_KPW", fits ? 2 : 1) == 2 && fits ? 2 : 1;
+  return fits ? 2 : 1;
 }
 
-template <int TB, int KPW, bool COMM>
+template <int TB, int KPW, bool COMM, bool CLUSTER>
 void (*pick_kernel_mode(int mode))(const DecodeParams) {
   switch (mode) {
-    case kScaleAfterSum: return woq_int4_decode_kernel<TB, kScaleAfterSum, KPW, COMM>;
-    case kExactShift: return woq_int4_decode_kernel<TB, kExactShift, KPW, COMM>;
-    default: return woq_int4_decode_kernel<TB, kExactInPlace, KPW, COMM>;
+    case kScaleAfterSum: return woq_int4_decode_kernel<TB, kScaleAfterSum, KPW, COMM, CLUSTER>;
+    case kExactShift: return woq_int4_decode_kernel<TB, kExactShift, KPW, COMM, CLUSTER>;
+    default: return woq_int4_decode_kernel<TB, kExactInPlace, KPW, COMM, CLUSTER>;
   }
 }
 template <int TB, int KPW>
-void (*pick_kernel(int mode, bool comm))(const DecodeParams) {
-  return comm ? pick_kernel_mode<TB, KPW, true>(mode) : pick_kernel_mode<TB, KPW, false>(mode);
+void (*pick_kernel(int mode, bool comm, bool cluster))(const DecodeParams) {
+  if (cluster) return comm ? pick_kernel_mode<TB, KPW, true, true>(mode) : pick_kernel_mode<TB, KPW, false, true>(mode);
+  return comm ? pick_kernel_mode<TB, KPW, true, false>(mode) : pick_kernel_mode<TB, KPW, false, false>(mode);
 }
 
 }  // namespace
 
-int decode_int4_unit(int m, int kb_per_group) {
-  // shares are dealt in pairs of k-blocks when a warp takes two, so that a pair never
-  // straddles two groups
-  int shift = 0;
-  while ((1 << (shift + 1)) <= kb_per_group && shift < 30) ++shift;
-  return pick_kpw(m, shift) == 2 && kb_per_group % 2 == 0 ? 2 : 1;
+void decode_int4_set_split(int mode) { tuning().split = mode; }
+
+namespace {
+
+// How many clusters of c CTAs the device keeps resident at once (thread-block clusters never
+// span GPCs, so this is less than slots / c), asked of the runtime once per cluster size for a
+// CTA that takes half an SM's shared memory [0] and for one that takes nearly all of it [1].
+struct ClusterCapacity {
+  int cap[2][9];
+};
+const ClusterCapacity& cluster_capacity(int num_sms) {
+  static ClusterCapacity cc = [num_sms] {
+    ClusterCapacity v{};
+    void (*kern)(const DecodeParams) = woq_int4_decode_kernel<1, kExactInPlace, 1, false, true>;
+    for (int big = 0; big < 2; ++big) {
+      const int smem = big ? 2 * kBudgetTwoCtas - 8 * 1024 : kBudgetTwoCtas;
+      const bool attr_ok =
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
+      for (int c = 1; c <= 8; ++c) {
+        int n = 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(c * 8);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = c;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (!attr_ok || cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+          cudaGetLastError();
+          n = (big ? 1 : 2) * num_sms / c * 7 / 8;  // conservative guess
+        }
+        v.cap[big][c] = n;
+      }
+    }
+    return v;
+  }();
+  return cc;
 }
 
-cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream) {
+}  // namespace
+
+DecodePlan decode_int4_plan(int m, int tiles, int kb_per_tile, int kb_per_group, int num_sms) {
+  int shift = 0;
+  while ((1 << (shift + 1)) <= kb_per_group && shift < 30) ++shift;
+  DecodePlan pl{};
+  const int slots = 2 * num_sms;  // CTAs resident at once
+  const int64_t total_kb = static_cast<int64_t>(tiles) * kb_per_tile;
+
+  // stream-K: 2 CTAs per SM, equal contiguous shares of the k-block sequence; shares are dealt
+  // in pairs of k-blocks when a warp takes two, so that a pair never straddles two groups
+  pl.kpw = pick_kpw(m, shift);
+  pl.unit = pl.kpw == 2 && kb_per_group % 2 == 0 ? 2 : 1;
+  pl.cluster = 0;
+  pl.smem_budget = kBudgetTwoCtas;
+  const int64_t units = total_kb / pl.unit;
+  pl.grid = static_cast<int>(units < slots ? (units < 1 ? 1 : units) : slots);
+  if (tuning().split == 1 || tiles > slots) return pl;
+
+  // cluster grid: tiles x C CTAs, all resident at once.  Work of the busiest SM against the
+  // even share gives the efficiency of a split, with a penalty for a single CTA per SM: the
+  // dequantising warps of one CTA alone do not keep an SM's issue slots busy.
+  const ClusterCapacity& cc = cluster_capacity(num_sms);
+  int best_c = 0;
+  double best_eff = 0.0;
+  for (int c = 1; c <= 8 && tiles * c <= slots; ++c) {
+    if (c > 1 && kb_per_tile / c < kConsumerWarps) break;
+    if (tiles > cc.cap[0][c]) continue;  // would need a second wave
+    const int slice = (kb_per_tile + c - 1) / c;
+    const int per_sm = (tiles * c + num_sms - 1) / num_sms;
+    double eff = static_cast<double>(total_kb) / (static_cast<double>(num_sms) * per_sm * slice);
+    if (per_sm < 2) eff *= 0.9;
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best_c = c;
+    }
+  }
+  if (best_c == 0) return pl;
+  // time estimates in microseconds: a stream-K launch pays about 9 us of dependency, fill and
+  // split-K fix-up round trips, a cluster launch about 5; streaming at about 4.5 TB/s
+  const double stream_us = static_cast<double>(total_kb) * kBlockBytes / 4.5e6;
+  if (tuning().split != 2 && stream_us / best_eff + 5.0 >= stream_us + 9.0) return pl;
+  pl.cluster = best_c;
+  pl.grid = tiles * best_c;
+  const int slice = kb_per_tile / best_c;
+  pl.kpw = m <= 8 && slice >= 2 * kConsumerWarps && kb_per_group % 2 == 0 && pick_kpw(m, shift) == 2 ? 2 : 1;
+  pl.unit = pl.kpw;
+  // a grid with at most one CTA per SM may use the shared memory two CTAs would share
+  if (pl.grid <= num_sms && tiles <= cc.cap[1][best_c]) pl.smem_budget = 2 * kBudgetTwoCtas - 8 * 1024;
+  return pl;
+}
+
+cudaError_t launch_decode_int4(DecodeParams p, const DecodePlan& plan, cudaStream_t stream) {
   const int tb = p.m <= 8 ? 1 : 2;
-  const int kpw = pick_kpw(p.m, p.kbpg_shift > 30 ? 30 : p.kbpg_shift);
+  const int kpw = plan.kpw;
+  p.unit = plan.unit;
   p.x_rows = p.m;
-  p.red_tok = (p.m + 1) & ~1;
+  p.red_tok = red_tok_for(p.m);
   const int skb = stage_kblocks(kpw);
   p.gps = (skb >> p.kbpg_shift) + 1;  // groups a stage can touch
   const int stage_bytes = skb * kBlockBytes + (p.gps + 1) * 256 + p.x_rows * x_row_bytes(kpw);
-  const int red_bytes = kConsumerWarps * p.red_tok * kRedTokStride * 4;
-  const int budget = kBudgetTwoCtas;
-  int stages = (budget - kHeaderBytes - red_bytes) / stage_bytes;
+  const int red_bytes = red_bytes_for(p.m);
+  const int parts_bytes = plan.cluster > 1 ? plan.cluster * p.red_tok * kRedTokStride * 4 : 0;
+  int stages = (plan.smem_budget - kHeaderBytes - red_bytes - parts_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  const int want = env_int("WOQ_B200_STAGES", 0);
-  if (want >= 2 && want <= stages) stages = want;
-  p.debug = env_int("WOQ_B200_DEBUG", p.debug);
-  if (stages < 2) return cudaErrorInvalidConfiguration;
+  if (plan.cluster) {
+    // one segment per CTA: no more stages than the longest slice needs
+    const int units_t = p.kb_per_tile / plan.unit;
+    const int slice = (units_t + plan.cluster - 1) / plan.cluster * plan.unit;
+    const int need = (slice + skb - 1) / skb;
+    if (stages > need) stages = need;
+    if (stages < 1) return cudaErrorInvalidConfiguration;
+  } else if (stages < 2) {
+    return cudaErrorInvalidConfiguration;
+  }
   p.stages = stages;
-  const size_t smem = kHeaderBytes + static_cast<size_t>(stages) * stage_bytes + red_bytes;
-  const int mode = env_int("WOQ_B200_DEQUANT_MODE", p.exact);
+#ifdef WOQ_B200_TIMELINE
+  static int launch_seq = 0;
+  p.launch_seq = launch_seq++;
+#endif
+  const size_t smem = kHeaderBytes + static_cast<size_t>(stages) * stage_bytes + red_bytes + parts_bytes;
   const bool comm = p.comm.mode != kCommNone;
-  void (*kern)(const DecodeParams) =
-      tb == 2 ? pick_kernel<2, 1>(mode, comm) : kpw == 2 ? pick_kernel<1, 2>(mode, comm) : pick_kernel<1, 1>(mode, comm);
+  const bool cl = plan.cluster > 0;
+  void (*kern)(const DecodeParams) = tb == 2     ? pick_kernel<2, 1>(p.exact, comm, cl)
+                                     : kpw == 2 ? pick_kernel<1, 2>(p.exact, comm, cl)
+                                                : pick_kernel<1, 1>(p.exact, comm, cl);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   // Programmatic dependent launch: this grid may start streaming weights while the previous
   // kernel in the stream drains (it waits for that kernel before it touches x, y or the
   // workspace).  After a kernel that never signals, or after a copy, this is ordinary ordering.
-  static const bool pdl = [] {
-    const char* e = getenv("WOQ_B200_PDL");
-    return !(e && atoi(e) == 0);
-  }();
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3(plan.grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (tuning().pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  if (cl) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = plan.cluster;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = n_attr;
   return cudaLaunchKernelEx(&cfg, kern, p);
 }
 

@@ -53,25 +53,31 @@ struct DecodeParams {
   int exact;  // 0: scale after the sum; 1, 2: per-weight bf16 rounding (2: shift-free high nibbles)
   int unit;   // CTA shares are multiples of this many k-blocks
   int x_rows, red_tok;  // shared-memory rows for x per stage / tokens in the reduction buffer
-  // experiment switches (timing only, results are wrong): 1 skip math, 2 skip x copies, 4 skip
-  // scale copies, 8 copy only the first pipeline fill, 16 consumers never wait
-  int debug;
+#ifdef WOQ_B200_TIMELINE
+  unsigned long long* stamps;  // measuring build only: [8 launches][1024 CTAs][8] global-timer stamps
+  int launch_seq;
+#endif
   CommParams comm;
 };
 
-struct DecodeShape {
-  int m, tiles, kb_per_tile, unit;
+// How a launch cuts the weight: `cluster` == 0 is the stream-K grid (equal contiguous shares of
+// the k-block sequence, split tiles reduced through the workspace); `cluster` == C >= 1 is
+// tiles x C CTAs in thread-block clusters of C that reduce through distributed shared memory.
+struct DecodePlan {
+  int grid, cluster, kpw, unit, smem_budget;
 };
 
-__device__ __forceinline__ int decode_row_to_n(const DecodeParams& p, int tile, int row) {
+template <class P>
+__device__ __forceinline__ int decode_row_to_n(const P& p, int tile, int row) {
   if (p.gate_up) return row < 32 ? tile * 32 + row : p.n / 2 + tile * 32 + (row - 32);
   return tile * kTileN + row;
 }
 
-int decode_int4_pick_grid(const DecodeShape& s, int num_sms);
-int decode_int4_unit(int m, int kb_per_group);
+// 0 per-layer choice, 1 always stream-K, 2 cluster grid whenever the tiles fit (see DecodePlan)
+void decode_int4_set_split(int mode);
+DecodePlan decode_int4_plan(int m, int tiles, int kb_per_tile, int kb_per_group, int num_sms);
 size_t decode_int4_partial_bytes(int grid);
-cudaError_t launch_decode_int4(DecodeParams p, int grid, cudaStream_t stream);
+cudaError_t launch_decode_int4(DecodeParams p, const DecodePlan& plan, cudaStream_t stream);
 
 // ---- INT4 tensor-core path (any M up to 256 per launch) --------------------------------
 // Row layout: tiles of 128 output rows x 64 k, 4096 bytes each, [tile][k-block][half][row][16 B].

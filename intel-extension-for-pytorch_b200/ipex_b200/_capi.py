@@ -24,11 +24,14 @@ FUSE_ADD, FUSE_ADD_ADD, FUSE_MUL, FUSE_SILU_MUL = 0x10, 0x20, 0x30, 0x100
 T_NONE, T_F32, T_F16, T_BF16, T_U8, T_S8, T_I32 = 0, 1, 2, 3, 4, 5, 6
 LAYOUT_GATE_UP, LAYOUT_STREAM_ONLY, LAYOUT_TC_ONLY, LAYOUT_SCALES_NK = 1, 2, 4, 8
 HINT_AUTO, HINT_TENSOR_CORE, HINT_STREAM, HINT_STREAM_FAST = 0, 1, 2, 3
+OPT_DECODE_SPLIT = 1
+SPLIT_AUTO, SPLIT_STREAM_K, SPLIT_CLUSTER = 0, 1, 2
 
 EXPORTS = [
     "woq_b200_version",
     "woq_b200_last_error",
     "woq_b200_kernel_launches",
+    "woq_b200_set_option",
     "woq_b200_ctx_create",
     "woq_b200_ctx_destroy",
     "woq_b200_ctx_desc",
@@ -45,6 +48,7 @@ EXPORTS = [
     "woq_b200_int8_internals",
     "woq_b200_int8_zero_points",
     "woq_b200_workspace_status",
+    "woq_b200_decode_plan",
     "woq_b200_comm_create",
     "woq_b200_comm_export",
     "woq_b200_comm_connect",
@@ -96,6 +100,7 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_version.restype = ctypes.c_int
     L.woq_b200_last_error.restype = ctypes.c_char_p
     L.woq_b200_kernel_launches.restype = i64
+    L.woq_b200_set_option.argtypes = [i32, i32]
     L.woq_b200_ctx_create.argtypes = [ctypes.POINTER(Desc), vp, vp, vp, vp, vp, ctypes.POINTER(vp)]
     L.woq_b200_ctx_destroy.argtypes = [vp]
     L.woq_b200_ctx_desc.argtypes = [vp, ctypes.POINTER(Desc)]
@@ -115,6 +120,7 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
     L.woq_b200_int8_zero_points.argtypes = [vp, i64, vp, vp, sz, vp]
     L.woq_b200_workspace_status.argtypes = [vp, vp]
+    L.woq_b200_decode_plan.argtypes = [vp, i64, ctypes.POINTER(i32)]
     L.woq_b200_comm_create.argtypes = [i32, i32, i64, sz, ctypes.POINTER(vp)]
     L.woq_b200_comm_export.argtypes = [vp, vp]
     L.woq_b200_comm_connect.argtypes = [vp, vp]
@@ -131,6 +137,11 @@ def lib() -> ctypes.CDLL:
 def _check(rc: int):
     if rc != 0:
         raise WoqError(rc, lib().woq_b200_last_error().decode())
+
+
+def set_option(option: int, value: int):
+    """Process-wide tuning switch (woq_b200_set_option)."""
+    _check(lib().woq_b200_set_option(option, value))
 
 
 def _stream() -> int:
@@ -293,6 +304,12 @@ class WoqContext:
 
     def workspace_bytes(self, m: int) -> int:
         return lib().woq_b200_workspace_bytes(self._h, m)
+
+    def decode_plan(self, m: int) -> dict:
+        """How the M <= 16 kernel would be launched for this layer (woq_b200_decode_plan)."""
+        out = (ctypes.c_int32 * 4)()
+        _check(lib().woq_b200_decode_plan(self._h, m, out))
+        return {"grid": out[0], "cluster": out[1], "kblocks_per_warp": out[2], "smem_budget": out[3]}
 
     def workspace(self, m: int) -> Workspace:
         need = self.workspace_bytes(m)
