@@ -32,10 +32,10 @@ for _p in (ROOT, PKG_DIR):
 
 HIDDEN, QKV_N, FFN, LAYERS, GROUP = 8192, 10240, 28672, 80, 128
 METRIC = "int4_woq_linear_weight_GBps_decode"
-# DRAM bytes (read + write) per algorithmic byte of the decode kernel, from the ncu capture
-# summarised in profiles/decode_int4_57344x8192_m1.md (the device keeps 4 bytes of scale and
-# zero point per row and group against 3 algorithmic ones, and split-K partial tiles are
-# written and read back); the traffic of a launch grows in proportion to its bytes.
+# DRAM bytes (read + write) per algorithmic byte of the decode kernel, from an ncu capture of a
+# gate_up-sized launch (the device keeps 4 bytes of scale and zero point per row and group
+# against 3 algorithmic ones, and split-K partial tiles are written and read back); the
+# traffic of a launch grows in proportion to its bytes.
 TRAFFIC_RATIO = 1.041
 FUSED_MAX_TOKENS = 8  # --collective auto: largest decode batch that takes the fused exchange
 UNIT = "GB/s"
@@ -119,12 +119,34 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------
 # reference arm: the CPU restatement of the reference's WOQ kernel on the host cores
 # ------------------------------------------------------------------------------------------
-def cpu_baseline(m, passes=3):
-    """Times oracle/woq_oracle_c.c (OpenMP, all host threads) on one of the 80 layers."""
+def host_cpu():
+    """Model name, logical CPUs and the ISA flags that matter for the reference's WOQ kernels."""
+    model, flags = "unknown", []
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name") and model == "unknown":
+                model = line.split(":", 1)[1].strip()
+            elif line.startswith("flags") and not flags:
+                have = set(line.split(":", 1)[1].split())
+                flags = [f for f in ("avx2", "avx512f", "avx512bw", "avx512_vnni", "avx512_bf16", "avx512_fp16",
+                                     "amx_bf16", "amx_int8") if f in have]
+    except OSError:
+        pass
+    return {"model": model, "logical_cpus": os.cpu_count(), "isa": flags}
+
+
+def cpu_baseline(m, warmup=5, passes=20):
+    """Times the C restatement of the reference's CPU kernel (oracle/woq_oracle_c.c, OpenMP on
+    every logical CPU of the host, set explicitly: a launcher's OMP_NUM_THREADS does not apply)
+    on one of the 80 layers.  Fewer than 5 tokens take the reference's fp16 small-M microkernel
+    (AVX512-FP16 intrinsics) where the CPU has it, as the reference's own dispatch does; otherwise
+    the bf16 tile kernel.  Median of `passes` passes after `warmup` warm-up passes."""
     import numpy as np
 
     from oracle import woq_oracle_c as OC
 
+    threads = os.cpu_count() or 1
+    small = m < 5 and OC.has_fp16_kernel()
     rng = np.random.default_rng(0)
     layers = []
     for name, n, k, _ in layer_shapes(1):
@@ -133,27 +155,38 @@ def cpu_baseline(m, passes=3):
         z = rng.integers(0, 16, (n, k // GROUP)).astype(np.float32)
         layers.append((name, OC.Layer(qw, n, k, s, z, None, GROUP), n, k))
     xs = {k: (rng.standard_normal((m, k)).astype(np.float32)) for k in (HIDDEN, FFN)}
-    for _, L, n, k in layers:  # warm-up pass
-        L.linear_bf16(xs[k], 0x100 if n == 2 * FFN else 0)
-    t0 = time.perf_counter()
-    for _ in range(passes):
+
+    def one_pass():
         for _, L, n, k in layers:
-            L.linear_bf16(xs[k], 0x100 if n == 2 * FFN else 0)
-    dt = (time.perf_counter() - t0) / passes
+            fusion = 0x100 if n == 2 * FFN else 0
+            if small:
+                L.linear_fp16_small_m(xs[k], fusion, threads=threads)
+            else:
+                L.linear_bf16(xs[k], fusion, threads=threads)
+
+    for _ in range(max(1, warmup)):
+        one_pass()
+    times = []
+    for _ in range(max(1, passes)):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
     gbps = full_layer_weight_bytes() / dt / 1e9
-    return {"value": gbps, "unit": UNIT, "cores": OC.max_threads(), "kind": "port",
+    kernel = ("fp16 small-M microkernel, AVX512-FP16 intrinsics (the reference's route for M < 5)" if small
+              else "bf16 tile-dequant + block GEMM, compiler-vectorised loops")
+    return {"value": gbps, "unit": UNIT, "cores": threads, "kind": "port", "cpu": host_cpu(), "kernel": kernel,
             "sample": f"1 of {LAYERS} layers (4 linears, {full_layer_weight_bytes() / 1e6:.0f} MB of "
-                      f"weights), M={m}, {passes} passes after 1 warm-up, blocked-layout C port of "
-                      "the reference kernel with OpenMP"}, dt
+                      f"weights), M={m}, median of {passes} passes after {warmup} warm-up, blocked-layout C "
+                      f"restatement of the reference kernel with OpenMP on {threads} threads"}, dt
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warm = max(1, args.steps), args.warmup
-    passes = max(1, min(steps, 5))
-    cb, dt = cpu_baseline(args.m, passes=passes)
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    cb, dt = cpu_baseline(args.m, warmup=max(5, warm), passes=max(20, steps))
     line = {
         "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": dt * 1e3 * LAYERS, "higher_is_better": True,
@@ -182,7 +215,7 @@ def build_layers(torch, capi, quant, p, rank, n_layers, device, m=1):
             qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
             del w
             # one tiling is enough: the streaming one for decode sizes, the tensor-core one above
-            flags = (capi.LAYOUT_STREAM_ONLY if m <= 16 else capi.LAYOUT_TC_ONLY) | (
+            flags = (capi.LAYOUT_STREAM_ONLY if m <= 16 else capi.LAYOUT_TC_ONLY) | capi.LAYOUT_DEFER_CHECK | (
                 capi.LAYOUT_GATE_UP if name == "gate_up" else 0)
             row[name] = capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP,
                                         capi.LOWP_BF16, layout_flags=flags)
@@ -190,6 +223,144 @@ def build_layers(torch, capi, quant, p, rank, n_layers, device, m=1):
         layers.append(row)
     torch.cuda.synchronize()
     return layers
+
+
+def _parity(torch, y, ref):
+    """max |y - ref| / ||ref||_inf and mean |y - ref| / mean |ref| (the tolerances of the tests:
+    1e-2 and 2e-3)."""
+    y, ref = y.float(), ref.float()
+    d = (y - ref).abs()
+    return float(d.max() / ref.abs().max()), float(d.mean() / ref.abs().mean())
+
+
+def verify_step(torch, dist, capi, L, p, rank, m, ws, hidden, resid, attn_slice, fused, comm, act_off,
+                qkv_out, o_out, act_out, d_out):
+    """Checks what the eager step left behind for the LAST layer (every layer gets the same
+    inputs, so the output buffers hold the last layer's results) before anything is timed.
+    The yardstick is a plain fp32 matmul on the layer's dequantised weights (dumped by the
+    library, which the tests pin bit for bit to the CPU oracle), with the partial sums of a
+    row-parallel layer added across ranks in fp32.  With N > 1 it also checks that every rank
+    holds the same bits.  Raises on a mismatch; returns the figures for the JSON line."""
+    bf = torch.bfloat16
+
+    def deq(ctx):
+        return ctx.dump_dequant().float()
+
+    def silu_mul(y):
+        half = y.shape[-1] // 2
+        gate, up = y[:, :half].to(bf).float(), y[:, half:].to(bf).float()
+        sig = torch.sigmoid(gate).to(bf).float()
+        return ((gate * sig).to(bf).float() * up).to(bf)
+
+    def reduce_ranks(t):
+        if p > 1:
+            dist.all_reduce(t)
+        return t
+
+    def gather_ranks(t):
+        if p == 1:
+            return t
+        out = torch.empty((p,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous())
+        return out.permute(1, 0, 2).reshape(t.shape[0], -1)
+
+    if fused:
+        qkv_out = comm.gathered(0, m, QKV_N)
+        act_out = comm.gathered(act_off, m, FFN)
+    else:
+        # NCCL path: [p, m, n/p] buffers (or the local [m, n] ones on one GPU)
+        if p > 1:
+            qkv_out = qkv_out.permute(1, 0, 2).reshape(m, -1)
+            act_out = act_out.permute(1, 0, 2).reshape(m, -1)
+    worst = [0.0, 0.0]
+
+    def compare(name, y, ref):
+        mx, mr = _parity(torch, y, ref)
+        worst[0], worst[1] = max(worst[0], mx), max(worst[1], mr)
+        if not (mx <= 1e-2 and mr <= 2e-3):
+            raise RuntimeError(f"bench check failed on rank {rank}: {name} max-abs/inf {mx:.3e}, mean-rel {mr:.3e}")
+
+    qkv_ref = gather_ranks((hidden.float() @ deq(L["qkv"]).T).to(bf))
+    compare("qkv", qkv_out, qkv_ref)
+    o_part = (attn_slice.float() @ deq(L["o_proj"]).T)
+    o_ref = (reduce_ranks(o_part.to(bf).float() if p > 1 else o_part).to(bf).float() + resid.float()).to(bf)
+    compare("o_proj", o_out, o_ref)
+    act_ref = gather_ranks(silu_mul(o_out.float() @ deq(L["gate_up"]).T))
+    compare("gate_up", act_out, act_ref)
+    act_mine = act_out[:, rank * (FFN // p):(rank + 1) * (FFN // p)]
+    d_part = (act_mine.float() @ deq(L["down_proj"]).T)
+    d_ref = (reduce_ranks(d_part.to(bf).float() if p > 1 else d_part).to(bf).float() + resid.float()).to(bf)
+    compare("down_proj", d_out, d_ref)
+    identical = True
+    if p > 1:
+        sums = torch.stack([t.contiguous().view(torch.int16).to(torch.int64).sum()
+                            for t in (qkv_out, o_out, act_out, d_out)])
+        every = torch.empty((p, 4), dtype=torch.int64, device=sums.device)
+        dist.all_gather_into_tensor(every, sums)
+        identical = bool((every == every[0]).all())
+        if not identical:
+            raise RuntimeError(f"bench check failed: ranks hold different output bits: {every.tolist()}")
+    ws.status()
+    torch.cuda.empty_cache()
+    return {"max_abs_over_inf": worst[0], "mean_rel": worst[1], "ranks_identical": identical,
+            "against": "fp32 matmul on the dequantised weights of the last layer, partial sums added over ranks in fp32"}
+
+
+def e2e_through_ops(torch, quant, m, device, n_layers=4, steps=20):
+    """The step of `n_layers` layers through the registered operators (torch.ops.torch_ipex.*
+    on contexts made by torch.ops.ipex_prepack.*), host activations in and host result out every
+    step, eager (no CUDA graph): what a caller of the reference's op surface pays per call."""
+    from ipex_b200 import _ops
+
+    _ops.load_ops()
+    pre = torch.ops.ipex_prepack
+    ops = torch.ops.torch_ipex
+    layers = []
+    for l in range(n_layers):
+        row = {}
+        for name, n, k, _ in layer_shapes(1):
+            g = torch.Generator(device=device).manual_seed(5000 + 10 * l + len(row))
+            w = torch.randn((n, k), device=device, generator=g) * 0.02
+            qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
+            del w
+            if name == "gate_up":
+                row[name] = pre.weight_only_qlinear_prepack_gate_up(qw, 2, [n, k], s.half(), z, None, GROUP, 2, -1)
+            else:
+                row[name] = pre.weight_only_qlinear_prepack(qw, 2, [n, k], s.half(), z, None, None, None, GROUP, 2,
+                                                            -1, False)
+            del qw, s, z
+        layers.append({k_: (v, v.get_data_handle()) for k_, v in row.items()})
+    bf = dict(dtype=torch.bfloat16, device=device)
+    hidden = torch.empty((m, HIDDEN), **bf)
+    resid = torch.randn((m, HIDDEN), **bf)
+    attn = torch.randn((m, HIDDEN), **bf)
+    x_host = torch.randn((m, HIDDEN)).bfloat16().pin_memory()
+    y_host = torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
+
+    def step():
+        hidden.copy_(x_host, non_blocking=True)
+        d = None
+        for L in layers:
+            ops.ipex_woq_linear(hidden, L["qkv"][1])
+            o = ops.woq_linear_add(attn, L["o_proj"][1], [resid])
+            a = ops.woq_linear_silu_mul(o, L["gate_up"][1])
+            d = ops.woq_linear_add(a, L["down_proj"][1], [resid])
+        y_host.copy_(d, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    ops.woq_check_status()
+    del layers
+    torch.cuda.empty_cache()
+    return {"value": full_layer_weight_bytes() * n_layers / dt / 1e9, "unit": UNIT, "layers": n_layers,
+            "ms_per_step": dt * 1e3, "us_per_linear": dt * 1e6 / (4 * n_layers), "cuda_graph": False,
+            "h2d_bytes_per_step": m * HIDDEN * 2, "d2h_bytes_per_step": m * HIDDEN * 2,
+            "api": "torch.ops.torch_ipex.{ipex_woq_linear, woq_linear_add, woq_linear_silu_mul}"}
 
 
 def run_ours(args):
@@ -293,6 +464,12 @@ def run_ours(args):
     # kernels this library really launched for one step (a linear above 256 tokens is several)
     launched_per_step = capi.kernel_launches() - launches_before
     log("eager step done")
+    check = None if args.no_check else verify_step(torch, dist, capi, layers[-1], p, rank, m, ws, hidden, resid,
+                                                     attn_slice, fused, comm, act_off if fused else 0,
+                                                     qkv_local if p == 1 else (None if fused else qkv_full),
+                                                     o_out, act_local if p == 1 else (None if fused else act_full),
+                                                     d_out)
+    log(f"outputs checked: {check}")
     graph = None
     if not args.no_graph:
         try:
@@ -421,6 +598,11 @@ def run_ours(args):
     e2e = {"value": total_w / e2e_s / 1e9, "unit": UNIT, "h2d_bytes_per_step": m * HIDDEN * 2,
            "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": e2e_s * 1e3}
 
+    e2e_ops = None
+    if p == 1 and m <= 16 and not args.no_e2e_ops:
+        e2e_ops = e2e_through_ops(torch, quant, m, device)
+        log(f"e2e through the ops: {e2e_ops}")
+
     # ---- prefill side of the metric: the tcgen05 kernel on one gate_up-sized layer ----------
     prefill = None
     if p == 1 and not args.no_prefill:
@@ -466,7 +648,8 @@ def run_ours(args):
                                       if fused else "nccl"),
                        "l2": f"weights ({total_w / 1e9:.1f} GB per step over all ranks) exceed L2; no flush needed",
                        "cuda_graph": graph is not None},
-            "roofline": roofline, "prefill": prefill, "e2e": e2e, "gpu_launches": launched_per_step * args.steps,
+            "roofline": roofline, "prefill": prefill, "e2e": e2e, "e2e_ops": e2e_ops,
+            "checked": check is not None, "check": check, "gpu_launches": launched_per_step * args.steps,
             "clocks": clocks,
         }
         if p == 1 and not args.no_cpu_baseline:
@@ -712,6 +895,8 @@ def main():
                     help="N > 1: exchange inside the linear kernels, NCCL after them, or (auto) the "
                          "fused exchange up to %d tokens" % FUSED_MAX_TOKENS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the check of the step's outputs before timing")
+    ap.add_argument("--no-e2e-ops", action="store_true", help="skip the end-to-end leg through torch.ops")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (tensor-core kernel) side line")
     ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
     ap.add_argument("--int8", action="store_true", help="--single: INT8 weights with INT8 compute")

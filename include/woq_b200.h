@@ -94,6 +94,12 @@ extern "C" {
 /* GPTQ / AWQ weights whose scales and zero points were already brought to [N, groups]
  * (what the reference's Python loaders hand to weight_only_qlinear_prepack_int4). */
 #define WOQ_B200_LAYOUT_SCALES_NK 0x8
+/* woq_b200_ctx_create validates the zero points on the device.  Normally it waits for the
+ * verdict (one stream synchronisation per context); with this flag the verdict travels to the
+ * host asynchronously and the first woq_b200_linear* call on the context reports it, so a
+ * loader can create hundreds of contexts back to back.  The inputs must stay alive until the
+ * stream has passed the create call either way.  Plain-format INT4 contexts only. */
+#define WOQ_B200_LAYOUT_DEFER_CHECK 0x10
 
 /* kernel selection for INT4 weights.  AUTO, TENSOR_CORE and STREAM all multiply by the
  * bf16-rounded dequantised weights bf16((q - zp) * bf16(scale)) and differ only in summation
@@ -152,7 +158,7 @@ int woq_b200_set_option(int32_t option, int32_t value);
  * scale/zero-point re-layout of ContextLinearWoq (csrc/cpu/jit/cpu/kernels/ContextLinearWoq.h:36-128).
  * Allocates the packed buffers with cudaMalloc on the current device; inputs may be freed
  * once the stream has passed this call.  Synchronises the stream once to validate the zero
- * points. */
+ * points (see WOQ_B200_LAYOUT_DEFER_CHECK). */
 int woq_b200_ctx_create(const woq_b200_desc* desc, const void* qweight, const void* scales,
                         const void* zero_points, const void* bias, void* stream,
                         woq_b200_ctx** out);
@@ -183,8 +189,9 @@ size_t woq_b200_workspace_header_bytes(void);
  * (csrc/cpu/aten/Linear.cpp:499-811 -> qlinear_woq_affine,
  * csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:56-165).  `others` is a HOST array of n_others
  * device pointers to [M, N] bf16 tensors (ADD: 1, ADD_ADD: 2, MUL: 1).  x rows are ldx
- * elements apart, y rows ldy (pass K and N_out for dense tensors).  N_out = N, or N/2 for
- * WOQ_B200_FUSE_SILU_MUL. */
+ * elements apart; y rows AND the rows of the extra tensors are ldy elements apart (pass K and
+ * N_out for dense tensors).  N_out = N, or N/2 for WOQ_B200_FUSE_SILU_MUL.  The current device
+ * must be the one the context was created on. */
 int woq_b200_linear(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx, int32_t fusion,
                     const void* const* others, int32_t n_others, void* y, int64_t ldy,
                     void* workspace, size_t workspace_bytes, void* stream);
@@ -243,10 +250,19 @@ int woq_b200_linear_allgather(const woq_b200_ctx* ctx, const woq_b200_comm* comm
  * for m > 16 and WOQ_B200_ERR_WORKSPACE when the GPU would need more than the 4 MiB (more than
  * 252 SMs).  The first call on each device looks up the array's address; make that call
  * outside any stream capture.  All calls on one GPU share the array: they must be
- * stream-ordered, two that overlap on the device race on the partial tiles and counters. */
+ * stream-ordered, two that overlap on the device race on the partial tiles and counters.  The
+ * current device must be the one the context was created on (the array used is the current
+ * device's). */
 int woq_b200_linear_static_scratch(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
                                    int32_t fusion, const void* const* others, int32_t n_others,
                                    void* y, int64_t ldy, void* stream);
+
+/* No counterpart in the reference.  woq_b200_workspace_status for the built-in array of the
+ * current device: synchronises the stream, returns WOQ_B200_ERR_DEVICE_WAIT if a kernel of an
+ * earlier woq_b200_linear_static_scratch call gave up a bounded wait (its output is then not
+ * valid), and clears the record.  Until it is called the record stays, and later kernels on the
+ * array do not wait either. */
+int woq_b200_static_scratch_status(void* stream);
 
 /* One expert of a mixture-of-experts layer on gathered tokens:
  * out[row_idx[i], :] = bf16(out[row_idx[i], :] + y[i, :] * row_weight[i]) with

@@ -26,6 +26,7 @@
 namespace {
 
 constexpr int64_t kHandleMagic = 0x574f5148414e444cll;  // "WOQHANDL"
+constexpr int64_t kGateUpStateBit = 0x100;                // pickled weight_dtype of a gate/up context
 
 int dtype_code(const at::Tensor& t) {
   switch (t.scalar_type()) {
@@ -46,16 +47,36 @@ int dtype_code(const at::Tensor& t) {
 
 // One zeroed workspace per (device, stream); grows on demand.  Calls on one stream are ordered,
 // which is what a shared workspace needs.
+std::mutex g_ws_mu;
+std::map<std::pair<int, cudaStream_t>, at::Tensor> g_ws_pool;
+
 at::Tensor& workspace_for(c10::DeviceIndex dev, cudaStream_t stream, size_t bytes) {
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, at::Tensor> pool;
-  std::lock_guard<std::mutex> lock(mu);
-  auto& t = pool[{dev, stream}];
+  // the same (device, stream) as the previous call of this thread: no lock, no look-up
+  thread_local int last_dev = -1;
+  thread_local cudaStream_t last_stream = nullptr;
+  thread_local at::Tensor* last = nullptr;
+  if (last && last_dev == dev && last_stream == stream && static_cast<size_t>(last->numel()) >= bytes) return *last;
+  std::lock_guard<std::mutex> lock(g_ws_mu);
+  auto& t = g_ws_pool[{dev, stream}];
   if (!t.defined() || static_cast<size_t>(t.numel()) < bytes) {
     t = at::zeros({static_cast<int64_t>(bytes)},
                   at::TensorOptions().dtype(at::kByte).device(at::Device(at::kCUDA, dev)));
   }
+  last_dev = dev;
+  last_stream = stream;
+  last = &t;  // std::map never moves its elements
   return t;
+}
+
+// Synchronises every stream that has run a WOQ op and raises if a kernel gave up one of its
+// bounded waits (its output is then not valid).  The ops themselves never synchronise.
+void woq_check_status() {
+  std::lock_guard<std::mutex> lock(g_ws_mu);
+  for (auto& kv : g_ws_pool) {
+    if (!kv.second.defined()) continue;
+    c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(kv.first.first));
+    WOQ_CHECK(woq_b200_workspace_status(kv.second.data_ptr(), kv.first.second));
+  }
 }
 
 // plain INT4 weight [N, K/2] (k even in the low nibble) with its input channels re-ordered
@@ -69,6 +90,11 @@ at::Tensor shuffle_int4_columns(const at::Tensor& w, const at::Tensor& order) {
 struct WoqLinearOpContext : torch::CustomClassHolder {
   int64_t magic = kHandleMagic;
   woq_b200_ctx* ctx = nullptr;
+  // INT4: `ctx` keeps the streaming tiling only (M <= 16); the tensor-core tiling is packed into
+  // a second context the first time a call brings more than 16 tokens, so that a model that only
+  // decodes holds one copy of its weights.
+  woq_b200_ctx* ctx_tc = nullptr;
+  std::mutex tc_mu;
   // constructor arguments, kept so that the context can be pickled in a layout-independent way
   int64_t weight_dtype, group_size, lowp_mode, act_quant_mode;
   bool cache_weight_for_large_batch;
@@ -81,6 +107,27 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
 
   ~WoqLinearOpContext() override {
     if (ctx) woq_b200_ctx_destroy(ctx);
+    if (ctx_tc) woq_b200_ctx_destroy(ctx_tc);
+  }
+
+  // the context a call with M tokens runs on
+  woq_b200_ctx* ctx_for(int64_t M) {
+    if (M <= 16 || weight_dtype != WOQ_B200_DTYPE_INT4 || (layout_flags & WOQ_B200_LAYOUT_TC_ONLY)) return ctx;
+    std::lock_guard<std::mutex> lock(tc_mu);
+    if (!ctx_tc) {
+      woq_b200_desc d{};
+      WOQ_CHECK(woq_b200_ctx_desc(ctx, &d));
+      d.weight_format = WOQ_B200_FMT_PLAIN;  // the plain weight comes out of the first context
+      d.layout_flags = (d.layout_flags & ~WOQ_B200_LAYOUT_STREAM_ONLY) | WOQ_B200_LAYOUT_TC_ONLY | WOQ_B200_LAYOUT_SCALES_NK;
+      auto stream = at::cuda::getCurrentCUDAStream(device);
+      auto plain = at::empty({weight_shape[0], (weight_shape[1] + 1) / 2},
+                             at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
+      WOQ_CHECK(woq_b200_ctx_unpack(ctx, plain.data_ptr(), stream.stream()));
+      WOQ_CHECK(woq_b200_ctx_create(&d, plain.data_ptr(), scales.data_ptr(),
+                                    zero_points.defined() ? zero_points.data_ptr() : nullptr,
+                                    bias.defined() ? bias.data_ptr() : nullptr, stream.stream(), &ctx_tc));
+    }
+    return ctx_tc;
   }
 
   static c10::intrusive_ptr<WoqLinearOpContext> create(
@@ -139,6 +186,8 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
     d.zp_dtype = z.defined() ? dtype_code(z) : WOQ_B200_T_NONE;
     d.bias_dtype = b.defined() ? dtype_code(b) : WOQ_B200_T_NONE;
     d.layout_flags = static_cast<int32_t>(layout_flags) | WOQ_B200_LAYOUT_SCALES_NK;
+    if (weight_dtype == WOQ_B200_DTYPE_INT4 && !(layout_flags & (WOQ_B200_LAYOUT_STREAM_ONLY | WOQ_B200_LAYOUT_TC_ONLY)))
+      d.layout_flags |= WOQ_B200_LAYOUT_STREAM_ONLY;
     d.kernel_hint = WOQ_B200_HINT_AUTO;
     auto stream = at::cuda::getCurrentCUDAStream(dev.index());
     WOQ_CHECK(woq_b200_ctx_create(&d, w.data_ptr(), s.data_ptr(), z.defined() ? z.data_ptr() : nullptr,
@@ -183,6 +232,38 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
   c10::optional<at::Tensor> get_cached_weight() { return c10::nullopt; }
   c10::optional<at::Tensor> get_cached_compensation() { return c10::nullopt; }
   at::Tensor pack(const at::Tensor& w) { return w; }
+  // reference: WoqLinearOpContext::load_from_ctx (csrc/cpu/jit/cpu/kernels/OpContext.cpp) takes
+  // over the packed weight and metadata of another context; here the other context's plain
+  // weight is packed anew on this context's device
+  void load_from_ctx(c10::intrusive_ptr<WoqLinearOpContext> other) {
+    TORCH_CHECK(other && other->ctx, "WOQ: load_from_ctx needs a live context");
+    if (other.get() == this) return;
+    auto fresh = create(other->get_weight(), other->weight_dtype, other->weight_shape, other->scales,
+                        other->zero_points.defined() ? c10::make_optional(other->zero_points) : c10::nullopt,
+                        other->bias.defined() ? c10::make_optional(other->bias) : c10::nullopt,
+                        other->g_idx.defined() ? c10::make_optional(other->g_idx) : c10::nullopt, other->batch_size,
+                        other->group_size, other->lowp_mode, other->act_quant_mode,
+                        other->cache_weight_for_large_batch, WOQ_B200_FMT_PLAIN,
+                        other->layout_flags & WOQ_B200_LAYOUT_GATE_UP);
+    std::lock_guard<std::mutex> lock(tc_mu);
+    std::swap(ctx, fresh->ctx);
+    std::swap(ctx_tc, fresh->ctx_tc);
+    weight_dtype = fresh->weight_dtype;
+    group_size = fresh->group_size;
+    lowp_mode = fresh->lowp_mode;
+    act_quant_mode = fresh->act_quant_mode;
+    cache_weight_for_large_batch = fresh->cache_weight_for_large_batch;
+    weight_shape = fresh->weight_shape;
+    scales = fresh->scales;
+    zero_points = fresh->zero_points;
+    bias = fresh->bias;
+    g_idx = fresh->g_idx;
+    perm = fresh->perm;
+    inv_perm = fresh->inv_perm;
+    batch_size = fresh->batch_size;
+    device = fresh->device;
+    layout_flags = fresh->layout_flags;
+  }
   // CPU int64 tensor holding the raw pointer to this object (non-owning), as in the reference
   at::Tensor get_data_handle() {
     auto t = at::empty({1}, at::TensorOptions().dtype(at::kLong));
@@ -211,7 +292,14 @@ at::Tensor run(WoqLinearOpContext* c, const at::Tensor& input, int32_t fusion,
   at::Tensor x = input.reshape({-1, K});
   if (c->perm.defined()) x = x.index_select(1, c->perm);  // act-order: channels in group order
   const auto in_dtype = x.scalar_type();
-  if (in_dtype != at::kBFloat16) x = x.to(at::kBFloat16);  // compute dtype of this path
+  // lowp NONE computes in the activation's dtype (reference: WoqLinearKrnl.cpp:75-106 routes fp32
+  // and fp16 activations to fp32 / fp16 kernels); only the bf16 route is built, and running the
+  // others in bf16 would narrow them without a word.  lowp BF16 and INT8 convert the activation
+  // themselves in the reference, so any floating input is taken there.
+  TORCH_CHECK(c->lowp_mode != WOQ_B200_LOWP_NONE || in_dtype == at::kBFloat16,
+              "WOQ: lowp_mode NONE computes in the activation dtype and only bfloat16 activations are built "
+              "(got ", in_dtype, "); use lowp_mode BF16 or cast the activation");
+  if (in_dtype != at::kBFloat16) x = x.to(at::kBFloat16);
   if (x.stride(-1) != 1 || (x.stride(0) % 8) != 0 || (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15))
     x = x.contiguous();
   const int64_t M = x.size(0);
@@ -228,9 +316,10 @@ at::Tensor run(WoqLinearOpContext* c, const at::Tensor& input, int32_t fusion,
   }
   auto stream = at::cuda::getCurrentCUDAStream(c->device);
   if (M > 0) {
-    const size_t need = woq_b200_workspace_bytes(c->ctx, M);
+    woq_b200_ctx* k = c->ctx_for(M);
+    const size_t need = woq_b200_workspace_bytes(k, M);
     at::Tensor& ws = workspace_for(c->device, stream.stream(), need);
-    WOQ_CHECK(woq_b200_linear(c->ctx, x.data_ptr(), M, x.stride(0), fusion,
+    WOQ_CHECK(woq_b200_linear(k, x.data_ptr(), M, x.stride(0), fusion,
                               optr.empty() ? nullptr : optr.data(), static_cast<int32_t>(optr.size()),
                               y.data_ptr(), y.stride(0), ws.data_ptr(), ws.numel(), stream.stream()));
   }
@@ -285,8 +374,9 @@ at::Tensor mixtral_moe_woq(const at::Tensor& hidden_states, const at::Tensor& to
   a = a.contiguous();
   const int64_t M = a.size(0);
   auto stream = at::cuda::getCurrentCUDAStream(d->device);
-  at::Tensor& ws = workspace_for(d->device, stream.stream(), woq_b200_workspace_bytes(d->ctx, M));
-  WOQ_CHECK(woq_b200_linear_scatter(d->ctx, a.data_ptr(), M, a.stride(0), ti.data_ptr<int32_t>(), w.data_ptr(),
+  woq_b200_ctx* dk = d->ctx_for(M);
+  at::Tensor& ws = workspace_for(d->device, stream.stream(), woq_b200_workspace_bytes(dk, M));
+  WOQ_CHECK(woq_b200_linear_scatter(dk, a.data_ptr(), M, a.stride(0), ti.data_ptr<int32_t>(), w.data_ptr(),
                                     output.data_ptr(), output.stride(0), ws.data_ptr(), ws.numel(),
                                     stream.stream()));
   return output;
@@ -429,25 +519,30 @@ TORCH_LIBRARY(ipex_prepack, m) {
       .def("pack", &WoqLinearOpContext::pack)
       .def("to_public", &WoqLinearOpContext::to_public)
       .def("get_data_handle", &WoqLinearOpContext::get_data_handle)
+      .def("load_from_ctx", &WoqLinearOpContext::load_from_ctx)
       .def_pickle(
-          // state: plain weight + every constructor argument (layout-independent)
+          // state: the reference's 12-tuple (csrc/cpu/jit/cpu/kernels/OpContext.h:363-375) with the
+          // weight in its plain format; a gate/up-interleaved context marks itself with one
+          // extra bit in the weight dtype
           [](const c10::intrusive_ptr<WoqLinearOpContext>& self) {
-            return std::make_tuple(self->get_weight().cpu(), self->weight_dtype, self->weight_shape,
+            return std::make_tuple(self->get_weight().cpu(),
+                                   self->weight_dtype | ((self->layout_flags & WOQ_B200_LAYOUT_GATE_UP) ? kGateUpStateBit : 0),
+                                   self->weight_shape,
                                    self->scales.cpu(),
                                    self->zero_points.defined() ? c10::make_optional(self->zero_points.cpu()) : c10::nullopt,
                                    self->bias.defined() ? c10::make_optional(self->bias.cpu()) : c10::nullopt,
                                    self->g_idx.defined() ? c10::make_optional(self->g_idx.cpu()) : c10::nullopt,
                                    self->batch_size, self->group_size,
-                                   self->lowp_mode, self->act_quant_mode, self->cache_weight_for_large_batch,
-                                   static_cast<int64_t>(self->layout_flags));
+                                   self->lowp_mode, self->act_quant_mode, self->cache_weight_for_large_batch);
           },
           [](std::tuple<at::Tensor, int64_t, std::vector<int64_t>, at::Tensor, c10::optional<at::Tensor>,
                         c10::optional<at::Tensor>, c10::optional<at::Tensor>, c10::optional<int64_t>, int64_t,
-                        int64_t, int64_t, bool, int64_t> st) {
-            return WoqLinearOpContext::create(std::get<0>(st), std::get<1>(st), std::get<2>(st), std::get<3>(st),
+                        int64_t, int64_t, bool> st) {
+            const int64_t wd = std::get<1>(st);
+            return WoqLinearOpContext::create(std::get<0>(st), wd & ~kGateUpStateBit, std::get<2>(st), std::get<3>(st),
                                               std::get<4>(st), std::get<5>(st), std::get<6>(st), std::get<7>(st),
                                               std::get<8>(st), std::get<9>(st), std::get<10>(st), std::get<11>(st),
-                                              WOQ_B200_FMT_PLAIN, std::get<12>(st));
+                                              WOQ_B200_FMT_PLAIN, (wd & kGateUpStateBit) ? WOQ_B200_LAYOUT_GATE_UP : 0);
           });
   m.def("weight_only_qlinear_prepack(Tensor W, int W_dtype, int[] W_shape, Tensor scales, Tensor? zero_points, "
         "Tensor? B, Tensor? g_idx, int? batch_size, int group_size, int lowp_mode, int act_quant_mode, "
@@ -481,6 +576,7 @@ TORCH_LIBRARY(torch_ipex, m) {
   m.def("woq_linear_mul(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
   m.def("mixtral_moe_woq(Tensor hidden_states, Tensor top_x, Tensor idx, Tensor gate_wei, Tensor up_wei, "
         "Tensor down_wei, Tensor routing_weights, Tensor output, bool is_distributed) -> Tensor");
+  m.def("woq_check_status() -> ()", woq_check_status);
   m.def("woq_linear(Tensor input, Tensor qweight, str weight_dtype, int[] weight_shape, Tensor[] weight_scales, "
         "Tensor[]? weight_zeros, Tensor[]? bias, Tensor? g_idx, int group_size, int lowp_mode, "
         "int act_quant_mode, Tensor? compensation) -> Tensor");

@@ -80,13 +80,48 @@ struct woq_b200_ctx {
   int kc_per_tile;   // INT8: K / 128
   float* bias;       // fp32 [n] or null
   size_t wq_bytes, sz_bytes;
+  // Prepack verdict (bit 0: a zero point is not an integer in 0..127, bit 1: scales or zero
+  // points outside the range of the shift-free dequantiser).  With WOQ_B200_LAYOUT_DEFER_CHECK
+  // the flag travels to pinned host memory asynchronously and is looked at by the first call
+  // that needs it, so that loading many layers does not synchronise once per layer.
+  int* d_flag;
+  int* h_flag;
+  cudaEvent_t flag_ready;
+  int flag_pending;  // 1 until the flag has been looked at
+  int flag_bad;
 };
 
+namespace woq {
+int ctx_device(const woq_b200_ctx* c) { return c && c->magic == kMagic ? c->device : -1; }
+}  // namespace woq
+
 namespace {
+
+// The buffers of a context (and the kernels' launch configuration) belong to one device: a
+// call made with another device current would hand this device's pointers to that one.
+int check_current_device(const woq_b200_ctx* c) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev != c->device)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "the context lives on device %d but device %d is current", c->device, dev);
+  return WOQ_B200_OK;
+}
 
 int check_ctx(const woq_b200_ctx* c) {
   if (!c) return fail(WOQ_B200_ERR_INVALID_ARG, "context is null");
   if (c->magic != kMagic) return fail(WOQ_B200_ERR_BAD_HANDLE, "context magic mismatch");
+  return WOQ_B200_OK;
+}
+
+// Looks at a deferred prepack verdict once (see woq_b200_ctx::d_flag).
+int settle_prepack_flag(const woq_b200_ctx* cc) {
+  woq_b200_ctx* c = const_cast<woq_b200_ctx*>(cc);
+  if (c->flag_pending) {
+    CUDA_TRY(cudaEventSynchronize(c->flag_ready));
+    c->flag_bad = (*c->h_flag & 1) ? 1 : 0;
+    c->plain_scales = (*c->h_flag & 2) ? 0 : 1;
+    c->flag_pending = 0;
+  }
+  if (c->flag_bad) return fail(WOQ_B200_ERR_INVALID_ARG, "zero points must be integers in [0, 127]");
   return WOQ_B200_OK;
 }
 
@@ -243,6 +278,14 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
   // ---- INT4 ----
   if (d->lowp_mode == WOQ_B200_LOWP_INT8)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 weights with INT8 compute are not built yet");
+  // This interface takes bf16 activations.  lowp NONE means "compute in the activation's
+  // dtype" in the reference (csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:75-106), which for bf16
+  // activations is the bf16 kernel, the same as lowp BF16.  FP16 compute would be narrowed
+  // silently by running it here, so it is refused.
+  if (d->lowp_mode == WOQ_B200_LOWP_FP16)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "lowp_mode FP16 (fp16 compute) is not built; BF16 and NONE with bf16 activations are");
+  if (d->lowp_mode != WOQ_B200_LOWP_BF16 && d->lowp_mode != WOQ_B200_LOWP_NONE)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "unknown lowp_mode %d", d->lowp_mode);
   if (d->k % 64 != 0)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 path needs K %% 64 == 0 (K=%lld)", (long long)d->k);
   const int64_t g_eff = d->group_size > 0 ? d->group_size : d->k;
@@ -282,10 +325,12 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
   uint8_t* tmp_plain = nullptr;
   uint8_t* tmp_zp = nullptr;
   auto cleanup = [&](int rc) {
-    if (d_flag) cudaFree(d_flag);
     if (tmp_plain) cudaFree(tmp_plain);
     if (tmp_zp) cudaFree(tmp_zp);
     if (rc != WOQ_B200_OK) {
+      if (c->d_flag) cudaFree(c->d_flag);
+      if (c->h_flag) cudaFreeHost(c->h_flag);
+      if (c->flag_ready) cudaEventDestroy(c->flag_ready);
       if (c->wq) cudaFree(c->wq);
       if (c->sz) cudaFree(c->sz);
       if (c->wq_tc) cudaFree(c->wq_tc);
@@ -314,7 +359,11 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
     CUDA_TRY_C(cudaMalloc(&c->wq_tc, c->wq_tc_bytes));
     CUDA_TRY_C(cudaMalloc(&c->sz_tc, c->sz_tc_bytes));
   }
-  CUDA_TRY_C(cudaMalloc(&d_flag, sizeof(int)));
+  CUDA_TRY_C(cudaMalloc(&c->d_flag, sizeof(int)));
+  CUDA_TRY_C(cudaMallocHost(&c->h_flag, sizeof(int)));
+  CUDA_TRY_C(cudaEventCreateWithFlags(&c->flag_ready, cudaEventDisableTiming));
+  d_flag = c->d_flag;
+  *c->h_flag = 0;
   CUDA_TRY_C(cudaMemsetAsync(d_flag, 0, sizeof(int), stream));
 
   const uint8_t* plain = static_cast<const uint8_t*>(qweight);
@@ -380,12 +429,15 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
     woq::count_launch();
     CUDA_TRY_C(cudaGetLastError());
   }
-  int h_flag = 0;
-  CUDA_TRY_C(cudaMemcpyAsync(&h_flag, d_flag, sizeof(int), cudaMemcpyDeviceToHost, stream));
-  CUDA_TRY_C(cudaStreamSynchronize(stream));
-  if (h_flag & 1)
-    return cleanup(fail(WOQ_B200_ERR_INVALID_ARG, "zero points must be integers in [0, 127]"));
-  c->plain_scales = (h_flag & 2) ? 0 : 1;
+  CUDA_TRY_C(cudaMemcpyAsync(c->h_flag, d_flag, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY_C(cudaEventRecord(c->flag_ready, stream));
+  c->flag_pending = 1;
+  c->plain_scales = 0;
+  if (!(d->layout_flags & WOQ_B200_LAYOUT_DEFER_CHECK) || tmp_plain || tmp_zp) {
+    // look at the verdict now (the temporaries of a checkpoint format are freed below, which
+    // waits for the device anyway)
+    if (int rc = settle_prepack_flag(c)) return cleanup(rc);
+  }
 #undef CUDA_TRY_C
   c->magic = kMagic;
   *out = c;
@@ -395,6 +447,9 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
 int woq_b200_ctx_destroy(woq_b200_ctx* c) {
   if (int rc = check_ctx(c)) return rc;
   c->magic = 0;
+  if (c->d_flag) cudaFree(c->d_flag);
+  if (c->h_flag) cudaFreeHost(c->h_flag);
+  if (c->flag_ready) cudaEventDestroy(c->flag_ready);
   cudaFree(c->wq);
   cudaFree(c->sz);
   cudaFree(c->wq_tc);
@@ -456,6 +511,7 @@ static int run_decode(const woq_b200_ctx* c, const void* x, int64_t m, int64_t l
                 woq_b200_workspace_bytes(c, m));
   if (c->tiles > kMaxCounterTiles)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the workspace header");
+  if (int rc = settle_prepack_flag(c)) return rc;
   woq::DecodeParams p{};
   p.wq = c->wq;
   p.sz = c->sz;
@@ -544,6 +600,7 @@ static int run_tc(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, 
                 woq_b200_workspace_bytes(c, m));
   if (c->tiles_tc > kMaxCounterTiles)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the workspace header");
+  if (int rc = settle_prepack_flag(c)) return rc;
   CUtensorMap xmap;
   const int64_t mt = m < 256 ? m : 256;
   int n_tok = static_cast<int>((mt + 15) / 16 * 16);
@@ -665,6 +722,7 @@ int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
   if (m == 0) return WOQ_B200_OK;
   if (!x || !y || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "x, y and workspace must be non-null");
   if (m < 0) return fail(WOQ_B200_ERR_INVALID_ARG, "negative M");
+  if (int rc = check_current_device(c)) return rc;
   if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
     return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
   int need = 0;
@@ -997,7 +1055,8 @@ int woq_b200_workspace_status(void* workspace, void* stream_) {
   CUDA_TRY(cudaMemcpyAsync(&h, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
   CUDA_TRY(cudaStreamSynchronize(stream));
   if (h != 0) {
-    CUDA_TRY(cudaMemsetAsync(workspace, 0, sizeof(int), stream));
+    // a kernel that gave up may have left arrival counters behind: the whole header starts over
+    CUDA_TRY(cudaMemsetAsync(workspace, 0, kWsHeaderBytes, stream));
     return fail(WOQ_B200_ERR_DEVICE_WAIT, "a bounded in-kernel wait gave up (code %d)", h);
   }
   return WOQ_B200_OK;

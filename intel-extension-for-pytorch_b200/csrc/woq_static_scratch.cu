@@ -7,7 +7,8 @@
 // re-entrant.  woq_b200_linear needs a caller-provided workspace (partial tiles of the
 // split-K reduction, per-tile arrival counters, a status word); this entry point takes that
 // workspace from a fixed array in the library's own device image instead, so the caller
-// passes nothing but inputs and outputs.
+// passes nothing but inputs and outputs.  woq_b200_static_scratch_status reads (and clears) the
+// array's status word, the way woq_b200_workspace_status does for a caller's workspace.
 //
 // The array below exists once per GPU that loads the library and stays resident until the
 // process exits.  In host code its name is only a handle for the runtime, not a device
@@ -32,6 +33,21 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 std::mutex g_mu;
 void* g_scratch_ptr[kMaxDevices] = {};
 
+// Address of the array on device `dev` (which must be current): looked up once per device.
+int scratch_for_device(int dev, void** out) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g_scratch_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p)
+      return woq::set_error(WOQ_B200_ERR_CUDA, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    // the array starts zeroed (static storage); nothing to clear here
+    g_scratch_ptr[dev] = p;
+  }
+  *out = g_scratch_ptr[dev];
+  return WOQ_B200_OK;
+}
+
 }  // namespace
 
 extern "C" int woq_b200_linear_static_scratch(const woq_b200_ctx* ctx, const void* x, int64_t m,
@@ -53,25 +69,31 @@ extern "C" int woq_b200_linear_static_scratch(const woq_b200_ctx* ctx, const voi
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     return woq::set_error(WOQ_B200_ERR_CUDA, "cudaGetDevice failed or device index out of range: %s",
                           cudaGetErrorString(e));
+  // the array of the CURRENT device is used, so that must be the device the context lives on
+  if (dev != woq::ctx_device(ctx))
+    return woq::set_error(WOQ_B200_ERR_INVALID_ARG, "the context lives on device %d but device %d is current",
+                          woq::ctx_device(ctx), dev);
   void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (!g_scratch_ptr[dev]) {
-      // set-up, once per device, with that device current
-      void* p = nullptr;
-      e = cudaGetSymbolAddress(&p, g_static_scratch);
-      if (e != cudaSuccess || !p)
-        return woq::set_error(WOQ_B200_ERR_CUDA, "cudaGetSymbolAddress failed: %s",
-                              cudaGetErrorString(e));
-      g_scratch_ptr[dev] = p;
-    }
-    scratch = g_scratch_ptr[dev];
-  }
-  // The array keeps whatever the previous call left.  The status word and the per-tile arrival
-  // counters must start at zero, the partial tiles are always written before they are read.
-  e = cudaMemsetAsync(scratch, 0, woq_b200_workspace_header_bytes(), static_cast<cudaStream_t>(stream));
+  if (int rc = scratch_for_device(dev, &scratch)) return rc;
+  // The array keeps whatever the previous call left.  The per-tile arrival counters must start
+  // at zero; the partial tiles are always written before they are read.  The status word is
+  // left alone: a call whose kernel gave up a bounded wait stays visible to
+  // woq_b200_static_scratch_status until that is called.
+  e = cudaMemsetAsync(static_cast<unsigned char*>(scratch) + 256, 0, woq_b200_workspace_header_bytes() - 256,
+                      static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
     return woq::set_error(WOQ_B200_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(e));
   return woq_b200_linear(ctx, x, m, ldx, fusion, others, n_others, y, ldy, scratch, kStaticScratchBytes,
                          stream);
+}
+
+extern "C" int woq_b200_static_scratch_status(void* stream) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return woq::set_error(WOQ_B200_ERR_CUDA, "cudaGetDevice failed or device index out of range: %s",
+                          cudaGetErrorString(e));
+  void* scratch = nullptr;
+  if (int rc = scratch_for_device(dev, &scratch)) return rc;
+  return woq_b200_workspace_status(scratch, stream);
 }

@@ -22,7 +22,7 @@ FMT_PLAIN, FMT_GPTQ, FMT_AWQ = 0, 1, 2
 FUSE_NONE, FUSE_GELU_ERF, FUSE_GELU_TANH, FUSE_RELU, FUSE_SILU = 0, 1, 2, 3, 4
 FUSE_ADD, FUSE_ADD_ADD, FUSE_MUL, FUSE_SILU_MUL = 0x10, 0x20, 0x30, 0x100
 T_NONE, T_F32, T_F16, T_BF16, T_U8, T_S8, T_I32 = 0, 1, 2, 3, 4, 5, 6
-LAYOUT_GATE_UP, LAYOUT_STREAM_ONLY, LAYOUT_TC_ONLY, LAYOUT_SCALES_NK = 1, 2, 4, 8
+LAYOUT_GATE_UP, LAYOUT_STREAM_ONLY, LAYOUT_TC_ONLY, LAYOUT_SCALES_NK, LAYOUT_DEFER_CHECK = 1, 2, 4, 8, 16
 HINT_AUTO, HINT_TENSOR_CORE, HINT_STREAM, HINT_STREAM_FAST = 0, 1, 2, 3
 OPT_DECODE_SPLIT = 1
 SPLIT_AUTO, SPLIT_STREAM_K, SPLIT_CLUSTER = 0, 1, 2
@@ -42,6 +42,7 @@ EXPORTS = [
     "woq_b200_linear",
     "woq_b200_linear_scatter",
     "woq_b200_linear_static_scratch",
+    "woq_b200_static_scratch_status",
     "woq_b200_moe_workspace_bytes",
     "woq_b200_moe_expert",
     "woq_b200_dump_dequant",
@@ -112,6 +113,7 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_workspace_header_bytes.restype = sz
     L.woq_b200_linear.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
     L.woq_b200_linear_static_scratch.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp]
+    L.woq_b200_static_scratch_status.argtypes = [vp]
     L.woq_b200_linear_scatter.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
     L.woq_b200_moe_workspace_bytes.argtypes = [vp, vp, i64]
     L.woq_b200_moe_workspace_bytes.restype = sz
@@ -142,6 +144,23 @@ def _check(rc: int):
 def set_option(option: int, value: int):
     """Process-wide tuning switch (woq_b200_set_option)."""
     _check(lib().woq_b200_set_option(option, value))
+
+
+def _others(others, m: int, n_out: int, out: torch.Tensor):
+    """Extra operands as the C ABI wants them: rows as far apart as the output's."""
+    oth = [o.reshape(m, n_out) for o in others]
+    if out.stride(0) == n_out:
+        return [o.contiguous() for o in oth]
+    for o in oth:
+        if o.stride(-1) != 1 or o.stride(0) != out.stride(0):
+            raise ValueError("extra operands must have the output's row stride "
+                             f"({out.stride(0)}), got {o.stride(0)}")
+    return oth
+
+
+def static_scratch_status():
+    """woq_b200_static_scratch_status on the current device: raises if a kernel gave up a wait."""
+    _check(lib().woq_b200_static_scratch_status(_stream()))
 
 
 def _stream() -> int:
@@ -336,7 +355,7 @@ class WoqContext:
         if out is None:
             out = torch.empty((m, n_out), dtype=torch.bfloat16, device=x.device)
         ws = workspace or self.workspace(m)
-        oth = [o.reshape(m, n_out).contiguous() for o in others]
+        oth = _others(others, m, n_out, out)
         arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
         with torch.cuda.device(self.device):
             _check(
@@ -393,7 +412,7 @@ class WoqContext:
         n_out = self.n // 2 if fusion == FUSE_SILU_MUL else self.n
         if out is None:
             out = torch.empty((m, n_out), dtype=torch.bfloat16, device=x.device)
-        oth = [o.reshape(m, n_out).contiguous() for o in others]
+        oth = _others(others, m, n_out, out)
         arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
         with torch.cuda.device(self.device):
             _check(

@@ -375,7 +375,14 @@ def woq_linear_bf16(
     x = np.ascontiguousarray(x, dtype=np.float32)
     M, K = x.shape
     w = dequantize_weight(qweight, scales, zps, dtype, K, group_size, scale_rounding)
-    acc = x @ w.T  # fp32 accumulate
+    return linear_from_dequantised(x, w, bias, fusion, others, return_f32)
+
+
+def linear_from_dequantised(x, w, bias=None, fusion: int = FUSE_NONE, others: Sequence[np.ndarray] = (),
+                            return_f32: bool = False) -> np.ndarray:
+    """The second half of woq_linear_bf16 for a weight that is already dequantised (a caller
+    that applies one large layer to several inputs dequantises it once)."""
+    acc = np.ascontiguousarray(x, dtype=np.float32) @ w.T  # fp32 accumulate
     if bias is not None:
         acc = acc + np.asarray(bias, dtype=np.float32)[None, :]
     if return_f32:

@@ -18,9 +18,15 @@
  *   - per-token symmetric int8 activation quantisation   csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750
  *   - int8 x int8 -> int32 per 128-k block, C += float(acc) * scale_a * scale_w
  *                                                        csrc/cpu/aten/utils/woq.h:2231-2354
+ *   - small-M (M < 5) fp16 microkernel: per 32-column block and 64-k block
+ *     acc[m][n] = sum_k x_fp16[m][k] * (LUT[q[k][n]] - zp[n]) with fp16 fused multiply-adds,
+ *     then C[m][n] += scale_fp16[n] * acc[m][n]; fp16 bias preloaded, fp16 -> bf16 at the end
+ *                                                        csrc/cpu/aten/utils/woq.h:784-951,1862-1920
+ *     (what qlinear_woq_affine runs for lowp BF16 and M < 5, kernels/WoqLinearKrnl.cpp:75-106)
  * The reference reaches its block GEMMs through libxsmm (BRGEMM), which is not part of the
  * reference tree; here they are plain loops the compiler vectorises (AVX-512 / AVX2 clones
- * picked at run time).  Parity of this file is pinned by tests that compare it with the
+ * picked at run time).  The small-M microkernel is written with AVX512-FP16 intrinsics like
+ * the reference's own (csrc/cpu/tpp/woq/vec.h) and is only offered where the CPU has them.  Parity of this file is pinned by tests that compare it with the
  * numpy oracle (oracle/woq_oracle.py), which in turn is pinned by the golden fixtures.
  */
 #include <math.h>
@@ -29,6 +35,10 @@
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
+#endif
+#if defined(__x86_64__) && defined(__GNUC__)
+#include <immintrin.h>
+#define WOQ_HAVE_FP16_KERNEL 1
 #endif
 
 #define NB 32 /* WOQ_N_BLOCK_SIZE, csrc/cpu/aten/utils/woq_defines.h:46 */
@@ -63,6 +73,7 @@ typedef struct {
   int n, k, npad, nc, kc, kb, group, ngroups, is_int8;
   uint8_t* packed;   /* INT4: [nc][kc][kb][16]; INT8: [nc][kc][kb][32] */
   float* scale;      /* [nc][ngroups][32]: bf16-rounded for INT4, fp32 for int8 compute */
+  float* scale32;    /* [nc][ngroups][32]: the fp32 scales as given (the fp16 kernel rounds them to fp16) */
   float* zp;         /* [nc][ngroups][32] */
   float* bias;       /* [npad] or NULL */
 } woq_layer;
@@ -76,7 +87,7 @@ static int pick_block_k(int k, int group, int base) {
 
 EXPORT void woq_oracle_layer_free(woq_layer* L) {
   if (!L) return;
-  free(L->packed); free(L->scale); free(L->zp); free(L->bias); free(L);
+  free(L->packed); free(L->scale); free(L->scale32); free(L->zp); free(L->bias); free(L);
 }
 
 /* scales: [n][ngroups] fp32 (already widened from fp16 if the checkpoint had fp16);
@@ -96,6 +107,7 @@ EXPORT woq_layer* woq_oracle_layer_create(const uint8_t* qweight, int n, int k, 
   L->packed = (uint8_t*)calloc((size_t)L->nc * L->kc, per_block);
   L->scale = (float*)calloc((size_t)L->nc * L->ngroups * NB, sizeof(float));
   L->zp = (float*)calloc((size_t)L->nc * L->ngroups * NB, sizeof(float));
+  L->scale32 = (float*)calloc((size_t)L->nc * L->ngroups * NB, sizeof(float));
   const int row_bytes = is_int8 ? k : (k + 1) / 2;
   for (int nc = 0; nc < L->nc; ++nc) {
     for (int kc = 0; kc < L->kc; ++kc) {
@@ -126,6 +138,7 @@ EXPORT woq_layer* woq_oracle_layer_create(const uint8_t* qweight, int n, int k, 
         float s = row < n ? scales[(size_t)row * L->ngroups + g] : 1.0f;
         float z = row < n ? (zps ? zps[(size_t)row * L->ngroups + g] : (is_int8 ? 0.f : 8.f)) : 0.f;
         L->scale[o] = int8_compute ? s : round_bf16(s);
+        L->scale32[o] = s;
         L->zp[o] = z;
       }
   }
@@ -275,6 +288,120 @@ EXPORT int woq_oracle_linear_bf16(const woq_layer* L, const uint16_t* x, int m, 
   }
   free(xf);
   return 0;
+}
+
+/* ---- small-M fp16 microkernel (woq.h:784-951) ------------------------------------------- */
+EXPORT int woq_oracle_has_fp16_kernel(void) {
+#ifdef WOQ_HAVE_FP16_KERNEL
+  return __builtin_cpu_supports("avx512fp16") && __builtin_cpu_supports("avx512bw");
+#else
+  return 0;
+#endif
+}
+
+#ifdef WOQ_HAVE_FP16_KERNEL
+#define FP16_TARGET __attribute__((target("avx512fp16,avx512bw,avx512vl,avx512dq,avx512f")))
+
+/* 32 floats -> 32 fp16 lanes (round to nearest even) */
+FP16_TARGET static inline __m512h load32_f32_as_ph(const float* p) {
+  const __m256h lo = _mm512_cvtxps_ph(_mm512_loadu_ps(p));
+  const __m256h hi = _mm512_cvtxps_ph(_mm512_loadu_ps(p + 16));
+  return _mm512_castsi512_ph(_mm512_inserti64x4(_mm512_castsi256_si512(_mm256_castph_si256(lo)),
+                                                _mm256_castph_si256(hi), 1));
+}
+
+/* One 32-column block, all K, M <= 4 token rows.  c[m] leaves as 32 fp16 lanes. */
+FP16_TARGET static void small_m_block_fp16(const woq_layer* L, int nc, const _Float16* xh, int m,
+                                           int kb_per_group, __m512h* c) {
+  /* LUT {0, ..., 15} as fp16 (asymmetric INT4; symmetric storage is q + 8 with zero point 8) */
+  __m512h lut;
+  {
+    _Float16 t[32];
+    for (int i = 0; i < 32; ++i) t[i] = (_Float16)(i & 15);
+    lut = _mm512_loadu_ph(t);
+  }
+  const __m128i nib = _mm_set1_epi8(0x0F);
+  for (int kc = 0; kc < L->kc; ++kc) {
+    const int g = kc / kb_per_group < L->ngroups ? kc / kb_per_group : L->ngroups - 1;
+    const size_t so = ((size_t)nc * L->ngroups + g) * NB;
+    const __m512h vs = load32_f32_as_ph(L->scale32 + so);
+    const __m512h vz = load32_f32_as_ph(L->zp + so);
+    const uint8_t* blk = L->packed + ((size_t)nc * L->kc + kc) * L->kb * (NB / 2);
+    __m512h acc[4];
+    for (int mm = 0; mm < m; ++mm) acc[mm] = _mm512_setzero_ph();
+    for (int kk = 0; kk < L->kb; ++kk) {
+      const __m128i b = _mm_loadu_si128((const __m128i*)(blk + kk * (NB / 2)));
+      _mm_prefetch((const char*)(blk + (kk + 64) * (NB / 2)), _MM_HINT_T0);
+      const __m256i lo = _mm256_cvtepu8_epi16(_mm_and_si128(b, nib));
+      const __m256i hi = _mm256_cvtepu8_epi16(_mm_and_si128(_mm_srli_epi16(b, 4), nib));
+      const __m512i idx = _mm512_inserti64x4(_mm512_castsi256_si512(lo), hi, 1);
+      const __m512h w = _mm512_sub_ph(_mm512_castsi512_ph(_mm512_permutexvar_epi16(idx, _mm512_castph_si512(lut))), vz);
+      const int kidx = kc * L->kb + kk;
+      for (int mm = 0; mm < m; ++mm)
+        acc[mm] = _mm512_fmadd_ph(_mm512_set1_ph(xh[(size_t)mm * L->k + kidx]), w, acc[mm]);
+    }
+    for (int mm = 0; mm < m; ++mm) c[mm] = _mm512_fmadd_ph(vs, acc[mm], c[mm]);
+  }
+}
+
+FP16_TARGET static int linear_fp16_small_m(const woq_layer* L, const uint16_t* x, int m, int fusion,
+                                           const uint16_t* other0, const uint16_t* other1, uint16_t* y,
+                                           int threads) {
+  const int k = L->k, n = L->n;
+  _Float16* xh = (_Float16*)malloc((size_t)m * k * sizeof(_Float16));
+  for (size_t i = 0; i < (size_t)m * k; ++i) xh[i] = (_Float16)bf16_to_f32(x[i]);
+  const int kb_per_group = L->group / L->kb > 0 ? L->group / L->kb : 1;
+  uint16_t* ytmp = NULL;
+  if (fusion == FUSE_SILU_MUL) ytmp = (uint16_t*)malloc((size_t)m * n * sizeof(uint16_t));
+  uint16_t* yo = ytmp ? ytmp : y;
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+#endif
+#pragma omp parallel for schedule(static)
+  for (int nc = 0; nc < L->nc; ++nc) {
+    __m512h c[4];
+    for (int mm = 0; mm < m; ++mm)
+      c[mm] = L->bias ? load32_f32_as_ph(L->bias + nc * NB) : _mm512_setzero_ph();
+    small_m_block_fp16(L, nc, xh, m, kb_per_group, c);
+    for (int mm = 0; mm < m; ++mm) {
+      _Float16 t[NB];
+      _mm512_storeu_ph(t, c[mm]);
+      for (int i = 0; i < NB; ++i) {
+        const int col = nc * NB + i;
+        if (col >= n) continue;
+        const size_t o = (size_t)mm * n + col;
+        float v = round_bf16((float)t[i]);
+        if (fusion != FUSE_SILU_MUL)
+          v = post_op(v, fusion, other0 ? bf16_to_f32(other0[o]) : 0.f, other1 ? bf16_to_f32(other1[o]) : 0.f);
+        yo[o] = f32_to_bf16_rne(v);
+      }
+    }
+  }
+  if (fusion == FUSE_SILU_MUL) {
+    const int half = n / 2;
+    for (int mm = 0; mm < m; ++mm)
+      for (int cc = 0; cc < half; ++cc) {
+        const float gate = bf16_to_f32(ytmp[(size_t)mm * n + cc]);
+        const float up = bf16_to_f32(ytmp[(size_t)mm * n + half + cc]);
+        y[(size_t)mm * half + cc] = f32_to_bf16_rne(up * silu_bf16(gate));
+      }
+    free(ytmp);
+  }
+  free(xh);
+  return 0;
+}
+#endif
+
+/* The reference's kernel for lowp BF16 and fewer than 5 tokens: INT4 weights, fp16 arithmetic.
+ * Returns -2 where the CPU lacks AVX512-FP16 (the caller then times the bf16 tile kernel). */
+EXPORT int woq_oracle_linear_fp16_small_m(const woq_layer* L, const uint16_t* x, int m, int fusion,
+                                          const uint16_t* other0, const uint16_t* other1, uint16_t* y,
+                                          int threads) {
+  if (L->is_int8 || m < 1 || m > 4) return -1;
+#ifdef WOQ_HAVE_FP16_KERNEL
+  if (woq_oracle_has_fp16_kernel()) return linear_fp16_small_m(L, x, m, fusion, other0, other1, y, threads);
+#endif
+  return -2;
 }
 
 /* Per-token symmetric activation quantisation; a row of zeros gets codes 0. */

@@ -29,6 +29,8 @@ def lib():
         L.woq_oracle_layer_free.argtypes = [vp]
         L.woq_oracle_linear_bf16.argtypes = [vp, vp, ci, ci, vp, vp, vp, ci]
         L.woq_oracle_linear_int8.argtypes = [vp, vp, ci, ci, vp, vp, vp, vp, ci]
+        L.woq_oracle_linear_fp16_small_m.argtypes = [vp, vp, ci, ci, vp, vp, vp, ci]
+        L.woq_oracle_has_fp16_kernel.restype = ci
         L.woq_oracle_quant_act_sym.argtypes = [vp, ci, ci, vp, vp]
         L.woq_oracle_max_threads.restype = ci
         _lib = L
@@ -75,6 +77,21 @@ class Layer:
                                      _p(o[1]) if len(o) > 1 else None, _p(y), threads)
         return _from_bits(y)
 
+    def linear_fp16_small_m(self, x, fusion=0, others=(), threads=0):
+        """The reference's fp16 small-M microkernel (1..4 tokens, INT4 weights); None where the
+        CPU has no AVX512-FP16."""
+        xb = _bf16_bits(x)
+        m = xb.shape[0]
+        n_out = self.n // 2 if fusion == 0x100 else self.n
+        y = np.empty((m, n_out), dtype=np.uint16)
+        o = [_bf16_bits(t) for t in others]
+        rc = lib().woq_oracle_linear_fp16_small_m(self._h, _p(xb), m, fusion, _p(o[0]) if o else None,
+                                                  _p(o[1]) if len(o) > 1 else None, _p(y), threads)
+        if rc == -2:
+            return None
+        assert rc == 0, rc
+        return _from_bits(y)
+
     def linear_int8(self, x, fusion=0, others=(), threads=0, want_acc=False):
         xb = _bf16_bits(x)
         m = xb.shape[0]
@@ -99,3 +116,7 @@ def quant_act_sym(x):
 
 def max_threads():
     return lib().woq_oracle_max_threads()
+
+
+def has_fp16_kernel():
+    return bool(lib().woq_oracle_has_fp16_kernel())

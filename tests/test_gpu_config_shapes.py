@@ -1,0 +1,215 @@
+"""Parity at the sizes the benchmark configurations name, against the CPU oracle.
+
+The layers are too large for the numpy oracle to finish in seconds, so the layer is quantised
+on the GPU (by the torch quantiser that tests/test_quantizer_torch.py pins bit for bit to the
+reference's), the GPU computes the whole output, and the oracle computes a spread subset of the
+output columns from the same packed weights (output columns are independent of each other).
+Bars as everywhere: max-abs <= 1e-2 * ||y_ref||_inf, mean relative error <= 2e-3.
+
+  config 5  Llama-3-70B linears, INT4 g128: QKV 10240x8192, o_proj 8192x8192 (+residual),
+            gate_up 57344x8192 (silu*mul), down_proj 8192x28672 (+residual); M in {1, 16, 128}
+  config 3  Llama-3-8B QKV 6144x4096 INT4 g128; M in {1, 8, 32, 1024}
+  config 2  Llama-3-8B gate_up 28672x4096 INT8 weights / INT8 compute (silu*mul); M = 512
+  config 4  Mixtral expert shapes (w13 28672x4096 silu*mul, w2 4096x14336 scaled add), 8 experts,
+            top-2; T in {16, 256} on every token, T = 4096 on a subset of the tokens
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import woq_oracle as O
+from tests.helpers import bf16_numpy, bf16_tensor, make_acts
+
+pytestmark = pytest.mark.gpu
+G = 128
+
+
+@pytest.fixture(scope="module")
+def env():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import ipex_b200
+
+    ipex_b200._capi.lib()
+    return ipex_b200
+
+
+def spread_rows(n, count=448):
+    """`count` rows spread over [0, n) plus the last 64 (tail tiles)."""
+    step = max(1, n // count)
+    rows = np.unique(np.concatenate([np.arange(0, n, step)[:count], np.arange(max(0, n - 64), n)]))
+    return rows
+
+
+def int4_layer(env, n, k, seed, flags=0):
+    """Quantised on the GPU; returns the context and host copies of (q, s16, zp)."""
+    capi, quant = env._capi, env.quantization
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn((n, k), device="cuda", generator=g) * 0.02
+    qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, G)
+    del w
+    s16 = s.half()
+    ctx = capi.WoqContext(qw, s16, z, None, n, k, capi.DTYPE_INT4, G, capi.LOWP_BF16, layout_flags=flags)
+    return ctx, (qw.cpu().numpy(), s16.cpu().numpy(), z.cpu().numpy())
+
+
+def check(y, y_ref, what=""):
+    mx, mr = O.parity_metrics(y, y_ref)
+    assert mx <= O.MAX_ABS_TOL, f"{what}: max-abs/inf-norm {mx:.3e}"
+    assert mr <= O.MEAN_REL_TOL, f"{what}: mean rel {mr:.3e}"
+    return mx, mr
+
+
+CONFIG5 = [("qkv", 10240, 8192, "none"), ("o_proj", 8192, 8192, "add"),
+           ("gate_up", 57344, 8192, "silu_mul"), ("down_proj", 8192, 28672, "add")]
+
+
+@pytest.mark.parametrize("name,n,k,fusion", CONFIG5)
+def test_config5_llama70b_linears(env, name, n, k, fusion):
+    capi = env._capi
+    ctx, (qw, s16, z) = int4_layer(env, n, k, seed=5000 + n % 977 + k % 13,
+                                   flags=capi.LAYOUT_GATE_UP if fusion == "silu_mul" else 0)
+    for m in (1, 16, 128):
+        x = make_acts(m, k, seed=50 + m)
+        xg = bf16_tensor(x, "cuda")
+        if fusion == "silu_mul":
+            half = n // 2
+            rows = spread_rows(half)
+            y = bf16_numpy(ctx.linear(xg, capi.FUSE_SILU_MUL))[:, rows]
+            both = np.concatenate([rows, rows + half])
+            ref = O.woq_linear_bf16(x, qw[both], s16[both], z[both], None, O.WOQ_DTYPE_INT4, G, O.FUSE_SILU_MUL)
+        elif fusion == "add":
+            rows = spread_rows(n)
+            r = make_acts(m, n, seed=60 + m)
+            y = bf16_numpy(ctx.linear(xg, capi.FUSE_ADD, [bf16_tensor(r, "cuda")]))[:, rows]
+            ref = O.woq_linear_bf16(x, qw[rows], s16[rows], z[rows], None, O.WOQ_DTYPE_INT4, G, O.FUSE_ADD,
+                                    [r[:, rows]])
+        else:
+            rows = spread_rows(n)
+            y = bf16_numpy(ctx.linear(xg))[:, rows]
+            ref = O.woq_linear_bf16(x, qw[rows], s16[rows], z[rows], None, O.WOQ_DTYPE_INT4, G)
+        ctx.workspace(m).status()
+        check(y, ref, f"{name} M={m}")
+    # the weights the kernels multiply by, on the same rows, bit for bit
+    rows = spread_rows(n)
+    w = bf16_numpy(ctx.dump_dequant()[torch.from_numpy(rows).cuda()])
+    w_ref = O.dequantize_weight(qw[rows], s16[rows], z[rows], O.WOQ_DTYPE_INT4, k, G)
+    np.testing.assert_array_equal(w.view(np.uint32), w_ref.view(np.uint32))
+
+
+def test_config3_qkv_full_size(env):
+    n, k = 6144, 4096
+    ctx, (qw, s16, z) = int4_layer(env, n, k, seed=3000)
+    rows = spread_rows(n, 1024)
+    for m in (1, 8, 32, 1024):
+        x = make_acts(m, k, seed=30 + m)
+        y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda")))[:, rows]
+        ctx.workspace(m).status()
+        check(y, O.woq_linear_bf16(x, qw[rows], s16[rows], z[rows], None, O.WOQ_DTYPE_INT4, G), f"qkv M={m}")
+
+
+def test_config2_gate_up_int8_512_tokens(env):
+    capi, quant = env._capi, env.quantization
+    n, k, m = 28672, 4096, 512
+    g = torch.Generator(device="cuda").manual_seed(2002)
+    w = torch.randn((n, k), device="cuda", generator=g) * 0.02
+    qw, s, _ = quant.quantize_per_channel(w, quant.WoqWeightDtype.INT8, sym_quant=True)
+    del w
+    ctx = capi.WoqContext(qw, s, None, None, n, k, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
+                          act_quant_mode=capi.ACT_PER_M_SYM, layout_flags=capi.LAYOUT_GATE_UP)
+    x = make_acts(m, k, seed=2002 + m)
+    half = n // 2
+    rows = spread_rows(half)
+    both = np.concatenate([rows, rows + half])
+    y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda"), capi.FUSE_SILU_MUL))[:, rows]
+    ctx.workspace(m).status()
+    qh, sh = qw.cpu().numpy(), s.cpu().numpy().reshape(-1)
+    check(y, O.woq_linear_int8(x, qh[both], sh[both], None, O.FUSE_SILU_MUL), "int8 gate_up M=512")
+
+
+# ---- config 4: Mixtral expert shapes ----------------------------------------------------------
+HID, FFN, E = 4096, 14336, 8
+
+
+@pytest.fixture(scope="module")
+def experts(env):
+    capi, quant = env._capi, env.quantization
+    out = []
+    for e in range(E):
+        g = torch.Generator(device="cuda").manual_seed(4400 + e)
+        w13 = torch.randn((2 * FFN, HID), device="cuda", generator=g) * 0.02
+        q13 = quant.quantize_per_block(w13, quant.WoqWeightDtype.INT4, G)
+        del w13
+        w2 = torch.randn((HID, FFN), device="cuda", generator=g) * 0.02
+        q2 = quant.quantize_per_block(w2, quant.WoqWeightDtype.INT4, G)
+        del w2
+        host = {"w13": (q13[0].cpu().numpy(), q13[1].half().cpu().numpy(), q13[2].cpu().numpy()),
+                "w2": (q2[0].cpu().numpy(), q2[1].half().cpu().numpy(), q2[2].cpu().numpy()),
+                "w13_dequantised": None}  # filled by the oracle on first use, shared by the three token counts
+        out.append((q13, q2, host))
+    return out
+
+
+def moe_contexts(capi, experts, many_tokens):
+    """The expert linears switch tiling with the token count, like the benchmark's."""
+    tiling = capi.LAYOUT_TC_ONLY if many_tokens else capi.LAYOUT_STREAM_ONLY
+    ctxs = []
+    for q13, q2, _ in experts:
+        c13 = capi.WoqContext(q13[0], q13[1].half(), q13[2], None, 2 * FFN, HID, capi.DTYPE_INT4, G,
+                              capi.LOWP_BF16, layout_flags=capi.LAYOUT_GATE_UP | tiling)
+        c2 = capi.WoqContext(q2[0], q2[1].half(), q2[2], None, HID, FFN, capi.DTYPE_INT4, G, capi.LOWP_BF16,
+                             layout_flags=tiling)
+        ctxs.append((c13, c2))
+    return ctxs
+
+
+def moe_reference(h, idx, w, experts, tokens, cols):
+    """The reference loop (decoder.py:919-962 + MoEKrnl.cpp:67-120) restricted to `tokens` and to
+    output columns `cols`: out = bf16(out + y * w) expert by expert in index order."""
+    ref = np.zeros((len(tokens), len(cols)), dtype=np.float32)
+    for e in range(E):
+        sel = [(i, t, int(np.nonzero(idx[t] == e)[0][0])) for i, t in enumerate(tokens) if e in idx[t]]
+        if not sel:
+            continue
+        host = experts[e][2]
+        xs = h[[t for _, t, _ in sel]]
+        if host["w13_dequantised"] is None:
+            q, s, z = host["w13"]
+            host["w13_dequantised"] = O.dequantize_weight(q, s, z, O.WOQ_DTYPE_INT4, HID, G)
+        a = O.linear_from_dequantised(xs, host["w13_dequantised"], None, O.FUSE_SILU_MUL)
+        q, s, z = host["w2"]
+        y = O.woq_linear_bf16(a, q[cols], s[cols], z[cols], None, O.WOQ_DTYPE_INT4, G)
+        for r, (i, t, j) in enumerate(sel):
+            ref[i] = O.rne_bf16(ref[i] + y[r] * w[t, j])
+    return ref
+
+
+@pytest.mark.parametrize("tokens", [16, 256, 4096])
+def test_config4_mixtral_layer_full_expert_shapes(env, experts, tokens):
+    capi = env._capi
+    rng = np.random.default_rng(4000 + tokens)
+    h = make_acts(tokens, HID, seed=4000 + tokens)
+    router = O.rne_bf16((rng.standard_normal((E, HID)) * 0.02).astype(np.float32))
+    idx, w = O.moe_route_top2(h, router)
+    per_expert = max(int((idx == e).sum()) for e in range(E))
+    ctxs = moe_contexts(capi, experts, many_tokens=per_expert > 16)
+    hg = bf16_tensor(h, "cuda")
+    out = torch.zeros((tokens, HID), dtype=torch.bfloat16, device="cuda")
+    wss = []
+    for e, (c13, c2) in enumerate(ctxs):
+        t_sel, j_sel = np.nonzero(idx == e)
+        if t_sel.size == 0:
+            continue
+        ti = torch.from_numpy(t_sel.astype(np.int32)).cuda()
+        tw = bf16_tensor(w[t_sel, j_sel], "cuda")
+        wss.append(capi.moe_expert(c13, c2, hg, ti, tw, out))
+    for ws in wss:
+        ws.status()
+    check_tokens = np.arange(tokens) if tokens <= 16 else np.unique(
+        np.concatenate([np.arange(0, tokens, max(1, tokens // 24))[:24], [tokens - 1]]))
+    cols = spread_rows(HID, 192)
+    ref = moe_reference(h, idx, w, experts, list(check_tokens), cols)
+    y = bf16_numpy(out)[np.ix_(check_tokens, cols)]
+    mx, mr = O.parity_metrics(y, ref)
+    print(f"moe T={tokens}: max-abs/inf {mx:.3e} mean-rel {mr:.3e}")
+    assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)

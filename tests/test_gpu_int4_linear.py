@@ -233,3 +233,38 @@ def test_errors_are_reported_not_thrown_from_kernels(capi):
     qw, s, _, _ = to_device_layer(layer, "cuda")
     with pytest.raises(capi.WoqError):
         capi.WoqContext(qw, s, zbad, None, 64, 128, capi.DTYPE_INT4, 64, capi.LOWP_BF16)
+
+
+def test_strided_output_takes_operands_with_the_same_row_stride(capi):
+    """y rows and the rows of the fused operands share one stride (ldy).  A column slice of a
+    wider buffer as output works with a residual sliced the same way; a dense residual beside a
+    strided output is refused by the ctypes layer instead of being read with the wrong stride."""
+    n, k, m = 320, 512, 6
+    layer = make_int4_layer(n, k, 128, seed=91, std=0.05)
+    ctx = make_ctx(capi, layer)
+    x = make_acts(m, k, seed=92)
+    r = make_acts(m, n, seed=93)
+    wide_out = torch.zeros((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+    wide_res = torch.zeros((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+    wide_res[:, n:] = bf16_tensor(r, "cuda")
+    ctx.linear(bf16_tensor(x, "cuda"), capi.FUSE_ADD, [wide_res[:, n:]], out=wide_out[:, n:])
+    assert_parity(bf16_numpy(wide_out[:, n:]), oracle_y(layer, x, O.FUSE_ADD, [r]))
+    assert not wide_out[:, :n].any()
+    with pytest.raises(ValueError, match="row stride"):
+        ctx.linear(bf16_tensor(x, "cuda"), capi.FUSE_ADD, [bf16_tensor(r, "cuda")], out=wide_out[:, n:])
+
+
+def test_deferred_zero_point_check_reports_at_first_use(capi):
+    layer = make_int4_layer(64, 128, 64, seed=1)
+    qw, s, _, _ = to_device_layer(layer, "cuda")
+    zbad = torch.full((64, 2), 3.5, device="cuda")
+    ctx = capi.WoqContext(qw, s, zbad, None, 64, 128, capi.DTYPE_INT4, 64, capi.LOWP_BF16,
+                          layout_flags=capi.LAYOUT_DEFER_CHECK)
+    x = torch.zeros((2, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(capi.WoqError) as e:
+        ctx.linear(x)
+    assert e.value.code == 1 and "zero points" in str(e.value)
+    good = capi.WoqContext(*to_device_layer(layer, "cuda")[:3], None, 64, 128, capi.DTYPE_INT4, 64,
+                           capi.LOWP_BF16, layout_flags=capi.LAYOUT_DEFER_CHECK)
+    y = bf16_numpy(good.linear(bf16_tensor(make_acts(2, 128, seed=3), "cuda")))
+    assert_parity(y, oracle_y(layer, make_acts(2, 128, seed=3)))

@@ -329,3 +329,71 @@ def test_row_parallel_shards_sum_to_the_full_layer(ipex):
     y_ref = O.row_parallel_linear(x, shards, [s.astype(np.float16)[:, r * 4:(r + 1) * 4] for r in range(p)],
                                   [z[:, r * 4:(r + 1) * 4] for r in range(p)], None, O.WOQ_DTYPE_INT4, g)
     parity(y, y_ref)
+
+
+def test_compute_dtypes_that_are_not_built_are_refused_not_narrowed(ipex):
+    """The reference routes lowp NONE by the activation dtype and has an fp16 kernel for lowp
+    FP16 (csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:75-106).  Only the bf16 route exists here; the
+    others must fail with a clear message instead of running in bf16."""
+    q = ipex.quantization
+    mods = ipex.nn.modules
+    lin = make_linear(128, 256, False, seed=21)
+    # lowp NONE with bf16 activations IS the reference's bf16 kernel: it runs
+    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
+        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.NONE, group_size=128).global_qconfig
+    mod = mods.WeightOnlyQuantizedLinear.from_float(copy.deepcopy(lin))  # from_float empties its input
+    xb = torch.randn(4, 256, device="cuda").bfloat16()
+    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
+        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.BF16, group_size=128).global_qconfig
+    assert torch.equal(mod(xb), mods.WeightOnlyQuantizedLinear.from_float(copy.deepcopy(lin))(xb))
+    # ... with fp32 or fp16 activations it would be an fp32 / fp16 kernel: refused
+    with pytest.raises(RuntimeError, match="lowp_mode NONE"):
+        mod(xb.float())
+    with pytest.raises(RuntimeError, match="lowp_mode NONE"):
+        mod(xb.half())
+    # lowp FP16: refused when the context is made
+    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
+        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.FP16, group_size=128).global_qconfig
+    with pytest.raises(RuntimeError, match="FP16"):
+        mods.WeightOnlyQuantizedLinear.from_float(copy.deepcopy(lin))
+
+
+def test_pickle_state_is_the_reference_twelve_tuple_and_load_from_ctx(ipex):
+    q = ipex.quantization
+    lin = make_linear(256, 512, True, seed=31)
+    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
+        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.BF16, group_size=128).global_qconfig
+    mod = ipex.nn.modules.WeightOnlyQuantizedLinear.from_float(lin)
+    state = mod._op_context.__getstate__()
+    if len(state) != 12 and isinstance(state[0], tuple):  # some torch versions wrap the C++ state
+        state = state[0]
+    assert len(state) == 12, [type(v) for v in state]  # csrc/cpu/jit/cpu/kernels/OpContext.h:363-375
+    other = make_linear(256, 512, True, seed=32)
+    other.qconfig = lin.qconfig
+    mod2 = ipex.nn.modules.WeightOnlyQuantizedLinear.from_float(other)
+    x = torch.randn(5, 512, device="cuda").bfloat16()
+    assert not torch.equal(mod(x), mod2(x))
+    mod2._op_context.load_from_ctx(mod._op_context)
+    assert torch.equal(mod(x), mod2(x))
+    assert torch.equal(mod2._op_context.get_weight(), mod._op_context.get_weight())
+
+
+def test_second_tiling_is_packed_on_first_large_batch(ipex):
+    """A context made through the ops keeps the streaming tiling; the tensor-core tiling appears
+    with the first call of more than 16 tokens and gives the same numbers as a context that had
+    it from the start (through the C ABI)."""
+    q = ipex.quantization
+    capi = ipex._capi
+    lin = make_linear(384, 1024, False, seed=41)
+    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
+        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.BF16, group_size=128).global_qconfig
+    w = lin.weight.detach().float().cuda()
+    mod = ipex.nn.modules.WeightOnlyQuantizedLinear.from_float(lin)
+    qw, s, z = q.quantize_per_block(w, q.WoqWeightDtype.INT4, 128)
+    both = capi.WoqContext(qw, s, z, None, 384, 1024, capi.DTYPE_INT4, 128, capi.LOWP_BF16)
+    small = torch.randn(8, 1024, device="cuda").bfloat16()
+    large = torch.randn(200, 1024, device="cuda").bfloat16()
+    assert torch.equal(mod(small), both.linear(small))
+    assert torch.equal(mod(large), both.linear(large))
+    assert torch.equal(mod(small), both.linear(small))
+    torch.ops.torch_ipex.woq_check_status()

@@ -28,11 +28,23 @@ def capi():
     return _capi
 
 
-def test_two_calls_in_a_row_match_the_regular_entry_point(capi):
-    n, k, g = 1536, 4096, 128          # K is split across CTAs: partial tiles and counters are used
+@pytest.mark.parametrize("split", ["stream_k", "auto"])
+def test_two_calls_in_a_row_match_the_regular_entry_point(capi, split):
+    """With the stream-K split forced, K is shared between thread blocks through the scratch
+    (partial tiles and arrival counters live in the built-in array); with the library's own
+    choice this layer reduces inside thread-block clusters and only the status word is used."""
+    n, k, g = 1536, 4096, 128
     layer = make_int4_layer(n, k, g, seed=4242, bias=True)
     qw, s, z, b = to_device_layer(layer, "cuda")
     ctx = capi.WoqContext(qw, s, z, b, n, k, capi.DTYPE_INT4, g, capi.LOWP_BF16)
+    capi.set_option(capi.OPT_DECODE_SPLIT, capi.SPLIT_STREAM_K if split == "stream_k" else capi.SPLIT_AUTO)
+    try:
+        _two_calls(capi, ctx, layer, n, k, g)
+    finally:
+        capi.set_option(capi.OPT_DECODE_SPLIT, capi.SPLIT_AUTO)
+
+
+def _two_calls(capi, ctx, layer, n, k, g):
 
     # call 1: plain linear, 3 tokens
     x1 = make_acts(3, k, seed=1)
@@ -56,6 +68,19 @@ def test_two_calls_in_a_row_match_the_regular_entry_point(capi):
                                O.WOQ_DTYPE_INT4, g, O.FUSE_ADD, [r2])
     mx, mr = O.parity_metrics(bf16_numpy(y_static2), y_ref2)
     assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)
+    capi.static_scratch_status()       # no kernel gave up a wait
+
+    # call 3: everything pre-allocated by the caller -> the library allocates nothing
+    xg, rg = bf16_tensor(x2, "cuda"), bf16_tensor(r2, "cuda")
+    out = torch.empty((16, n), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    allocated_before = torch.cuda.memory_allocated()
+    ctx.linear_static_scratch(xg, capi.FUSE_ADD, [rg], out=out)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_allocated() == allocated_before
+    assert torch.equal(out, y_regular2)
 
 
 def test_sizes_beyond_the_built_in_scratch_are_refused(capi):
