@@ -394,9 +394,11 @@ def run_ours(args):
     ws = capi.Workspace(layers[0]["qkv"].workspace_bytes(m), device)
 
     bf = dict(dtype=torch.bfloat16, device=device)
-    hidden = torch.randn((m, HIDDEN), **bf)
-    resid = torch.randn((m, HIDDEN), **bf)
-    attn_in = torch.randn((m, HIDDEN), **bf)            # what attention would hand to o_proj
+    # activations are replicated under tensor parallelism: the same seed on every rank
+    gen = torch.Generator(device=device).manual_seed(20240607)
+    hidden = torch.randn((m, HIDDEN), generator=gen, **bf)
+    resid = torch.randn((m, HIDDEN), generator=gen, **bf)
+    attn_in = torch.randn((m, HIDDEN), generator=gen, **bf)            # what attention would hand to o_proj
     qkv_local = torch.empty((m, QKV_N // p), **bf)
     qkv_full = torch.empty((p, m, QKV_N // p), **bf) if p > 1 else None
     act_local = torch.empty((m, FFN // p), **bf)

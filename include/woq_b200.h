@@ -234,13 +234,28 @@ int woq_b200_linear_allreduce(const woq_b200_ctx* ctx, const woq_b200_comm* comm
 
 /* Column-parallel linear fused with the all-gather: this rank's N shard; the gathered
  * [M, world * N_out_local] bf16 tensor appears at byte `gather_offset` of every rank's
- * gather area (rank r's columns at r * N_out_local) and is complete there when the kernel has
- * finished.  A gather destination may be written again only after a later exchange on the
- * same comm has completed on this rank. */
+ * gather area (rank r's columns at r * N_out_local).  This rank's own column block is there
+ * when the kernel has finished; the other ranks' blocks arrive over NVLink without anybody
+ * waiting for them and are put in place by the NEXT fused call on the same comm (while its
+ * weights stream) or by woq_b200_comm_fence: the whole tensor is complete when that call has
+ * finished.  A consumer that only reads its own block (a row-parallel layer behind a
+ * column-parallel one, as in the reference's tensor-parallel chain,
+ * intel_extension_for_pytorch/nn/modules/weight_only_quantization.py:536-633) never waits.
+ * A gather destination may be written again only after a later exchange on the same comm has
+ * completed on this rank.  A sequence of fused calls captured in a CUDA graph must begin and
+ * end with no gather outstanding (call woq_b200_comm_fence before the capture, and let a
+ * reduce or a fence be the last captured call). */
 int woq_b200_linear_allgather(const woq_b200_ctx* ctx, const woq_b200_comm* comm, const void* x,
                               int64_t m, int64_t ldx, int32_t fusion, const void* const* others,
                               int32_t n_others, size_t gather_offset, void* workspace,
                               size_t workspace_bytes, void* stream);
+
+/* Completes an outstanding all-gather on this rank without running a linear (a small kernel
+ * on `stream` that waits, bounded, for the other ranks' column blocks and puts them in place).
+ * No-op when nothing is outstanding.  woq_b200_comm_status then reports, after synchronising the
+ * stream, whether that kernel gave up waiting (WOQ_B200_ERR_DEVICE_WAIT). */
+int woq_b200_comm_fence(woq_b200_comm* comm, void* stream);
+int woq_b200_comm_status(woq_b200_comm* comm, void* stream);
 
 /* No counterpart in the reference.  Same computation as woq_b200_linear for at most 16 tokens,
  * for callers that may not allocate device memory (memory-planned graphs, servers that forbid

@@ -774,6 +774,9 @@ struct woq_b200_comm {
   uint8_t* local;       // this rank's buffer (cudaMalloc)
   uint8_t* peer[woq::kCommMaxRanks];
   bool connected;
+  int num_sms;
+  int* status;          // status word of the fence kernel (inside `local`)
+  woq::CommPending pending;  // the all-gather of the latest launch, if it was one
 };
 
 static int check_comm(const woq_b200_comm* cm) {
@@ -793,14 +796,16 @@ int woq_b200_comm_create(int32_t rank, int32_t world, int64_t max_n, size_t gath
   cm->rank = rank;
   cm->world = world;
   cm->ar_n = (max_n + woq::kTileN - 1) / woq::kTileN * woq::kTileN;
-  // {2 x bf16, stamp} words: [2 parities][8 sources][ar_n / 64 tiles][16 tokens][32 lanes] x 8 B
-  const size_t ar_bytes = static_cast<size_t>(cm->ar_n) * 1024;
+  // {2 x bf16, stamp} words: [4 sets][8 sources][ar_n / 64 tiles][16 tokens][32 lanes] x 8 B
+  const size_t ar_bytes = static_cast<size_t>(cm->ar_n) * 512 * woq::kCommSets;
   cm->gather_off = (woq::kCommCtlBytes + ar_bytes + 255) / 256 * 256;
   cm->gather_bytes = (gather_bytes + 255) / 256 * 256;
   cm->total_bytes = cm->gather_off + cm->gather_bytes;
   cm->connected = false;
   for (auto& q : cm->peer) q = nullptr;
+  cm->pending = woq::CommPending{};
   cudaError_t e = cudaGetDevice(&cm->device);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&cm->num_sms, cudaDevAttrMultiProcessorCount, cm->device);
   if (e == cudaSuccess) e = cudaMalloc(&cm->local, cm->total_bytes);
   if (e == cudaSuccess) e = cudaMemset(cm->local, 0, cm->total_bytes);
   if (e != cudaSuccess) {
@@ -808,6 +813,7 @@ int woq_b200_comm_create(int32_t rank, int32_t world, int64_t max_n, size_t gath
     return fail(WOQ_B200_ERR_CUDA, "comm buffer: %s", cudaGetErrorString(e));
   }
   cm->peer[rank] = cm->local;
+  cm->status = reinterpret_cast<int*>(cm->local + 2048);  // inside the control block, never a control word
   cm->magic = kMagic + 1;
   *out = cm;
   return WOQ_B200_OK;
@@ -864,6 +870,7 @@ static int comm_params(const woq_b200_ctx* c, const woq_b200_comm* cm, int64_t m
   cp->world = cm->world;
   cp->rank = cm->rank;
   cp->ar_n = cm->ar_n;
+  cp->pend = cm->pending;  // this launch receives it; the caller records its own afterwards
   return WOQ_B200_OK;
 }
 
@@ -885,9 +892,11 @@ int woq_b200_linear_allreduce(const woq_b200_ctx* c, const woq_b200_comm* cm, co
   if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
     return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
   if (ldy < c->desc.n) return fail(WOQ_B200_ERR_INVALID_ARG, "ldy smaller than the output width");
-  return run_decode(c, x, m, ldx, fusion, need > 0 ? others[0] : nullptr, need > 1 ? others[1] : nullptr,
-                    nullptr, nullptr, y, ldy, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_),
-                    &cp, bias);
+  const int rc = run_decode(c, x, m, ldx, fusion, need > 0 ? others[0] : nullptr, need > 1 ? others[1] : nullptr,
+                            nullptr, nullptr, y, ldy, workspace, workspace_bytes, static_cast<cudaStream_t>(stream_),
+                            &cp, bias);
+  if (rc == WOQ_B200_OK) const_cast<woq_b200_comm*>(cm)->pending = woq::CommPending{};  // received by this launch
+  return rc;
 }
 
 int woq_b200_linear_allgather(const woq_b200_ctx* c, const woq_b200_comm* cm, const void* x, int64_t m,
@@ -915,9 +924,53 @@ int woq_b200_linear_allgather(const woq_b200_ctx* c, const woq_b200_comm* cm, co
   // y = this rank's column block of the gathered tensor; `others` are local [M, N_out] tensors
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(cm->local + cm->gather_off + gather_offset) +
                      static_cast<int64_t>(cm->rank) * n_out;
-  return run_decode(c, x, m, ldx, fusion, need > 0 ? others[0] : nullptr, need > 1 ? others[1] : nullptr,
-                    nullptr, nullptr, y, n_out * cm->world, workspace, workspace_bytes,
-                    static_cast<cudaStream_t>(stream_), &cp, nullptr, n_out);
+  const int rc = run_decode(c, x, m, ldx, fusion, need > 0 ? others[0] : nullptr, need > 1 ? others[1] : nullptr,
+                            nullptr, nullptr, y, n_out * cm->world, workspace, workspace_bytes,
+                            static_cast<cudaStream_t>(stream_), &cp, nullptr, n_out);
+  if (rc == WOQ_B200_OK) {
+    // the other ranks' column blocks are received by the next launch on this comm
+    woq::CommPending g{};
+    g.dst = reinterpret_cast<__nv_bfloat16*>(cm->local + cm->gather_off + gather_offset);
+    g.m = static_cast<int>(m);
+    g.n = static_cast<int>(c->desc.n);
+    g.n_out = static_cast<int>(n_out);
+    g.tiles = c->tiles;
+    g.gate_up = c->gate_up;
+    g.pair = fusion != WOQ_B200_FUSE_SILU_MUL;
+    const_cast<woq_b200_comm*>(cm)->pending = cm->world > 1 ? g : woq::CommPending{};
+  }
+  return rc;
+}
+
+int woq_b200_comm_fence(woq_b200_comm* cm, void* stream_) {
+  if (int rc = check_comm(cm)) return rc;
+  if (!cm->pending.dst || cm->world == 1) {
+    cm->pending = woq::CommPending{};
+    return WOQ_B200_OK;
+  }
+  woq::CommParams cp{};
+  for (int q = 0; q < woq::kCommMaxRanks; ++q) cp.peer[q] = cm->peer[q];
+  cp.world = cm->world;
+  cp.rank = cm->rank;
+  cp.ar_n = cm->ar_n;
+  cp.pend = cm->pending;
+  CUDA_TRY(woq::launch_comm_fence(cp, cm->status, cm->num_sms, static_cast<cudaStream_t>(stream_)));
+  woq::count_launch();
+  cm->pending = woq::CommPending{};
+  return WOQ_B200_OK;
+}
+
+int woq_b200_comm_status(woq_b200_comm* cm, void* stream_) {
+  if (int rc = check_comm(cm)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int h = 0;
+  CUDA_TRY(cudaMemcpyAsync(&h, cm->status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  if (h != 0) {
+    CUDA_TRY(cudaMemsetAsync(cm->status, 0, sizeof(int), stream));
+    return fail(WOQ_B200_ERR_DEVICE_WAIT, "woq_b200_comm_fence gave up waiting for a peer (code %d)", h);
+  }
+  return WOQ_B200_OK;
 }
 
 int woq_b200_linear_scatter(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx,

@@ -121,7 +121,7 @@ __device__ __forceinline__ void st_cluster_f32(float* local, uint32_t rank, floa
 __device__ __forceinline__ uint32_t* comm_ctl(uint8_t* base) { return reinterpret_cast<uint32_t*>(base); }
 // Exchange slots carry their own arrival mark: every 8-byte word is {two bf16 values, stamp},
 // written with one store, so data and mark arrive together and no fence is needed.
-// [epoch parity][source rank][tile][token][lane] words.
+// [epoch & 3][source rank][tile][token][lane] words.
 __device__ __forceinline__ uint2* comm_ar_word(const CommParams& c, uint8_t* base, int parity, int src,
                                                int tile, int tok, int lane) {
   const size_t tiles = static_cast<size_t>(c.ar_n / kTileN);
@@ -156,20 +156,6 @@ __device__ __forceinline__ uint32_t comm_wait_word(const uint2* w, uint32_t stam
       }
     }
   }
-}
-
-// The words of tokens h .. h+7 from source rank r: one load each, all in flight together,
-// then the bounded wait only for those that had not arrived.
-template <typename WordAt>
-__device__ __forceinline__ void comm_wait_words8(WordAt word_at, int h, int m, uint32_t stamp, int* status,
-                                                 uint32_t* data) {
-  uint2 v[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    if (h + i < m) v[i] = ld_relaxed_sys_v2(word_at(h + i));
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-    if (h + i < m) data[i] = v[i].y == stamp ? v[i].x : comm_wait_word(word_at(h + i), stamp, status);
 }
 
 // Timeline probe, compiled in only with -DWOQ_B200_TIMELINE (a measuring build, never the
@@ -217,7 +203,7 @@ __device__ __noinline__ void decode_tile_epilogue(const EpiParams& p, int tl, in
     // bits; bias and post-op follow the reduction.
     const CommParams& c = p.comm;
     const uint32_t stamp = epoch + 1;
-    const int parity = epoch & 1;
+    const int parity = epoch & (kCommSets - 1);
     uint32_t mine[NTOK];
 #pragma unroll
     for (int tok = 0; tok < NTOK; ++tok)
@@ -229,30 +215,40 @@ __device__ __noinline__ void decode_tile_epilogue(const EpiParams& p, int tl, in
             st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
                               make_uint2(mine[tok], stamp));
       }
+    // Two tokens at a time: the words of every source rank are requested together (one round
+    // trip to the local L2 for all of them, not one per rank), then added in rank order; only a
+    // word that had not arrived yet is polled for.
 #pragma unroll
-    for (int h = 0; h < NTOK; h += 8) {
+    for (int h = 0; h < NTOK; h += 2) {
       if (h >= p.m) continue;
-      float s0[8], s1[8];
+      uint2 v[kCommMaxRanks][2];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s0[i] = s1[i] = 0.f;
-      for (int r = 0; r < c.world; ++r) {
-        uint32_t w[8];
-        if (r == c.rank) {
+      for (int r = 0; r < kCommMaxRanks; ++r)
+        if (r < c.world && r != c.rank) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = mine[h + i];
-        } else {
-          comm_wait_words8([&](int tok) { return comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane); }, h,
-                           p.m, stamp, p.status, w);
+          for (int i = 0; i < 2; ++i)
+            if (h + i < p.m) v[r][i] = ld_relaxed_sys_v2(comm_ar_word(c, c.peer[c.rank], parity, r, tl, h + i, lane));
+        }
+      float s0[2] = {0.f, 0.f}, s1[2] = {0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kCommMaxRanks; ++r)
+        if (r < c.world) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            if (h + i < p.m) {
+              uint32_t w;
+              if (r == c.rank)
+                w = mine[h + i];
+              else if (v[r][i].y == stamp)
+                w = v[r][i].x;
+              else
+                w = comm_wait_word(comm_ar_word(c, c.peer[c.rank], parity, r, tl, h + i, lane), stamp, p.status);
+              s0[i] += __uint_as_float(w << 16);
+              s1[i] += __uint_as_float(w & 0xffff0000u);
+            }
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (h + i < p.m) {
-            s0[i] += __uint_as_float(w[i] << 16);
-            s1[i] += __uint_as_float(w[i] & 0xffff0000u);
-          }
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
+      for (int i = 0; i < 2; ++i)
         if (h + i < p.m) {
           a0[h + i] = bf16_round(s0[i]);
           a1[h + i] = bf16_round(s1[i]);
@@ -392,12 +388,12 @@ __device__ __noinline__ void decode_tile_epilogue(const EpiParams& p, int tl, in
   }
   if (COMM && p.comm.mode == kCommAllGather) {
     // Column-parallel linear: p.y is this rank's column block of the gathered tensor.  The
-    // tile also goes to every other rank, and the same tile of every other rank is copied
-    // from this rank's slots into its column block here, so that the gathered tensor is
-    // written by local stores only and is complete when this kernel ends.
+    // tile also goes to every other rank's slots; nobody waits here.  The other ranks' tiles
+    // are copied into this rank's gathered tensor by the next launch on the comm
+    // (comm_receive_pending), off the critical path of this one.
     const CommParams& c = p.comm;
     const uint32_t stamp = epoch + 1;
-    const int parity = epoch & 1;
+    const int parity = epoch & (kCommSets - 1);
 #pragma unroll
     for (int tok = 0; tok < NTOK; ++tok)
       if (tok < p.m)
@@ -405,28 +401,55 @@ __device__ __noinline__ void decode_tile_epilogue(const EpiParams& p, int tl, in
           if (q != c.rank)
             st_relaxed_sys_v2(comm_ar_word(c, c.peer[q], parity, c.rank, tl, tok, lane),
                               make_uint2(out[tok], stamp));
-    const bool pair = p.fusion != FUSE_SILU_MUL;
-    const int c0 = pair ? decode_row_to_n(p, tl, lane) : tl * 32 + lane;
-    const int c1 = decode_row_to_n(p, tl, lane + 32);
-    for (int r = 0; r < c.world; ++r) {
-      if (r == c.rank) continue;
-      __nv_bfloat16* dst = p.y + (static_cast<int64_t>(r) - c.rank) * p.n_out;
+  }
+}
+
+// Receives the previous launch's all-gather (see CommPending): the (tile, source rank) pairs
+// are dealt round-robin to the CTAs, one warp each; lane l copies its word of every token into
+// this rank's gathered tensor.  `epoch` is the running launch's, the words carry the stamp of
+// the launch before it.
+__device__ __noinline__ void comm_receive_pending(const CommParams& c, uint32_t epoch, int* status, int lane,
+                                                  int worker, int workers) {
+  const CommPending& g = c.pend;
+  const uint32_t stamp = epoch;  // (epoch - 1) + 1
+  const int set = (epoch - 1u) & (kCommSets - 1);
+  const int items = g.tiles * (c.world - 1);
+  for (int item = worker; item < items; item += workers) {
+    const int tl = item / (c.world - 1);
+    int r = item - tl * (c.world - 1);
+    if (r >= c.rank) ++r;
+    int c0, c1;
+    if (g.gate_up) {
+      c0 = tl * 32 + lane;
+      c1 = g.n / 2 + tl * 32 + lane;
+    } else {
+      c0 = tl * kTileN + lane;
+      c1 = tl * kTileN + lane + 32;
+    }
+    __nv_bfloat16* dst = g.dst + static_cast<int64_t>(r) * g.n_out;
+    const int64_t ld = static_cast<int64_t>(g.n_out) * c.world;
+    for (int h = 0; h < g.m; h += 4) {
+      uint2 v[4];
 #pragma unroll
-      for (int h = 0; h < NTOK; h += 8) {
-        if (h >= p.m) continue;
-        uint32_t w[8];
-        comm_wait_words8([&](int tok) { return comm_ar_word(c, c.peer[c.rank], parity, r, tl, tok, lane); }, h, p.m,
-                         stamp, p.status, w);
+      for (int i = 0; i < 4; ++i)
+        if (h + i < g.m) v[i] = ld_relaxed_sys_v2(comm_ar_word(c, c.peer[c.rank], set, r, tl, h + i, lane));
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (h + i < p.m) {
-            const size_t o = static_cast<size_t>(h + i) * p.ldy;
-            if (c0 < p.n_out) dst[o + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w[i] & 0xffffu));
-            if (pair && c1 < p.n_out) dst[o + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w[i] >> 16));
-          }
-      }
+      for (int i = 0; i < 4; ++i)
+        if (h + i < g.m) {
+          const uint32_t w = v[i].y == stamp
+                                 ? v[i].x
+                                 : comm_wait_word(comm_ar_word(c, c.peer[c.rank], set, r, tl, h + i, lane), stamp, status);
+          const int64_t o = static_cast<int64_t>(h + i) * ld;
+          if (c0 < g.n_out) dst[o + c0] = __ushort_as_bfloat16(static_cast<unsigned short>(w & 0xffffu));
+          if (g.pair && c1 < g.n_out) dst[o + c1] = __ushort_as_bfloat16(static_cast<unsigned short>(w >> 16));
+        }
     }
   }
+}
+
+__global__ void __launch_bounds__(32) comm_fence_kernel(const __grid_constant__ CommParams c, int* status) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(c.peer[c.rank]));
+  comm_receive_pending(c, epoch, status, threadIdx.x, blockIdx.x, gridDim.x);
 }
 
 // COMM: compiled with the tensor-parallel exchange in the epilogue (the plain variant carries
@@ -597,11 +620,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     if (lane == 0) second = atomicAdd(&hdr->finished_warps, 1);
     if (!__shfl_sync(0xffffffffu, second, 0)) return;
     if (lane == 0) {
+      // the end of the grid orders these stores before anything the next launch reads
       uint32_t* ctl = comm_ctl(p.comm.peer[p.comm.rank]);
-      __threadfence();
       if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {
         ctl[1] = 0;
-        __threadfence();
         *reinterpret_cast<volatile uint32_t*>(ctl) = epoch + 1;
       }
     }
@@ -834,8 +856,12 @@ __global__ void __launch_bounds__(kThreads, 2)
     int pend_tile = -1;
     unsigned pend_old = 0;
     grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid now
-    if (COMM && p.comm.mode != kCommNone)
+    if (COMM && p.comm.mode != kCommNone) {
       epoch = *reinterpret_cast<volatile uint32_t*>(comm_ctl(p.comm.peer[p.comm.rank]));
+      // the previous launch's all-gather, received while this launch's weights stream
+      if (p.comm.pend.dst && p.comm.world > 1)
+        comm_receive_pending(hdr->epi.comm, epoch, p.status, lane, blockIdx.x, gridDim.x);
+    }
     if constexpr (!CLUSTER) {
       for (int sg = 0; sg + 1 < nseg; ++sg) {
         take_segment(kBarRedFull, true, tile0 + sg, sg > 0 || kb00 == 0, sg == 0, v0, v1, pend_tile,
@@ -1194,6 +1220,11 @@ DecodePlan decode_int4_plan(int m, int tiles, int kb_per_tile, int kb_per_group,
   // a grid with at most one CTA per SM may use the shared memory two CTAs would share
   if (pl.grid <= num_sms && tiles <= cc.cap[1][best_c]) pl.smem_budget = 2 * kBudgetTwoCtas - 8 * 1024;
   return pl;
+}
+
+cudaError_t launch_comm_fence(const CommParams& c, int* status, int num_sms, cudaStream_t stream) {
+  comm_fence_kernel<<<num_sms, 32, 0, stream>>>(c, status);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_decode_int4(DecodeParams p, const DecodePlan& plan, cudaStream_t stream) {

@@ -129,13 +129,6 @@ __device__ __forceinline__ void tc_store8(const TcParams& p, int tile, int row, 
     }
 }
 
-// Timeline probe for experiments (debug bit 64): CTA 0 writes cycle stamps of its first 64
-// stages into the partial-tile area, [role][stage][4].
-__device__ __forceinline__ void tc_stamp(const TcParams& p, int role, int stage, int k) {
-  if ((p.debug & 64) && blockIdx.x == 0 && stage < 64)
-    reinterpret_cast<long long*>(p.partials)[(role * 64 + stage) * 4 + k] = clock64();
-}
-
 __global__ void __launch_bounds__(kTcThreads, 1)
     woq_int4_tc_kernel(const TcParams p, const __grid_constant__ CUtensorMap xmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -208,23 +201,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   if (warp == kProducerWarp) {
     // packed weights and their group scales
     if (lane == 0) {
-      int pst = 0;
       while (b < b_end) {
         const int nkb = stage_len();
         uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
         const int g0 = kb0 >> p.kbpg_shift;
         const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
-        tc_stamp(p, 0, pst, 0);
         mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 11);
-        tc_stamp(p, 0, pst, 1);
         mbar_arrive_expect_tx(&hdr->w_full[slot], nkb * kTcBlockBytes + ng * 512);
         bulk_g2s(ws, p.wq + (static_cast<size_t>(tile) * p.kb_per_tile + kb0) * kTcBlockBytes,
                  nkb * kTcBlockBytes, &hdr->w_full[slot]);
         bulk_g2s(ws + p.kbs * kTcBlockBytes,
                  p.sz + (static_cast<size_t>(tile) * p.groups + g0) * kTcTileN, ng * 512,
                  &hdr->w_full[slot]);
-        tc_stamp(p, 0, pst, 2);
-        ++pst;
         advance(nkb);
       }
     }
@@ -235,13 +223,9 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const int nkb = stage_len();
         uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
         mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 12);
-        if (p.debug & 8) {
-          mbar_arrive(&hdr->full[slot]);
-        } else {
-          mbar_arrive_expect_tx(&hdr->full[slot], nkb * p.n_tok * 128);
-          for (int j = 0; j < nkb; ++j)
-            tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->full[slot]);
-        }
+        mbar_arrive_expect_tx(&hdr->full[slot], nkb * p.n_tok * 128);
+        for (int j = 0; j < nkb; ++j)
+          tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->full[slot]);
         advance(nkb);
       }
     }
@@ -266,13 +250,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         const int nkb = stage_len();
         const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
         if ((mst & 1) == me) {
-          if (me == 0) tc_stamp(p, 1, mst, 0);
           mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 13);
-          if (me == 0) tc_stamp(p, 1, mst, 1);
           if (first_of_segment) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 15);
           // the previous stage's MMAs have been issued (by the other thread)
           if (mst > 0) mbar_wait(&hdr->issued[me ^ 1], ((mst - 1) >> 1) & 1, abort_flag, p.status, 14);
-          if (me == 0) tc_stamp(p, 1, mst, 2);
           tc_fence_after_sync();
           uint32_t accumulate = first_of_segment ? 0u : 1u;
           uint32_t a_addr = tmem_base + kACol0 + slot * (p.kbs * 32);
@@ -280,19 +261,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           for (int j = 0; j < nkb; ++j) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              if (!(p.debug & 2))
-                umma_f16_ts(d_addr, a_addr + ks * 8, desc_hi | (b_lo + ks * 2), idesc, accumulate);
+              umma_f16_ts(d_addr, a_addr + ks * 8, desc_hi | (b_lo + ks * 2), idesc, accumulate);
               accumulate = 1;
             }
             a_addr += 32;
             b_lo += x_blk_lo;
           }
           mbar_arrive(&hdr->issued[me]);
-          if (p.debug & 16)
-            mbar_arrive(&hdr->free_[slot]);
-          else
-            tc_commit(&hdr->free_[slot]);
-          if (me == 0) tc_stamp(p, 1, mst, 3);
+          tc_commit(&hdr->free_[slot]);
         }
         first_of_segment = false;
         if (seg_end) {
@@ -391,9 +367,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
       // the stages go round-robin to the four warpgroups; the others only keep count
       if ((stage_no & (kWarpGroups - 1)) == wg) {
-        if (tid == 0) tc_stamp(p, 2, stage_no, 0);
         mbar_wait(&hdr->w_full[slot], phase, abort_flag, p.status, 16);
-        if (tid == 0) tc_stamp(p, 2, stage_no, 1);
         const int g0 = kb0 >> p.kbpg_shift;
         for (int j = 0; j < nkb; ++j) {
           const uint4* wp = reinterpret_cast<const uint4*>(ws + j * kTcBlockBytes);
@@ -411,22 +385,15 @@ __global__ void __launch_bounds__(kTcThreads, 1)
                   bf16x2_sub(lop3_and_or(words[jj] >> (4 * s), 0x000f000fu, kBf16Magic), z2), s2);
           }
           if (j == 0) {
-            if (tid == 0) tc_stamp(p, 2, stage_no, 2);
             mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 17);
             tc_fence_after_sync();
-            if (tid == 0) tc_stamp(p, 2, stage_no, 3);
           }
-          if (!(p.debug & 4)) {
-            tmem_st_x32(lane_addr + kACol0 + slot * (p.kbs * 32) + j * 32, r);
-          } else if (r[3] == 0x12345u) {
-            p.status[1] = 1;
-          }
+          tmem_st_x32(lane_addr + kACol0 + slot * (p.kbs * 32) + j * 32, r);
         }
-        if (!(p.debug & 4)) tc_wait_st();
+        tc_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->full[slot]);
-        if (tid == 0) tc_stamp(p, 0, stage_no, 3);
       }
       ++stage_no;
 
@@ -542,16 +509,11 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
   const int budget = 224 * 1024;
   int stages = (budget - kTcHeaderBytes) / (x_stage + w_stage);
   if (stages > kASlots / p.kbs) stages = kASlots / p.kbs;  // one A group in TMEM per slot
-  if (const char* e = getenv("WOQ_B200_TC_STAGES")) {
-    const int want = atoi(e);
-    if (want >= 4 && want <= stages) stages = want;
-  }
   // A warpgroup works on every fourth stage.  With fewer than four pipeline slots it could
   // reach a slot two uses ahead of the producer or of the MMA warp, and a parity wait cannot
   // tell those apart.
   if (stages < 4) return cudaErrorInvalidConfiguration;
   p.stages = stages;
-  if (const char* e = getenv("WOQ_B200_DEBUG")) p.debug = atoi(e);
   const size_t smem = kTcHeaderBytes + static_cast<size_t>(stages) * (x_stage + w_stage);
   cudaError_t e = cudaFuncSetAttribute(woq_int4_tc_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,

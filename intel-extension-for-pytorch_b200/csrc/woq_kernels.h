@@ -10,25 +10,38 @@ namespace woq {
 // Every rank of one node owns a "symmetric" buffer with the same layout and maps all peers'
 // buffers (CUDA IPC).  Layout of one buffer:
 //   [0, 4096)               control words: epoch (u32 @0), finished CTAs of the running grid (u32 @4)
-//   [4096, +slot_n*1024)    exchange words {2 x bf16, stamp}, 8 bytes each:
-//                           [epoch parity][source rank][tile][token][lane]
+//   [4096, +slot_n*2048)    exchange words {2 x bf16, stamp}, 8 bytes each:
+//                           [epoch & 3][source rank][tile][token][lane]
 //   [gather_off, ..)        gather area (the caller places gathered tensors here)
 // A launch with a comm mode is one "epoch" (the same number on every rank, because all ranks
 // issue the same sequence of launches); its stamp is epoch + 1.  The warp that finishes a
 // tile stores each lane's two results and the stamp as one 8-byte word into every other
-// rank's slot (data and mark arrive together, no fence), then polls its own slots for the
-// other ranks' words of the same tile and adds them (all-reduce) or copies them into its
-// gathered tensor (all-gather).  Slots alternate with the epoch's parity: a rank can be at
-// most one epoch ahead of a peer, because finishing an epoch takes every peer's words.
+// rank's slot (data and mark arrive together, no fence).
+//   all-reduce: the same warp then reads its own slots for the other ranks' words of the same
+//     tile (all ranks' loads in flight together) and adds them in rank order;
+//   all-gather: nobody waits.  The NEXT launch on the comm (or comm_fence) copies the words of
+//     the other ranks into this rank's gathered tensor with its otherwise idle epilogue warps,
+//     while its own weights stream: the gathered tensor is complete when that launch ends.
+// Four slot sets, indexed by epoch & 3: finishing the launch of epoch X takes every peer's
+// words of epoch X - 1 at least, so a rank that writes set E & 3 knows every peer has finished
+// the launches up to E - 3, and with them the reading of epoch E - 4.
 constexpr int kCommMaxRanks = 8;
 constexpr int kCommMaxTiles = 1024;
 constexpr int kCommCtlBytes = 4096;
+constexpr int kCommSets = 4;
 enum CommMode { kCommNone = 0, kCommAllReduce = 1, kCommAllGather = 2 };
+
+// The all-gather of the previous launch on the comm, still to be received on this rank.
+struct CommPending {
+  __nv_bfloat16* dst;  // this rank's gathered tensor [m][world * n_out]; null: nothing pending
+  int m, n, n_out, tiles, gate_up, pair;  // of the launch that sent it (pair: two values per word)
+};
 
 struct CommParams {
   uint8_t* peer[kCommMaxRanks];  // base of every rank's buffer as mapped here (peer[rank]: own)
   int mode, world, rank;
   int64_t ar_n;        // 64 x the tiles a slot set holds
+  CommPending pend;
 };
 
 // ---- INT4 decode (M <= 16) -----------------------------------------------------------
@@ -78,6 +91,8 @@ void decode_int4_set_split(int mode);
 DecodePlan decode_int4_plan(int m, int tiles, int kb_per_tile, int kb_per_group, int num_sms);
 size_t decode_int4_partial_bytes(int grid);
 cudaError_t launch_decode_int4(DecodeParams p, const DecodePlan& plan, cudaStream_t stream);
+// Receives a pending all-gather without running a linear (status: the workspace-style status word).
+cudaError_t launch_comm_fence(const CommParams& c, int* status, int num_sms, cudaStream_t stream);
 
 // ---- INT4 tensor-core path (any M up to 256 per launch) --------------------------------
 // Row layout: tiles of 128 output rows x 64 k, 4096 bytes each, [tile][k-block][half][row][16 B].
@@ -106,7 +121,6 @@ struct TcParams {
   int tiles, kb_per_tile, kbpg_shift, groups;
   int kbs, stages;
   int fusion, gate_up;
-  int debug;  // experiment switches: 1 skip dequant math, 2 skip MMA issue, 4 skip TMEM stores
 };
 
 int tc_pick_grid(int tiles, int kb_per_tile, int num_sms);

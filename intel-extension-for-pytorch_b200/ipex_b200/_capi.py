@@ -55,6 +55,8 @@ EXPORTS = [
     "woq_b200_comm_connect",
     "woq_b200_comm_gather_ptr",
     "woq_b200_comm_destroy",
+    "woq_b200_comm_fence",
+    "woq_b200_comm_status",
     "woq_b200_linear_allreduce",
     "woq_b200_linear_allgather",
 ]
@@ -129,6 +131,8 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_comm_gather_ptr.argtypes = [vp]
     L.woq_b200_comm_gather_ptr.restype = vp
     L.woq_b200_comm_destroy.argtypes = [vp]
+    L.woq_b200_comm_fence.argtypes = [vp, vp]
+    L.woq_b200_comm_status.argtypes = [vp, vp]
     L.woq_b200_linear_allreduce.argtypes = [vp, vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, vp, i64,
                                             vp, sz, vp]
     L.woq_b200_linear_allgather.argtypes = [vp, vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, sz, vp, sz, vp]
@@ -244,6 +248,17 @@ class Comm:
         """View of the [m, n_full] bf16 tensor at byte `offset` of this rank's gather area."""
         nbytes = m * n_full * 2
         return self._gather[offset:offset + nbytes].view(torch.bfloat16).view(m, n_full)
+
+    def fence(self):
+        """Completes an outstanding all-gather on this rank (woq_b200_comm_fence): after it the
+        whole gathered tensor is in place.  Needed before reading other ranks' columns unless
+        another fused call on the comm has run since the gather."""
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_comm_fence(self._h, _stream()))
+
+    def status(self):
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_comm_status(self._h, _stream()))
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value:

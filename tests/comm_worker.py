@@ -78,7 +78,10 @@ def main():
         x = bf16_tensor(make_acts(m, K_COL, seed=seed), dev)
         full = cctx.linear_allgather(comm, x, gather_offset=0)
         act = gctx.linear_allgather(comm, x, capi.FUSE_SILU_MUL, gather_offset=off2)
+        # the first gather was completed by the second call; the second one by the fence
+        comm.fence()
         torch.cuda.synchronize()
+        comm.status()
         res[f"col_m{m}"] = bf16_numpy(full)
         res[f"gateup_m{m}"] = bf16_numpy(act)
         # an exchange between two gathers into the same place, as the API asks

@@ -2,7 +2,8 @@
 woq_b200_linear_allgather), through the C ABI.
 
 One GPU: a single-rank comm goes through the same epilogue code (stores, stamps, epochs) and
-must reproduce the plain linear bit for bit.  Two or more GPUs: one process per GPU
+must reproduce the plain linear bit for bit.  An all-gather leaves the other ranks' columns to
+the next fused call or to Comm.fence(); the workers read a gathered tensor only after one.  Two or more GPUs: one process per GPU
 (tests/comm_worker.py); the row-parallel result is checked against the oracle's
 row_parallel_linear and must be bit-identical on all ranks, the gathered column-parallel
 result must be bit-identical to the unsharded linear.
