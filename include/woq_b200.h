@@ -14,6 +14,8 @@
  *       W[n,k] = (q[n,k] - zp[n,g]) * bf16(scale[n,g]), fp32 accumulation.
  *   INT8 weights, lowp INT8:       per-token symmetric int8 activations, int32 accumulation,
  *       y = bf16( float(acc) * scale_a[m] * scale_w[n] + bias[n] ), then post-op.
+ *   Everything else the reference routes (NF4 / FP8 / INT8 weights with floating compute, fp16
+ *   and fp32 compute, shapes off the 64-element grid): woq_b200_linear_any.
  */
 #ifndef WOQ_B200_H_
 #define WOQ_B200_H_
@@ -46,13 +48,17 @@ extern "C" {
 #define WOQ_B200_LOWP_INT8 3
 
 /* Dynamic activation quantisation of the INT8 compute path (woq_defines.h:11-19): one range
- * for the whole activation tensor or one per token; asymmetric u8 codes with a zero point, or
- * symmetric s8 codes.  The per-K-block modes (1, 3, 5, 7) are not built. */
+ * for the whole activation tensor, per K block (shared by all tokens), per token, or per token
+ * and K block; asymmetric u8 codes with a zero point, or (+4) symmetric s8 codes. */
 #define WOQ_B200_ACT_NONE (-1)
 #define WOQ_B200_ACT_PER_TENSOR 0
+#define WOQ_B200_ACT_PER_K_BLOCK 1
 #define WOQ_B200_ACT_PER_M 2
+#define WOQ_B200_ACT_PER_M_K_BLOCK 3
 #define WOQ_B200_ACT_PER_TENSOR_SYM 4
+#define WOQ_B200_ACT_PER_K_BLOCK_SYM 5
 #define WOQ_B200_ACT_PER_M_SYM 6
+#define WOQ_B200_ACT_PER_M_K_BLOCK_SYM 7
 
 #define WOQ_B200_FMT_PLAIN 0 /* INT4: [N, K/2] u8, even k in the low nibble; INT8: [N, K] s8 */
 #define WOQ_B200_FMT_GPTQ 1  /* [K/8, N] int32                                             */
@@ -100,6 +106,12 @@ extern "C" {
  * loader can create hundreds of contexts back to back.  The inputs must stay alive until the
  * stream has passed the create call either way.  Plain-format INT4 contexts only. */
 #define WOQ_B200_LAYOUT_DEFER_CHECK 0x10
+/* Keep the weight in its plain layout and run it through the general kernel (any weight dtype,
+ * fp32 / fp16 / bf16 compute, any K, group sizes that are multiples of 8).  Descriptions the
+ * tuned kernels do not take (NF4 / FP8 weights, INT8 weights without INT8 compute, lowp FP16,
+ * K not a multiple of 64, group sizes below 64) get this route without the flag; set it to run
+ * an INT4 layer on fp32 or fp16 activations under lowp NONE. */
+#define WOQ_B200_LAYOUT_GENERIC 0x20
 
 /* kernel selection for INT4 weights.  AUTO, TENSOR_CORE and STREAM all multiply by the
  * bf16-rounded dequantised weights bf16((q - zp) * bf16(scale)) and differ only in summation
@@ -170,6 +182,17 @@ int woq_b200_ctx_destroy(woq_b200_ctx* ctx);
 /* Copy of the descriptor a context was created with. */
 int woq_b200_ctx_desc(const woq_b200_ctx* ctx, woq_b200_desc* out);
 
+/* Which kernels a context runs on (decided by woq_b200_ctx_create from the description):
+ * the tuned INT4 / bf16 kernels, the tcgen05 INT8 kernel (INT8 weights, whole-K activation
+ * ranges), the general kernel (woq_b200_linear_any), or the K-block INT8 kernel.  -1: not a
+ * context.  No reference counterpart (the reference picks its kernel per call,
+ * csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:56-165). */
+#define WOQ_B200_ROUTE_INT4_BF16 0
+#define WOQ_B200_ROUTE_INT8 1
+#define WOQ_B200_ROUTE_GENERAL 2
+#define WOQ_B200_ROUTE_INT8_BLOCK 3
+int woq_b200_ctx_route(const woq_b200_ctx* ctx);
+
 /* Bytes of the packed weight + scale buffers held on the device. */
 size_t woq_b200_ctx_device_bytes(const woq_b200_ctx* ctx);
 
@@ -195,6 +218,20 @@ size_t woq_b200_workspace_header_bytes(void);
 int woq_b200_linear(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx, int32_t fusion,
                     const void* const* others, int32_t n_others, void* y, int64_t ldy,
                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* woq_b200_linear for activations, outputs and extra tensors of `io_dtype` (WOQ_B200_T_BF16,
+ * _F16 or _F32).  The compute dtype follows the reference's routing
+ * (csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:75-165): lowp BF16 -> bf16, lowp FP16 -> fp16, lowp
+ * NONE -> the activation's dtype; W = round_c((code - zp) * round_c(scale)) with round_c the
+ * rounding to the compute dtype (none for fp32), activations rounded to it, fp32 accumulation,
+ * result rounded to io_dtype, post-op on io_dtype data.  Codes: INT4 0..15, NF4 through the
+ * reference's table (csrc/cpu/aten/utils/woq_utils.h:34-51), INT8 -128..127, FP8 e4m3 through
+ * the reference's conversion (csrc/cpu/aten/utils/woq.h:465-483).  Contexts on the general
+ * route take every io_dtype; the others take bf16 only (and forward to woq_b200_linear).
+ * No fused silu*mul on the general route. */
+int woq_b200_linear_any(const woq_b200_ctx* ctx, const void* x, int32_t io_dtype, int64_t m, int64_t ldx,
+                        int32_t fusion, const void* const* others, int32_t n_others, void* y, int64_t ldy,
+                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- Tensor-parallel layers on the GPUs of one node ------------------------------------------
  * The reference shards column-parallel layers along N and row-parallel layers along K and
@@ -306,6 +343,10 @@ int woq_b200_moe_expert(const woq_b200_ctx* w13, const woq_b200_ctx* w2, const v
  * uses for its tiles (the reference's Dequantize<bfloat16>, csrc/cpu/aten/utils/woq.h:1501-1581). */
 int woq_b200_dump_dequant(const woq_b200_ctx* ctx, void* w_bf16, void* stream);
 
+/* The same for a general-route context: [N, K] fp32 holding the values the kernel multiplies by
+ * when it computes in `compute_dtype` (WOQ_B200_T_BF16 / _F16 / _F32). */
+int woq_b200_dump_dequant_f32(const woq_b200_ctx* ctx, int32_t compute_dtype, float* w_f32, void* stream);
+
 /* INT8-lowp internals for M tokens: quantised activations qa[M, K] (s8, or u8 in the
  * asymmetric modes), their scales sa[M] f32 (dynamic_quantize_per_block,
  * csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750) and the int32 accumulators acc[M, N]
@@ -314,6 +355,18 @@ int woq_b200_dump_dequant(const woq_b200_ctx* ctx, void* w_bf16, void* stream);
 int woq_b200_int8_internals(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx,
                             int8_t* qa, float* sa, int32_t* acc, void* workspace,
                             size_t workspace_bytes, void* stream);
+
+/* The same for the K-block INT8 route (INT4 weights with INT8 compute, grouped INT8 weights, or
+ * an activation range per K block: act_quant_mode 1, 3, 5, 7): the activation codes qa[M, K] in
+ * natural order (u8 for the asymmetric modes, s8 bit patterns for the symmetric ones), scales
+ * sa[M, K / block] and zero points zpa[M, K / block] per token and K block (modes that share a
+ * range repeat it), and the int32 block accumulators acc[K / block, M, N] after the weight zero
+ * point and the activation compensation (csrc/cpu/aten/utils/woq.h:962-1126).  Any output may
+ * be null.  woq_b200_int8_block_size gives the K block (0 for other contexts). */
+int woq_b200_int8_block_internals(const woq_b200_ctx* ctx, const void* x, int64_t m, int64_t ldx, uint8_t* qa,
+                                  float* sa, int32_t* zpa, int32_t* acc, void* workspace,
+                                  size_t workspace_bytes, void* stream);
+int woq_b200_int8_block_size(const woq_b200_ctx* ctx);
 
 /* The activation zero points zp[M] (int32) that the latest INT8 call on `workspace` with M
  * tokens left there; zeros for the symmetric modes. */

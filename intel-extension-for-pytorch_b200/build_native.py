@@ -25,6 +25,8 @@ CUDA_SOURCES = [
     "woq_int4_tc.cu",
     "woq_int8.cu",
     "woq_static_scratch.cu",
+    "woq_generic.cu",
+    "woq_int8_block.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

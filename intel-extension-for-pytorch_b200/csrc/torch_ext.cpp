@@ -94,6 +94,9 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
   // a second context the first time a call brings more than 16 tokens, so that a model that only
   // decodes holds one copy of its weights.
   woq_b200_ctx* ctx_tc = nullptr;
+  // lowp NONE computes in the activation's dtype: fp32 / fp16 activations run on a general-route
+  // copy of the layer, packed the first time such a call arrives
+  woq_b200_ctx* ctx_gen = nullptr;
   std::mutex tc_mu;
   // constructor arguments, kept so that the context can be pickled in a layout-independent way
   int64_t weight_dtype, group_size, lowp_mode, act_quant_mode;
@@ -108,11 +111,35 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
   ~WoqLinearOpContext() override {
     if (ctx) woq_b200_ctx_destroy(ctx);
     if (ctx_tc) woq_b200_ctx_destroy(ctx_tc);
+    if (ctx_gen) woq_b200_ctx_destroy(ctx_gen);
+  }
+
+  // the general-route context for activations that are not bf16 (lowp NONE on a tuned INT4 layer)
+  woq_b200_ctx* ctx_general() {
+    if (woq_b200_ctx_route(ctx) == WOQ_B200_ROUTE_GENERAL) return ctx;
+    std::lock_guard<std::mutex> lock(tc_mu);
+    if (!ctx_gen) {
+      woq_b200_desc d{};
+      WOQ_CHECK(woq_b200_ctx_desc(ctx, &d));
+      TORCH_CHECK(!(d.layout_flags & WOQ_B200_LAYOUT_GATE_UP), "WOQ: a gate/up layer takes bf16 activations only");
+      d.weight_format = WOQ_B200_FMT_PLAIN;
+      d.layout_flags = WOQ_B200_LAYOUT_GENERIC | WOQ_B200_LAYOUT_SCALES_NK;
+      auto stream = at::cuda::getCurrentCUDAStream(device);
+      auto plain = at::empty({weight_shape[0], (weight_shape[1] + 1) / 2},
+                             at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
+      WOQ_CHECK(woq_b200_ctx_unpack(ctx, plain.data_ptr(), stream.stream()));
+      WOQ_CHECK(woq_b200_ctx_create(&d, plain.data_ptr(), scales.data_ptr(),
+                                    zero_points.defined() ? zero_points.data_ptr() : nullptr,
+                                    bias.defined() ? bias.data_ptr() : nullptr, stream.stream(), &ctx_gen));
+    }
+    return ctx_gen;
   }
 
   // the context a call with M tokens runs on
   woq_b200_ctx* ctx_for(int64_t M) {
-    if (M <= 16 || weight_dtype != WOQ_B200_DTYPE_INT4 || (layout_flags & WOQ_B200_LAYOUT_TC_ONLY)) return ctx;
+    if (M <= 16 || weight_dtype != WOQ_B200_DTYPE_INT4 || (layout_flags & WOQ_B200_LAYOUT_TC_ONLY) ||
+        woq_b200_ctx_route(ctx) != WOQ_B200_ROUTE_INT4_BF16)
+      return ctx;
     std::lock_guard<std::mutex> lock(tc_mu);
     if (!ctx_tc) {
       woq_b200_desc d{};
@@ -215,9 +242,10 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
   // plain [N, K/2] u8 (INT4) or [N, K] s8 (INT8): the reference's to_public(get_weight())
   at::Tensor get_weight() {
     c10::cuda::CUDAGuard guard(device);
-    const bool int4 = weight_dtype == WOQ_B200_DTYPE_INT4;
+    const bool int4 = weight_dtype == WOQ_B200_DTYPE_INT4 || weight_dtype == WOQ_B200_DTYPE_NF4;
+    const bool bytes_u8 = int4 || weight_dtype == WOQ_B200_DTYPE_FP8;
     auto out = at::empty({weight_shape[0], int4 ? (weight_shape[1] + 1) / 2 : weight_shape[1]},
-                         at::TensorOptions().dtype(int4 ? at::kByte : at::kChar).device(at::kCUDA, device));
+                         at::TensorOptions().dtype(bytes_u8 ? at::kByte : at::kChar).device(at::kCUDA, device));
     WOQ_CHECK(woq_b200_ctx_unpack(ctx, out.data_ptr(), at::cuda::getCurrentCUDAStream(device).stream()));
     return inv_perm.defined() ? shuffle_int4_columns(out, inv_perm) : out;
   }
@@ -248,6 +276,7 @@ struct WoqLinearOpContext : torch::CustomClassHolder {
     std::lock_guard<std::mutex> lock(tc_mu);
     std::swap(ctx, fresh->ctx);
     std::swap(ctx_tc, fresh->ctx_tc);
+    std::swap(ctx_gen, fresh->ctx_gen);
     weight_dtype = fresh->weight_dtype;
     group_size = fresh->group_size;
     lowp_mode = fresh->lowp_mode;
@@ -292,15 +321,19 @@ at::Tensor run(WoqLinearOpContext* c, const at::Tensor& input, int32_t fusion,
   at::Tensor x = input.reshape({-1, K});
   if (c->perm.defined()) x = x.index_select(1, c->perm);  // act-order: channels in group order
   const auto in_dtype = x.scalar_type();
-  // lowp NONE computes in the activation's dtype (reference: WoqLinearKrnl.cpp:75-106 routes fp32
-  // and fp16 activations to fp32 / fp16 kernels); only the bf16 route is built, and running the
-  // others in bf16 would narrow them without a word.  lowp BF16 and INT8 convert the activation
-  // themselves in the reference, so any floating input is taken there.
-  TORCH_CHECK(c->lowp_mode != WOQ_B200_LOWP_NONE || in_dtype == at::kBFloat16,
-              "WOQ: lowp_mode NONE computes in the activation dtype and only bfloat16 activations are built "
-              "(got ", in_dtype, "); use lowp_mode BF16 or cast the activation");
-  if (in_dtype != at::kBFloat16) x = x.to(at::kBFloat16);
-  if (x.stride(-1) != 1 || (x.stride(0) % 8) != 0 || (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15))
+  TORCH_CHECK(in_dtype == at::kBFloat16 || in_dtype == at::kHalf || in_dtype == at::kFloat,
+              "WOQ: activations must be bfloat16, float16 or float32, got ", in_dtype);
+  // Compute dtype as the reference routes it (WoqLinearKrnl.cpp:75-165): lowp BF16 / INT8 convert
+  // the activation themselves, so any floating input is cast to bf16 for the tuned kernels; lowp
+  // NONE computes in the activation's dtype and lowp FP16 in fp16, which the general kernel does
+  // (on the layer's general-route context) with the activation left as it is.
+  const int route = woq_b200_ctx_route(c->ctx);
+  const bool general = route == WOQ_B200_ROUTE_GENERAL ||
+                       (route == WOQ_B200_ROUTE_INT4_BF16 && c->lowp_mode == WOQ_B200_LOWP_NONE &&
+                        in_dtype != at::kBFloat16);
+  if (!general && in_dtype != at::kBFloat16) x = x.to(at::kBFloat16);
+  const int64_t esz = static_cast<int64_t>(x.element_size());
+  if (x.stride(-1) != 1 || (x.stride(0) * esz % 16) != 0 || (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15))
     x = x.contiguous();
   const int64_t M = x.size(0);
   const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? N / 2 : N;
@@ -310,23 +343,32 @@ at::Tensor run(WoqLinearOpContext* c, const at::Tensor& input, int32_t fusion,
   for (auto& o : others) {
     at::Tensor t = o.reshape({-1, n_out});
     TORCH_CHECK(t.size(0) == M, "WOQ: extra operand has ", t.size(0), " rows, expected ", M);
-    if (t.scalar_type() != at::kBFloat16) t = t.to(at::kBFloat16);
+    if (t.scalar_type() != x.scalar_type()) t = t.to(x.scalar_type());
     oth.push_back(t.contiguous());
     optr.push_back(oth.back().data_ptr());
   }
   auto stream = at::cuda::getCurrentCUDAStream(c->device);
   if (M > 0) {
-    woq_b200_ctx* k = c->ctx_for(M);
+    woq_b200_ctx* k = general ? c->ctx_general() : c->ctx_for(M);
     const size_t need = woq_b200_workspace_bytes(k, M);
     at::Tensor& ws = workspace_for(c->device, stream.stream(), need);
-    WOQ_CHECK(woq_b200_linear(k, x.data_ptr(), M, x.stride(0), fusion,
-                              optr.empty() ? nullptr : optr.data(), static_cast<int32_t>(optr.size()),
-                              y.data_ptr(), y.stride(0), ws.data_ptr(), ws.numel(), stream.stream()));
+    if (general) {
+      const int io = x.scalar_type() == at::kBFloat16 ? WOQ_B200_T_BF16
+                     : x.scalar_type() == at::kHalf   ? WOQ_B200_T_F16
+                                                      : WOQ_B200_T_F32;
+      WOQ_CHECK(woq_b200_linear_any(k, x.data_ptr(), io, M, x.stride(0), fusion,
+                                    optr.empty() ? nullptr : optr.data(), static_cast<int32_t>(optr.size()),
+                                    y.data_ptr(), y.stride(0), ws.data_ptr(), ws.numel(), stream.stream()));
+    } else {
+      WOQ_CHECK(woq_b200_linear(k, x.data_ptr(), M, x.stride(0), fusion,
+                                optr.empty() ? nullptr : optr.data(), static_cast<int32_t>(optr.size()),
+                                y.data_ptr(), y.stride(0), ws.data_ptr(), ws.numel(), stream.stream()));
+    }
   }
   auto sizes = input.sizes().vec();
   sizes.back() = n_out;
   y = y.view(sizes);
-  return in_dtype == at::kBFloat16 ? y : y.to(in_dtype);
+  return y.scalar_type() == in_dtype ? y : y.to(in_dtype);
 }
 
 at::Tensor woq_unary(const at::Tensor& input, const at::Tensor& handle, int32_t fusion) {

@@ -7,6 +7,8 @@
 #include <cstring>
 #include <new>
 
+#include <cuda_fp16.h>
+
 #include "../../include/woq_b200.h"
 #include "woq_internal.h"
 #include "woq_kernels.h"
@@ -84,6 +86,14 @@ struct woq_b200_ctx {
   // points outside the range of the shift-free dequantiser).  With WOQ_B200_LAYOUT_DEFER_CHECK
   // the flag travels to pinned host memory asynchronously and is looked at by the first call
   // that needs it, so that loading many layers does not synchronise once per layer.
+  // general route (woq_generic.cu): plain weight bytes, fp32 scales / zero points [n][groups]
+  int is_generic;
+  uint8_t* g_w;
+  float* g_scales;
+  float* g_zps;
+  int g_row_bytes, g_group, g_groups;
+  // INT8 compute with K-block scaling (woq_int8_block.cu): the buffers above plus comp
+  int is_i8block, kb, kc;
   int* d_flag;
   int* h_flag;
   cudaEvent_t flag_ready;
@@ -229,6 +239,254 @@ Int8Workspace int8_ws_layout(const woq_b200_ctx* c, int64_t m) {
 
 }  // namespace
 
+namespace {
+
+__global__ void to_f32_kernel(const void* src, float* dst, int64_t count, int dtype) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  float v;
+  switch (dtype) {
+    case WOQ_B200_T_F32: v = static_cast<const float*>(src)[i]; break;
+    case WOQ_B200_T_F16: v = __half2float(static_cast<const __half*>(src)[i]); break;
+    case WOQ_B200_T_BF16: v = __bfloat162float(static_cast<const __nv_bfloat16*>(src)[i]); break;
+    case WOQ_B200_T_U8: v = static_cast<float>(static_cast<const uint8_t*>(src)[i]); break;
+    default: v = static_cast<float>(static_cast<const int8_t*>(src)[i]); break;
+  }
+  dst[i] = v;
+}
+
+// Does a description need the general route (woq_generic.cu)?  The tuned kernels take INT4 with
+// bf16 compute on 64-aligned shapes and INT8 with INT8 compute.
+bool wants_generic(const woq_b200_desc* d) {
+  if (d->layout_flags & WOQ_B200_LAYOUT_GENERIC) return true;
+  if (d->weight_dtype == WOQ_B200_DTYPE_NF4 || d->weight_dtype == WOQ_B200_DTYPE_FP8) return true;
+  if (d->lowp_mode == WOQ_B200_LOWP_INT8) return false;
+  if (d->weight_dtype == WOQ_B200_DTYPE_INT8) return true;
+  if (d->lowp_mode == WOQ_B200_LOWP_FP16) return true;
+  if (d->k % 64 != 0) return true;
+  const int64_t g_eff = d->group_size > 0 ? d->group_size : d->k;
+  if (g_eff < d->k && (g_eff % 64 != 0 || (g_eff & (g_eff - 1)) != 0)) return true;
+  return false;
+}
+
+// lowp INT8 descriptions the tcgen05 INT8 kernel does not take: INT4 weights, grouped weight
+// scales, or an activation range per K block (modes 1, 3, 5, 7)
+bool wants_i8block(const woq_b200_desc* d) {
+  if (d->lowp_mode != WOQ_B200_LOWP_INT8) return false;
+  if (d->weight_dtype == WOQ_B200_DTYPE_INT4) return true;
+  if (d->weight_dtype != WOQ_B200_DTYPE_INT8) return false;
+  if (d->group_size > 0 && d->group_size < d->k) return true;
+  return (d->act_quant_mode & 1) != 0;
+}
+
+struct I8BlockWs {
+  size_t qa, sa, zpa, sumqa, range, folded, total;
+};
+I8BlockWs i8block_ws(const woq_b200_ctx* c, int64_t m) {
+  I8BlockWs w;
+  const size_t mk = static_cast<size_t>(m) * c->kc;
+  size_t off = kWsHeaderBytes;
+  w.sa = off;      off += (mk * 4 + 255) / 256 * 256;
+  w.zpa = off;     off += (mk * 4 + 255) / 256 * 256;
+  w.sumqa = off;   off += (mk * 4 + 255) / 256 * 256;
+  w.range = off;   off += (mk * 8 + 255) / 256 * 256;
+  w.folded = off;  off += (static_cast<size_t>(m > c->kc ? m : c->kc) * 8 + 255) / 256 * 256;
+  w.qa = off;      off += (static_cast<size_t>(m) * c->desc.k + 255) / 256 * 256;
+  w.total = off;
+  return w;
+}
+
+int create_generic(const woq_b200_desc* d, const void* qweight, const void* scales, const void* zero_points,
+                   const void* bias, cudaStream_t stream, woq_b200_ctx** out);
+
+int create_i8block(const woq_b200_desc* d, const void* qweight, const void* scales, const void* zero_points,
+                   const void* bias, cudaStream_t stream, woq_b200_ctx** out) {
+  if (d->act_quant_mode < 0 || d->act_quant_mode > 7)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "activation quantisation mode must be 0..7 for lowp INT8, got %d", d->act_quant_mode);
+  if (d->layout_flags & WOQ_B200_LAYOUT_GATE_UP)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "no fused silu*mul on the K-block INT8 route (use silu, then mul)");
+  int kb = d->group_size > 0 && d->group_size < 128 ? d->group_size : 128;
+  while (d->k % kb) kb /= 2;
+  if (kb < 64)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT8 compute needs a K block of 64 or 128 (K=%lld, group %d give %d)",
+                (long long)d->k, d->group_size, kb);
+  // storage: the plain weight and fp32 scales / zero points of the general route
+  woq_b200_desc g = *d;
+  g.lowp_mode = WOQ_B200_LOWP_BF16;
+  g.layout_flags |= WOQ_B200_LAYOUT_GENERIC;
+  woq_b200_ctx* c = nullptr;
+  if (int rc = create_generic(&g, qweight, scales, zero_points, bias, stream, &c)) return rc;
+  c->desc = *d;
+  c->is_generic = 0;
+  c->is_i8block = 1;
+  c->kb = kb;
+  c->kc = static_cast<int>(d->k / kb);
+  if (!(d->act_quant_mode & 4)) {
+    cudaError_t e = cudaMalloc(&c->comp, static_cast<size_t>(d->n) * c->kc * sizeof(int32_t));
+    if (e == cudaSuccess)
+      e = woq::launch_weight_block_sum(c->g_w, c->g_zps, (int)d->n, (int)d->k, kb, c->g_group, c->g_groups,
+                                       d->weight_dtype == WOQ_B200_DTYPE_INT4 ? 8.f : 0.f,
+                                       d->weight_dtype == WOQ_B200_DTYPE_INT4, c->comp, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) {
+      woq_b200_ctx_destroy(c);
+      return fail(WOQ_B200_ERR_CUDA, "block sums of the weight: %s", cudaGetErrorString(e));
+    }
+    woq::count_launch();
+  }
+  *out = c;
+  return WOQ_B200_OK;
+}
+
+int run_i8block(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion, const void* o0,
+                const void* o1, void* y, int64_t ldy, uint8_t* qa_natural, float* sa_out, int32_t* zpa_out,
+                int32_t* acc_out, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  const I8BlockWs L = i8block_ws(c, m);
+  if (ws_bytes < L.total) return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", ws_bytes, L.total);
+  if (fusion == WOQ_B200_FUSE_SILU_MUL)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "no fused silu*mul on the K-block INT8 route (use silu, then mul)");
+  uint8_t* w8 = static_cast<uint8_t*>(ws);
+  const int mode = c->desc.act_quant_mode;
+  const int w4 = c->desc.weight_dtype == WOQ_B200_DTYPE_INT4;
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  float* sa = reinterpret_cast<float*>(w8 + L.sa);
+  int32_t* zpa = reinterpret_cast<int32_t*>(w8 + L.zpa);
+  int32_t* sumqa = reinterpret_cast<int32_t*>(w8 + L.sumqa);
+  float* range = reinterpret_cast<float*>(w8 + L.range);
+  float* folded = reinterpret_cast<float*>(w8 + L.folded);
+  if (qa_natural) {  // parity hook: the codes in natural order
+    CUDA_TRY(woq::launch_act_block_quant(xb, ldx, (int)m, (int)c->desc.k, c->kb, mode, 0, qa_natural, sa, zpa, sumqa,
+                                         range, folded, stream));
+    woq::count_launch();
+  }
+  CUDA_TRY(woq::launch_act_block_quant(xb, ldx, (int)m, (int)c->desc.k, c->kb, mode, w4, w8 + L.qa, sa, zpa, sumqa,
+                                       range, folded, stream));
+  woq::count_launch();
+  const size_t mk = static_cast<size_t>(m) * c->kc;
+  if (sa_out) CUDA_TRY(cudaMemcpyAsync(sa_out, sa, mk * 4, cudaMemcpyDeviceToDevice, stream));
+  if (zpa_out) CUDA_TRY(cudaMemcpyAsync(zpa_out, zpa, mk * 4, cudaMemcpyDeviceToDevice, stream));
+  if (!y && !acc_out) return WOQ_B200_OK;
+  woq::I8BlockParams p{};
+  p.w = c->g_w;
+  p.sw = c->g_scales;
+  p.zpw = c->g_zps;
+  p.comp = c->comp;
+  p.qa = w8 + L.qa;
+  p.sa = sa;
+  p.zpa = zpa;
+  p.sumqa = sumqa;
+  p.bias = c->bias;
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.other0 = static_cast<const __nv_bfloat16*>(o0);
+  p.other1 = static_cast<const __nv_bfloat16*>(o1);
+  p.acc_out = acc_out;
+  p.ldy = ldy;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(c->desc.n);
+  p.k = static_cast<int>(c->desc.k);
+  p.kb = c->kb;
+  p.kc = c->kc;
+  p.group = c->g_group;
+  p.groups = c->g_groups;
+  p.fusion = fusion;
+  p.w4 = w4;
+  p.asym = (mode & 4) ? 0 : 1;
+  p.default_zp = w4 ? 8.f : 0.f;
+  CUDA_TRY(woq::launch_i8_block(p, stream));
+  woq::count_launch();
+  return WOQ_B200_OK;
+}
+
+int create_generic(const woq_b200_desc* d, const void* qweight, const void* scales, const void* zero_points,
+                   const void* bias, cudaStream_t stream, woq_b200_ctx** out) {
+  if (d->lowp_mode == WOQ_B200_LOWP_INT8)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the general route computes in fp32 / fp16 / bf16, not INT8");
+  if (d->weight_format != WOQ_B200_FMT_PLAIN)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the general route takes plain-format weights (GPTQ / AWQ layouts go "
+                "through the INT4 bf16 route: K %% 64 == 0, power-of-two group size >= 64)");
+  if (d->layout_flags & WOQ_B200_LAYOUT_GATE_UP)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the gate/up layout belongs to the INT4 bf16 and INT8 routes");
+  const int64_t g_eff = d->group_size > 0 && d->group_size < d->k ? d->group_size : d->k;
+  if (g_eff < d->k && g_eff % 8 != 0)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "group size must be a multiple of 8 (got %d)", d->group_size);
+  const bool four_bit = d->weight_dtype == WOQ_B200_DTYPE_INT4 || d->weight_dtype == WOQ_B200_DTYPE_NF4;
+  if ((d->weight_dtype == WOQ_B200_DTYPE_NF4 || d->weight_dtype == WOQ_B200_DTYPE_FP8) && zero_points)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "NF4 / FP8 weights are symmetric: no zero points");
+  woq_b200_ctx* c = new (std::nothrow) woq_b200_ctx();
+  if (!c) return fail(WOQ_B200_ERR_CUDA, "out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->desc = *d;
+  c->is_generic = 1;
+  c->g_row_bytes = static_cast<int>(four_bit ? (d->k + 1) / 2 : d->k);
+  c->g_group = static_cast<int>(g_eff);
+  c->g_groups = static_cast<int>((d->k + g_eff - 1) / g_eff);
+  auto bail = [&](int rc) {
+    cudaFree(c->g_w);
+    cudaFree(c->g_scales);
+    cudaFree(c->g_zps);
+    cudaFree(c->bias);
+    delete c;
+    return rc;
+  };
+#define CUDA_TRY_G(expr)                                                                    \
+  do {                                                                                      \
+    cudaError_t e__ = (expr);                                                               \
+    if (e__ != cudaSuccess)                                                                 \
+      return bail(fail(WOQ_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__))); \
+  } while (0)
+  CUDA_TRY_G(cudaGetDevice(&c->device));
+  CUDA_TRY_G(cudaDeviceGetAttribute(&c->num_sms, cudaDevAttrMultiProcessorCount, c->device));
+  c->wq_bytes = static_cast<size_t>(d->n) * c->g_row_bytes;
+  const int64_t sg = d->n * c->g_groups;
+  c->sz_bytes = static_cast<size_t>(sg) * sizeof(float) * (zero_points ? 2 : 1);
+  CUDA_TRY_G(cudaMalloc(&c->g_w, c->wq_bytes));
+  CUDA_TRY_G(cudaMalloc(&c->g_scales, sg * sizeof(float)));
+  CUDA_TRY_G(cudaMemcpyAsync(c->g_w, qweight, c->wq_bytes, cudaMemcpyDeviceToDevice, stream));
+  to_f32_kernel<<<static_cast<unsigned>((sg + 255) / 256), 256, 0, stream>>>(scales, c->g_scales, sg, d->scale_dtype);
+  woq::count_launch();
+  if (zero_points) {
+    if (d->zp_dtype != WOQ_B200_T_F32 && d->zp_dtype != WOQ_B200_T_U8 && d->zp_dtype != WOQ_B200_T_S8)
+      return bail(fail(WOQ_B200_ERR_INVALID_ARG, "zero points must be fp32, u8 or s8 here"));
+    CUDA_TRY_G(cudaMalloc(&c->g_zps, sg * sizeof(float)));
+    to_f32_kernel<<<static_cast<unsigned>((sg + 255) / 256), 256, 0, stream>>>(zero_points, c->g_zps, sg, d->zp_dtype);
+    woq::count_launch();
+  }
+  if (bias) {
+    CUDA_TRY_G(cudaMalloc(&c->bias, static_cast<size_t>(d->n) * sizeof(float)));
+    to_f32_kernel<<<static_cast<unsigned>((d->n + 255) / 256), 256, 0, stream>>>(bias, c->bias, d->n, d->bias_dtype);
+    woq::count_launch();
+  }
+  CUDA_TRY_G(cudaGetLastError());
+  CUDA_TRY_G(cudaStreamSynchronize(stream));
+#undef CUDA_TRY_G
+  c->magic = kMagic;
+  *out = c;
+  return WOQ_B200_OK;
+}
+
+// compute dtype of a call on a general-route context
+int generic_compute_dtype(const woq_b200_ctx* c, int io_dtype) {
+  if (c->desc.lowp_mode == WOQ_B200_LOWP_BF16) return WOQ_B200_T_BF16;
+  if (c->desc.lowp_mode == WOQ_B200_LOWP_FP16) return WOQ_B200_T_F16;
+  return io_dtype;  // lowp NONE: the activation's dtype (WoqLinearKrnl.cpp:75-106)
+}
+
+void fill_generic(const woq_b200_ctx* c, woq::GenericParams* p) {
+  p->w = c->g_w;
+  p->scales = c->g_scales;
+  p->zps = c->g_zps;
+  p->bias = c->bias;
+  p->n = static_cast<int>(c->desc.n);
+  p->k = static_cast<int>(c->desc.k);
+  p->group = c->g_group;
+  p->groups = c->g_groups;
+  p->row_bytes = c->g_row_bytes;
+  p->weight_dtype = c->desc.weight_dtype;
+  p->default_zp = c->desc.weight_dtype == WOQ_B200_DTYPE_INT4 ? 8.f : 0.f;
+}
+
+}  // namespace
+
 extern "C" {
 
 int woq_b200_version(void) { return 100; }
@@ -257,10 +515,10 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
   *out = nullptr;
   if (d->n <= 0 || d->k <= 0 || d->n > (1 << 24) || d->k > (1 << 24))
     return fail(WOQ_B200_ERR_INVALID_ARG, "bad shape N=%lld K=%lld", (long long)d->n, (long long)d->k);
-  if (d->weight_dtype == WOQ_B200_DTYPE_NF4 || d->weight_dtype == WOQ_B200_DTYPE_FP8)
-    return fail(WOQ_B200_ERR_UNSUPPORTED, "NF4 / FP8 weights are not built yet");
-  if (d->weight_dtype != WOQ_B200_DTYPE_INT4 && d->weight_dtype != WOQ_B200_DTYPE_INT8)
+  if (d->weight_dtype < WOQ_B200_DTYPE_INT8 || d->weight_dtype > WOQ_B200_DTYPE_FP8)
     return fail(WOQ_B200_ERR_INVALID_ARG, "unknown weight dtype %d", d->weight_dtype);
+  if (d->lowp_mode < WOQ_B200_LOWP_NONE || d->lowp_mode > WOQ_B200_LOWP_INT8)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "unknown lowp_mode %d", d->lowp_mode);
   if (d->group_size == 0 || d->group_size < -1)
     return fail(WOQ_B200_ERR_INVALID_ARG, "group_size must be -1 or positive, got %d", d->group_size);
   if ((zero_points == nullptr) != (d->zp_dtype == WOQ_B200_T_NONE))
@@ -274,18 +532,10 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
       d->scale_dtype != WOQ_B200_T_BF16)
     return fail(WOQ_B200_ERR_INVALID_ARG, "scales must be fp32, fp16 or bf16");
 
+  if (wants_i8block(d)) return create_i8block(d, qweight, scales, zero_points, bias, stream, out);
+  if (wants_generic(d)) return create_generic(d, qweight, scales, zero_points, bias, stream, out);
   if (d->weight_dtype == WOQ_B200_DTYPE_INT8) return create_int8(d, qweight, scales, zero_points, bias, stream, out);
   // ---- INT4 ----
-  if (d->lowp_mode == WOQ_B200_LOWP_INT8)
-    return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 weights with INT8 compute are not built yet");
-  // This interface takes bf16 activations.  lowp NONE means "compute in the activation's
-  // dtype" in the reference (csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:75-106), which for bf16
-  // activations is the bf16 kernel, the same as lowp BF16.  FP16 compute would be narrowed
-  // silently by running it here, so it is refused.
-  if (d->lowp_mode == WOQ_B200_LOWP_FP16)
-    return fail(WOQ_B200_ERR_UNSUPPORTED, "lowp_mode FP16 (fp16 compute) is not built; BF16 and NONE with bf16 activations are");
-  if (d->lowp_mode != WOQ_B200_LOWP_BF16 && d->lowp_mode != WOQ_B200_LOWP_NONE)
-    return fail(WOQ_B200_ERR_INVALID_ARG, "unknown lowp_mode %d", d->lowp_mode);
   if (d->k % 64 != 0)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "INT4 path needs K %% 64 == 0 (K=%lld)", (long long)d->k);
   const int64_t g_eff = d->group_size > 0 ? d->group_size : d->k;
@@ -450,6 +700,9 @@ int woq_b200_ctx_destroy(woq_b200_ctx* c) {
   if (c->d_flag) cudaFree(c->d_flag);
   if (c->h_flag) cudaFreeHost(c->h_flag);
   if (c->flag_ready) cudaEventDestroy(c->flag_ready);
+  cudaFree(c->g_w);
+  cudaFree(c->g_scales);
+  cudaFree(c->g_zps);
   cudaFree(c->wq);
   cudaFree(c->sz);
   cudaFree(c->wq_tc);
@@ -477,6 +730,10 @@ int woq_b200_ctx_unpack(const woq_b200_ctx* c, void* qweight_plain, void* stream
   if (int rc = check_ctx(c)) return rc;
   if (!qweight_plain) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (c->is_generic || c->is_i8block) {
+    CUDA_TRY(cudaMemcpyAsync(qweight_plain, c->g_w, c->wq_bytes, cudaMemcpyDeviceToDevice, stream));
+    return WOQ_B200_OK;
+  }
   if (c->is_int8) {
     CUDA_TRY(woq::launch_unpack_int8(reinterpret_cast<const int8_t*>(c->wq), static_cast<int8_t*>(qweight_plain),
                                      (int)c->desc.n, (int)c->desc.k, c->gate_up, stream));
@@ -491,6 +748,8 @@ int woq_b200_ctx_unpack(const woq_b200_ctx* c, void* qweight_plain, void* stream
 
 size_t woq_b200_workspace_bytes(const woq_b200_ctx* c, int64_t m) {
   if (check_ctx(c)) return 0;
+  if (c->is_generic) return kWsHeaderBytes;  // the general route needs no scratch
+  if (c->is_i8block) return i8block_ws(c, m < 1 ? 1 : m).total;
   if (c->is_int8) return int8_ws_layout(c, m < 1 ? 1 : m).total;
   // header + one pair of partial tiles per CTA of the largest grid
   size_t decode = woq::decode_int4_partial_bytes(2 * c->num_sms);
@@ -714,10 +973,84 @@ static bool use_tc_path(const woq_b200_ctx* c, int64_t m) {
   return m > 16;
 }
 
+int woq_b200_linear_any(const woq_b200_ctx* c, const void* x, int32_t io_dtype, int64_t m, int64_t ldx,
+                        int32_t fusion, const void* const* others, int32_t n_others, void* y, int64_t ldy,
+                        void* workspace, size_t workspace_bytes, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!c->is_generic) {
+    if (io_dtype != WOQ_B200_T_BF16)
+      return fail(WOQ_B200_ERR_UNSUPPORTED, "this context was packed for bf16 activations; create it with "
+                  "WOQ_B200_LAYOUT_GENERIC to run it on fp32 or fp16 ones");
+    return woq_b200_linear(c, x, m, ldx, fusion, others, n_others, y, ldy, workspace, workspace_bytes, stream_);
+  }
+  if (io_dtype != WOQ_B200_T_BF16 && io_dtype != WOQ_B200_T_F16 && io_dtype != WOQ_B200_T_F32)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "activations must be bf16, fp16 or fp32");
+  if (m == 0) return WOQ_B200_OK;
+  if (!x || !y || m < 0) return fail(WOQ_B200_ERR_INVALID_ARG, "x and y must be non-null, M non-negative");
+  if (int rc = check_current_device(c)) return rc;
+  if (ldx < c->desc.k || ldy < c->desc.n) return fail(WOQ_B200_ERR_INVALID_ARG, "ldx / ldy smaller than K / N");
+  int need = 0;
+  switch (fusion) {
+    case WOQ_B200_FUSE_NONE: case WOQ_B200_FUSE_GELU_ERF: case WOQ_B200_FUSE_GELU_TANH:
+    case WOQ_B200_FUSE_RELU: case WOQ_B200_FUSE_SILU: need = 0; break;
+    case WOQ_B200_FUSE_ADD: case WOQ_B200_FUSE_MUL: need = 1; break;
+    case WOQ_B200_FUSE_ADD_ADD: need = 2; break;
+    case WOQ_B200_FUSE_SILU_MUL:
+      return fail(WOQ_B200_ERR_UNSUPPORTED, "the general route has no fused silu*mul (use silu, then mul)");
+    default: return fail(WOQ_B200_ERR_INVALID_ARG, "unexpected fusion type %#x", fusion);
+  }
+  if (n_others != need || (need > 0 && (!others || !others[0])) || (need > 1 && !others[1]))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "fusion %#x takes %d extra tensors, got %d", fusion, need, n_others);
+  woq::GenericParams p{};
+  fill_generic(c, &p);
+  p.x = x;
+  p.y = y;
+  p.other0 = need > 0 ? others[0] : nullptr;
+  p.other1 = need > 1 ? others[1] : nullptr;
+  p.ldx = ldx;
+  p.ldy = ldy;
+  p.m = static_cast<int>(m);
+  p.io_dtype = io_dtype;
+  p.compute_dtype = generic_compute_dtype(c, io_dtype);
+  p.fusion = fusion;
+  // tokens in slabs that keep the grid's y dimension in range
+  for (int64_t m0 = 0; m0 < m; m0 += 65535 * 8) {
+    woq::GenericParams q = p;
+    const size_t esz = io_dtype == WOQ_B200_T_F32 ? 4 : 2;
+    q.m = static_cast<int>(m - m0 < 65535 * 8 ? m - m0 : 65535 * 8);
+    q.x = static_cast<const uint8_t*>(x) + m0 * ldx * esz;
+    q.y = static_cast<uint8_t*>(y) + m0 * ldy * esz;
+    if (q.other0) q.other0 = static_cast<const uint8_t*>(p.other0) + m0 * ldy * esz;
+    if (q.other1) q.other1 = static_cast<const uint8_t*>(p.other1) + m0 * ldy * esz;
+    CUDA_TRY(woq::launch_generic(q, static_cast<cudaStream_t>(stream_)));
+    woq::count_launch();
+  }
+  (void)workspace;
+  (void)workspace_bytes;
+  return WOQ_B200_OK;
+}
+
+int woq_b200_dump_dequant_f32(const woq_b200_ctx* c, int32_t compute_dtype, float* w_f32, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!c->is_generic) return fail(WOQ_B200_ERR_UNSUPPORTED, "general-route contexts only (see woq_b200_dump_dequant)");
+  if (!w_f32) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
+  if (compute_dtype != WOQ_B200_T_BF16 && compute_dtype != WOQ_B200_T_F16 && compute_dtype != WOQ_B200_T_F32)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "compute dtype must be bf16, fp16 or fp32");
+  woq::GenericParams p{};
+  fill_generic(c, &p);
+  p.compute_dtype = compute_dtype;
+  CUDA_TRY(woq::launch_dump_generic(p, w_f32, static_cast<cudaStream_t>(stream_)));
+  woq::count_launch();
+  return WOQ_B200_OK;
+}
+
 int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
                     const void* const* others, int32_t n_others, void* y, int64_t ldy,
                     void* workspace, size_t workspace_bytes, void* stream_) {
   if (int rc = check_ctx(c)) return rc;
+  if (c->is_generic)
+    return woq_b200_linear_any(c, x, WOQ_B200_T_BF16, m, ldx, fusion, others, n_others, y, ldy, workspace,
+                               workspace_bytes, stream_);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (m == 0) return WOQ_B200_OK;
   if (!x || !y || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "x, y and workspace must be non-null");
@@ -745,6 +1078,9 @@ int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
   if ((need > 0 && !o0) || (need > 1 && !o1)) return fail(WOQ_B200_ERR_INVALID_ARG, "null extra tensor");
   const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? c->desc.n / 2 : c->desc.n;
   if (ldy < n_out) return fail(WOQ_B200_ERR_INVALID_ARG, "ldy smaller than the output width");
+  if (c->is_i8block)
+    return run_i8block(c, x, m, ldx, fusion, o0, o1, y, ldy, nullptr, nullptr, nullptr, nullptr, workspace,
+                       workspace_bytes, stream);
   if (c->is_int8)
     return run_int8(c, x, m, ldx, fusion, o0, o1, y, ldy, nullptr, nullptr, nullptr, workspace,
                     workspace_bytes, stream);
@@ -862,8 +1198,8 @@ static int comm_params(const woq_b200_ctx* c, const woq_b200_comm* cm, int64_t m
   if (int rc = check_ctx(c)) return rc;
   if (int rc = check_comm(cm)) return rc;
   if (!cm->connected && cm->world > 1) return fail(WOQ_B200_ERR_INVALID_ARG, "comm is not connected");
-  if (c->is_int8 || m > 16 || m < 1)
-    return fail(WOQ_B200_ERR_UNSUPPORTED, "the fused exchange covers INT4 weights and 1..16 tokens");
+  if (c->is_int8 || c->is_generic || c->is_i8block || m > 16 || m < 1)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the fused exchange covers INT4 weights with bf16 compute and 1..16 tokens");
   if (!c->wq) return fail(WOQ_B200_ERR_UNSUPPORTED, "context was packed without the streaming layout");
   if (c->tiles > woq::kCommMaxTiles) return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the stamp table");
   for (int q = 0; q < woq::kCommMaxRanks; ++q) cp->peer[q] = cm->peer[q];
@@ -985,7 +1321,8 @@ int woq_b200_linear_scatter(const woq_b200_ctx* c, const void* x, int64_t m, int
   if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
     return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
   if (ld_out < c->desc.n) return fail(WOQ_B200_ERR_INVALID_ARG, "ld_out smaller than N");
-  if (c->is_int8) return fail(WOQ_B200_ERR_UNSUPPORTED, "scatter epilogue is built for INT4 contexts");
+  if (c->is_int8 || c->is_generic || c->is_i8block)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "scatter epilogue is built for INT4 bf16 contexts");
   if (use_tc_path(c, m))
     return run_tc(c, x, m, ldx, WOQ_B200_FUSE_SCALED_SCATTER_ADD, nullptr, nullptr, row_idx, row_weight,
                   out, ld_out, workspace, workspace_bytes, stream);
@@ -1042,8 +1379,10 @@ int woq_b200_dump_dequant(const woq_b200_ctx* c, void* w_bf16, void* stream_) {
   if (int rc = check_ctx(c)) return rc;
   if (!w_bf16) return fail(WOQ_B200_ERR_INVALID_ARG, "output is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (c->is_int8)
+  if (c->is_int8 || c->is_i8block)
     return fail(WOQ_B200_ERR_UNSUPPORTED, "the INT8 compute path never dequantises its weights");
+  if (c->is_generic)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "general-route context: use woq_b200_dump_dequant_f32");
   if (c->wq_tc) {
     // the routine the tensor-core kernel uses for its tiles
     CUDA_TRY(woq::launch_dump_dequant_int4_tc(c->wq_tc, c->sz_tc, static_cast<__nv_bfloat16*>(w_bf16),
@@ -1070,6 +1409,31 @@ int woq_b200_int8_internals(const woq_b200_ctx* c, const void* x, int64_t m, int
                   workspace, workspace_bytes, static_cast<cudaStream_t>(stream_));
 }
 
+int woq_b200_int8_block_internals(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, uint8_t* qa,
+                                  float* sa, int32_t* zpa, int32_t* acc, void* workspace, size_t workspace_bytes,
+                                  void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (!c->is_i8block) return fail(WOQ_B200_ERR_INVALID_ARG, "context does not use INT8 compute with K blocks");
+  if (m <= 0 || !x || !workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "bad arguments");
+  if (ldx < c->desc.k || (ldx % 8) != 0 || !aligned16(x))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x must be 16-byte aligned with ldx >= K and ldx %% 8 == 0");
+  return run_i8block(c, x, m, ldx, WOQ_B200_FUSE_NONE, nullptr, nullptr, nullptr, c->desc.n, qa, sa, zpa, acc,
+                     workspace, workspace_bytes, static_cast<cudaStream_t>(stream_));
+}
+
+int woq_b200_ctx_route(const woq_b200_ctx* c) {
+  if (check_ctx(c)) return -1;
+  if (c->is_i8block) return WOQ_B200_ROUTE_INT8_BLOCK;
+  if (c->is_generic) return WOQ_B200_ROUTE_GENERAL;
+  if (c->is_int8) return WOQ_B200_ROUTE_INT8;
+  return WOQ_B200_ROUTE_INT4_BF16;
+}
+
+int woq_b200_int8_block_size(const woq_b200_ctx* c) {
+  if (check_ctx(c) || !c->is_i8block) return 0;
+  return c->kb;
+}
+
 int woq_b200_int8_zero_points(const woq_b200_ctx* c, int64_t m, int32_t* zp, const void* workspace,
                               size_t workspace_bytes, void* stream_) {
   if (int rc = check_ctx(c)) return rc;
@@ -1091,7 +1455,7 @@ int woq_b200_int8_zero_points(const woq_b200_ctx* c, int64_t m, int32_t* zp, con
 
 int woq_b200_decode_plan(const woq_b200_ctx* c, int64_t m, int32_t* out) {
   if (int rc = check_ctx(c)) return rc;
-  if (!out || m < 1 || m > 16 || c->is_int8 || !c->wq)
+  if (!out || m < 1 || m > 16 || c->is_int8 || c->is_generic || c->is_i8block || !c->wq)
     return fail(WOQ_B200_ERR_INVALID_ARG, "decode plan: INT4 context with the streaming layout, 1..16 tokens");
   const woq::DecodePlan plan = woq::decode_int4_plan((int)m, c->tiles, c->kb_per_tile, c->kb_per_group, c->num_sms);
   out[0] = plan.grid;

@@ -165,6 +165,50 @@ cudaError_t launch_weight_row_sum(const int8_t* plain, int n, int k, int32_t* co
 size_t int8_partial_bytes(int grid, int n_tok);
 cudaError_t launch_int8_tc(I8Params p, const CUtensorMap& qamap, int grid, cudaStream_t stream);
 
+// ---- INT8 compute with K-block scaling (woq_int8_block.cu) --------------------------------
+struct I8BlockParams {
+  const uint8_t* w;      // plain [n][k/2] nibbles (w4) or [n][k] s8
+  const float* sw;       // [n][groups] weight scales
+  const float* zpw;      // [n][groups] weight zero points or null (default_zp)
+  const int32_t* comp;   // [n][kc] sums of (qw - zp_w) per K block (asymmetric activations)
+  const uint8_t* qa;     // [m][k] activation codes (w4: even / odd interleaved inside every 8)
+  const float* sa;       // [m][kc]
+  const int32_t* zpa;    // [m][kc]
+  const int32_t* sumqa;  // [m][kc] sums of the activation codes per K block
+  const float* bias;
+  __nv_bfloat16* y;      // may be null when only the accumulators are wanted
+  const __nv_bfloat16* other0;
+  const __nv_bfloat16* other1;
+  int32_t* acc_out;      // optional [kc][m][n] block accumulators after the compensation
+  int64_t ldy;
+  int m, n, k, kb, kc, group, groups, fusion, w4, asym;
+  float default_zp;
+};
+cudaError_t launch_act_block_quant(const __nv_bfloat16* x, int64_t ldx, int m, int k, int kb, int act_mode,
+                                   int interleave, uint8_t* qa, float* sa, int32_t* zpa, int32_t* sumqa,
+                                   float* range, float* folded, cudaStream_t stream);
+cudaError_t launch_weight_block_sum(const uint8_t* w, const float* zpw, int n, int k, int kb, int group, int groups,
+                                    float default_zp, int w4, int32_t* comp, cudaStream_t stream);
+cudaError_t launch_i8_block(const I8BlockParams& p, cudaStream_t stream);
+
+// ---- general route: any weight dtype, fp32 / fp16 / bf16 compute, plain layout -----------
+struct GenericParams {
+  const uint8_t* w;     // plain [n][row_bytes]: nibbles (even k low) or bytes
+  const float* scales;  // [n][groups] fp32 as given (rounded to the compute dtype in the kernel)
+  const float* zps;     // [n][groups] or null (then default_zp)
+  const float* bias;    // [n] or null
+  const void* x;        // [m][ldx] of io_dtype
+  void* y;              // [m][ldy] of io_dtype
+  const void* other0;
+  const void* other1;
+  int64_t ldx, ldy;
+  int m, n, k, group, groups, row_bytes;
+  int weight_dtype, compute_dtype, io_dtype, fusion;  // WOQ_B200_DTYPE_* / WOQ_B200_T_*
+  float default_zp;
+};
+cudaError_t launch_generic(const GenericParams& p, cudaStream_t stream);
+cudaError_t launch_dump_generic(const GenericParams& p, float* out, cudaStream_t stream);
+
 // ---- pack / unpack / dump ------------------------------------------------------------
 struct PackInt4Args {
   const uint8_t* plain;  // [n][ceil(k/2)]

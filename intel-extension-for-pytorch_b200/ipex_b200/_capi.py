@@ -18,11 +18,14 @@ LIB_PATH = os.path.join(_HERE, "libwoq_b200.so")
 DTYPE_INT8, DTYPE_INT4, DTYPE_NF4, DTYPE_FP8 = 1, 2, 3, 4
 LOWP_NONE, LOWP_FP16, LOWP_BF16, LOWP_INT8 = 0, 1, 2, 3
 ACT_NONE, ACT_PER_TENSOR, ACT_PER_M, ACT_PER_TENSOR_SYM, ACT_PER_M_SYM = -1, 0, 2, 4, 6
+ACT_PER_K_BLOCK, ACT_PER_M_K_BLOCK, ACT_PER_K_BLOCK_SYM, ACT_PER_M_K_BLOCK_SYM = 1, 3, 5, 7
+ROUTE_INT4_BF16, ROUTE_INT8, ROUTE_GENERAL, ROUTE_INT8_BLOCK = 0, 1, 2, 3
 FMT_PLAIN, FMT_GPTQ, FMT_AWQ = 0, 1, 2
 FUSE_NONE, FUSE_GELU_ERF, FUSE_GELU_TANH, FUSE_RELU, FUSE_SILU = 0, 1, 2, 3, 4
 FUSE_ADD, FUSE_ADD_ADD, FUSE_MUL, FUSE_SILU_MUL = 0x10, 0x20, 0x30, 0x100
 T_NONE, T_F32, T_F16, T_BF16, T_U8, T_S8, T_I32 = 0, 1, 2, 3, 4, 5, 6
 LAYOUT_GATE_UP, LAYOUT_STREAM_ONLY, LAYOUT_TC_ONLY, LAYOUT_SCALES_NK, LAYOUT_DEFER_CHECK = 1, 2, 4, 8, 16
+LAYOUT_GENERIC = 32
 HINT_AUTO, HINT_TENSOR_CORE, HINT_STREAM, HINT_STREAM_FAST = 0, 1, 2, 3
 OPT_DECODE_SPLIT = 1
 SPLIT_AUTO, SPLIT_STREAM_K, SPLIT_CLUSTER = 0, 1, 2
@@ -40,6 +43,8 @@ EXPORTS = [
     "woq_b200_workspace_bytes",
     "woq_b200_workspace_header_bytes",
     "woq_b200_linear",
+    "woq_b200_linear_any",
+    "woq_b200_dump_dequant_f32",
     "woq_b200_linear_scatter",
     "woq_b200_linear_static_scratch",
     "woq_b200_static_scratch_status",
@@ -47,6 +52,9 @@ EXPORTS = [
     "woq_b200_moe_expert",
     "woq_b200_dump_dequant",
     "woq_b200_int8_internals",
+    "woq_b200_int8_block_internals",
+    "woq_b200_int8_block_size",
+    "woq_b200_ctx_route",
     "woq_b200_int8_zero_points",
     "woq_b200_workspace_status",
     "woq_b200_decode_plan",
@@ -114,6 +122,8 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_workspace_bytes.restype = sz
     L.woq_b200_workspace_header_bytes.restype = sz
     L.woq_b200_linear.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
+    L.woq_b200_linear_any.argtypes = [vp, vp, i32, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
+    L.woq_b200_dump_dequant_f32.argtypes = [vp, i32, vp, vp]
     L.woq_b200_linear_static_scratch.argtypes = [vp, vp, i64, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp]
     L.woq_b200_static_scratch_status.argtypes = [vp]
     L.woq_b200_linear_scatter.argtypes = [vp, vp, i64, i64, vp, vp, vp, i64, vp, sz, vp]
@@ -122,6 +132,9 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_moe_expert.argtypes = [vp, vp, vp, i64, vp, vp, i64, vp, i64, vp, sz, vp]
     L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
+    L.woq_b200_int8_block_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, vp, sz, vp]
+    L.woq_b200_int8_block_size.argtypes = [vp]
+    L.woq_b200_ctx_route.argtypes = [vp]
     L.woq_b200_int8_zero_points.argtypes = [vp, i64, vp, vp, sz, vp]
     L.woq_b200_workspace_status.argtypes = [vp, vp]
     L.woq_b200_decode_plan.argtypes = [vp, i64, ctypes.POINTER(i32)]
@@ -381,6 +394,34 @@ class WoqContext:
             )
         return out.reshape(*x.shape[:-1], n_out)
 
+    def linear_any(self, x: torch.Tensor, fusion: int = FUSE_NONE, others: Sequence[torch.Tensor] = (),
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """woq_b200_linear_any: activations, extra tensors and output of x's dtype (bf16, fp16
+        or fp32); the compute dtype follows the context's lowp mode."""
+        if x.dtype not in (torch.bfloat16, torch.float16, torch.float32) or not x.is_cuda:
+            raise ValueError("x must be a bf16, fp16 or fp32 CUDA tensor")
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        m = x2.shape[0]
+        if out is None:
+            out = torch.empty((m, self.n), dtype=x.dtype, device=x.device)
+        oth = [o.to(x.dtype) for o in _others(others, m, self.n, out)]
+        arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
+        ws = self.workspace(m)
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_linear_any(
+                self._h, x2.data_ptr(), _TORCH_T[x.dtype], m, x2.stride(0), fusion, arr, len(oth),
+                out.data_ptr(), out.stride(0), ws.buf.data_ptr(), ws.nbytes, _stream()))
+        return out.reshape(*x.shape[:-1], self.n)
+
+    def dump_dequant_f32(self, compute_dtype: torch.dtype) -> torch.Tensor:
+        """General-route contexts: the values the kernel multiplies by, as fp32 [n, k]."""
+        out = torch.empty((self.n, self.k), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_dump_dequant_f32(self._h, _TORCH_T[compute_dtype], out.data_ptr(), _stream()))
+        return out
+
     def linear_allreduce(self, comm: "Comm", x, fusion: int = FUSE_NONE, others: Sequence[torch.Tensor] = (),
                          bias: Optional[torch.Tensor] = None, out=None, workspace=None) -> torch.Tensor:
         """Row-parallel linear (this rank's K shard) fused with the all-reduce; 1..16 tokens."""
@@ -453,10 +494,11 @@ class WoqContext:
         return out
 
     def unpack(self) -> torch.Tensor:
-        if self.weight_dtype == DTYPE_INT4:
+        if self.weight_dtype in (DTYPE_INT4, DTYPE_NF4):
             out = torch.empty((self.n, (self.k + 1) // 2), dtype=torch.uint8, device=self.device)
         else:
-            out = torch.empty((self.n, self.k), dtype=torch.int8, device=self.device)
+            out = torch.empty((self.n, self.k), dtype=torch.uint8 if self.weight_dtype == DTYPE_FP8 else torch.int8,
+                              device=self.device)
         with torch.cuda.device(self.device):
             _check(lib().woq_b200_ctx_unpack(self._h, out.data_ptr(), _stream()))
         return out
@@ -466,6 +508,27 @@ class WoqContext:
         with torch.cuda.device(self.device):
             _check(lib().woq_b200_dump_dequant(self._h, out.data_ptr(), _stream()))
         return out
+
+    def route(self) -> int:
+        return lib().woq_b200_ctx_route(self._h)
+
+    def int8_block_internals(self, x: torch.Tensor):
+        """K-block INT8 route: codes [m, k] (u8 bit patterns), scales and zero points [m, k / block],
+        block accumulators [k / block, m, n] (woq_b200_int8_block_internals)."""
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        m = x2.shape[0]
+        kb = lib().woq_b200_int8_block_size(self._h)
+        kc = self.k // kb
+        qa = torch.empty((m, self.k), dtype=torch.uint8, device=self.device)
+        sa = torch.empty((m, kc), dtype=torch.float32, device=self.device)
+        zpa = torch.empty((m, kc), dtype=torch.int32, device=self.device)
+        acc = torch.empty((kc, m, self.n), dtype=torch.int32, device=self.device)
+        ws = self.workspace(m)
+        with torch.cuda.device(self.device):
+            _check(lib().woq_b200_int8_block_internals(
+                self._h, x2.data_ptr(), m, x2.stride(0), qa.data_ptr(), sa.data_ptr(), zpa.data_ptr(),
+                acc.data_ptr(), ws.buf.data_ptr(), ws.nbytes, _stream()))
+        return qa, sa, zpa, acc
 
     def int8_internals(self, x: torch.Tensor):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()

@@ -7,6 +7,8 @@ scale = (max - min) / 15 (INT4 asym), max|w| / 7 (INT4 sym), max|w| / 127 (INT8 
 (max - min) / 255 (INT8 asym, zero point shifted by -128), clamped below by fp32 eps;
 values are multiplied by the reciprocal scale, rounded half to even, shifted by the zero
 point (8 for symmetric INT4) and clamped; INT4 codes are packed two per byte, even k low.
+NF4 (symmetric only): scale = max|w|, code = the number of the last threshold of the
+reference's NF4_QUANT_TABLE below w / scale (:789-846).
 Written group-parallel so that it runs at memory speed on a GPU.
 """
 from typing import Optional, Tuple
@@ -14,6 +16,21 @@ from typing import Optional, Tuple
 import torch
 
 from ._qconfig import WoqWeightDtype
+
+
+# thresholds / values of the 16 NF4 codes (reference: quantization/_quantize_utils.py:789-826)
+NF4_QUANT_TABLE = [
+    -1.0 - 1e-2, -0.8480964004993439, -0.6106329262256622, -0.4599952697753906,
+    -0.33967943489551544, -0.23460740596055984, -0.13791173323988914, -0.045525018125772476,
+    0.03979014977812767, 0.1202552504837513, 0.2035212516784668, 0.2920137718319893,
+    0.3893125355243683, 0.5016634166240692, 0.6427869200706482, 0.8614784181118011,
+]
+NF4_DEQUANT_TABLE = [
+    -1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453,
+    -0.28444138169288635, -0.18477343022823334, -0.09105003625154495, 0.0,
+    0.07958029955625534, 0.16093020141124725, 0.24611230194568634, 0.33791524171829224,
+    0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0,
+]
 
 
 def is_4bit(dtype) -> bool:
@@ -36,8 +53,11 @@ def _qparams(mins, maxs, dtype, sym_quant):
         else:
             scales = ((maxs - mins) / 15).clamp_min(eps)
             zps = -torch.round(mins / scales)
+    elif dtype == WoqWeightDtype.NF4:
+        assert sym_quant, "NF4 must be symmetric quant"
+        scales = torch.maximum(maxs.abs(), mins.abs()).clamp_min(eps)
     else:
-        raise NotImplementedError("NF4 / FP8 weights are not supported by this build")
+        raise NotImplementedError("FP8 weights come from checkpoints, there is no FP8 quantiser")
     return scales, zps
 
 
@@ -49,6 +69,12 @@ def _pack_int4(q: torch.Tensor) -> torch.Tensor:
 
 def _quantize_groups(t, dtype, scales, zps, sym_quant):
     inv = 1 / scales.unsqueeze(-1)
+    if dtype == WoqWeightDtype.NF4:
+        # the last threshold below the value: thresholds ascend, so count them
+        v = t * inv
+        table = torch.tensor(NF4_QUANT_TABLE, dtype=torch.float32, device=t.device)
+        code = (v.unsqueeze(-1) > table).sum(dim=-1) - 1
+        return code.clamp_(0, 15)
     r = torch.round(t * inv)
     if dtype == WoqWeightDtype.INT8:
         if zps is not None:
@@ -108,7 +134,11 @@ def _unpack_int4(qt: torch.Tensor) -> torch.Tensor:
 
 def dequantize_per_channel(qt, scales, zps: Optional[torch.Tensor], dtype, weight_shape=None):
     scales = scales.reshape(-1)
-    if dtype == WoqWeightDtype.INT4:
+    if dtype == WoqWeightDtype.NF4:
+        table = torch.tensor(NF4_DEQUANT_TABLE, dtype=torch.float32, device=qt.device)
+        q = table[_unpack_int4(qt).long()]
+        z = torch.zeros_like(scales)
+    elif dtype == WoqWeightDtype.INT4:
         q = _unpack_int4(qt).float()
         z = zps.reshape(-1) if zps is not None else torch.full_like(scales, 8.0)
     else:
@@ -122,7 +152,10 @@ def dequantize_per_channel(qt, scales, zps: Optional[torch.Tensor], dtype, weigh
 
 def dequantize_per_block(qt, scales, zps: Optional[torch.Tensor], dtype, group_size,
                          weight_shape=None):
-    q = _unpack_int4(qt).float() if dtype == WoqWeightDtype.INT4 else qt.float()
+    if dtype == WoqWeightDtype.NF4:
+        q = torch.tensor(NF4_DEQUANT_TABLE, dtype=torch.float32, device=qt.device)[_unpack_int4(qt).long()]
+    else:
+        q = _unpack_int4(qt).float() if dtype == WoqWeightDtype.INT4 else qt.float()
     N, K = q.shape
     if scales.dim() > 2:
         scales = scales.squeeze()

@@ -102,9 +102,44 @@ def _qparams(mins, maxs, dtype: int, sym: bool):
             scales = (maxs - mins) / np.float32(15)
             scales = np.maximum(scales, F32_EPS)
             zps = -_round_half_even(mins / scales)
+    elif dtype == WOQ_DTYPE_NF4:
+        if not sym:
+            raise ValueError("NF4 must be symmetric quant")
+        scales = np.maximum(np.maximum(np.abs(maxs), np.abs(mins)), F32_EPS)
     else:
-        raise NotImplementedError("oracle covers INT8 and INT4 weights")
+        raise NotImplementedError("FP8 weights come from checkpoints: no quantiser")
     return scales.astype(np.float32), (None if zps is None else zps.astype(np.float32))
+
+
+# NF4 thresholds and values (quantization/_quantize_utils.py:789-826, woq_utils.h:15-51)
+NF4_QUANT_TABLE = np.array([
+    -1.0 - 1e-2, -0.8480964004993439, -0.6106329262256622, -0.4599952697753906,
+    -0.33967943489551544, -0.23460740596055984, -0.13791173323988914, -0.045525018125772476,
+    0.03979014977812767, 0.1202552504837513, 0.2035212516784668, 0.2920137718319893,
+    0.3893125355243683, 0.5016634166240692, 0.6427869200706482, 0.8614784181118011], dtype=np.float32)
+NF4_DEQUANT_TABLE = np.array([
+    -1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453,
+    -0.28444138169288635, -0.18477343022823334, -0.09105003625154495, 0.0,
+    0.07958029955625534, 0.16093020141124725, 0.24611230194568634, 0.33791524171829224,
+    0.44070982933044434, 0.5626170039176941, 0.7229568362236023, 1.0], dtype=np.float32)
+
+
+def map_float_to_nf4(t: np.ndarray) -> np.ndarray:
+    """out[t > NF4_QUANT_TABLE[i]] = i for ascending i (quantization/_quantize_utils.py:831-837)."""
+    out = np.zeros(t.shape, dtype=np.uint8)
+    for i, thr in enumerate(NF4_QUANT_TABLE):
+        out[t > thr] = i
+    return out
+
+
+def fp8_e4m3_to_f32(codes: np.ndarray) -> np.ndarray:
+    """The reference's byte -> fp32 conversion for FP8 weights (csrc/cpu/aten/utils/woq.h:465-483):
+    exponent rebias by 120, three mantissa bits, zero when the low seven bits are zero; no
+    special case for NaN or subnormal codes."""
+    x = np.ascontiguousarray(codes).view(np.uint8).astype(np.uint32)
+    bits = ((x & 7) << 20) | ((((x >> 3) & 15) + 120) << 23)
+    bits = np.where((x & 127) == 0, 0, bits) | ((x & 128) << 24)
+    return bits.astype(np.uint32).view(np.float32)
 
 
 def pack_nibbles(q: np.ndarray) -> np.ndarray:
@@ -150,6 +185,9 @@ def quantize_per_block(
         s, z = _qparams(mins, maxs, dtype, sym)
         scales[:, g] = s
         inv = (np.float32(1) / s)[:, None]
+        if dtype == WOQ_DTYPE_NF4:
+            q[:, g * G : min(K, (g + 1) * G)] = map_float_to_nf4((blk * inv).astype(np.float32))
+            continue
         r = _round_half_even(blk * inv)
         if dtype == WOQ_DTYPE_INT8:
             r = r + (z[:, None] if z is not None else np.float32(0))
@@ -160,7 +198,7 @@ def quantize_per_block(
         if z is not None:
             zps[:, g] = z
         q[:, g * G : min(K, (g + 1) * G)] = r
-    if dtype == WOQ_DTYPE_INT4:
+    if dtype in (WOQ_DTYPE_INT4, WOQ_DTYPE_NF4):
         return pack_nibbles(q.astype(np.uint8)), scales, zps
     return q.astype(np.int8), scales, zps
 
@@ -235,6 +273,10 @@ def weight_integers(qweight: np.ndarray, dtype: int, K: int) -> np.ndarray:
         return unpack_nibbles(qweight)[:, :K].astype(np.float32)
     if dtype == WOQ_DTYPE_INT8:
         return np.ascontiguousarray(qweight).view(np.int8)[:, :K].astype(np.float32)
+    if dtype == WOQ_DTYPE_NF4:
+        return NF4_DEQUANT_TABLE[unpack_nibbles(qweight)[:, :K]]
+    if dtype == WOQ_DTYPE_FP8:
+        return fp8_e4m3_to_f32(qweight)[:, :K]
     raise NotImplementedError
 
 
@@ -279,6 +321,62 @@ def dequantize_weight(
     w = (q - z_full) * s_full
     w = w.astype(np.float32)
     return rne_bf16(w) if round_output else w
+
+
+def _round_to(v: np.ndarray, compute: str) -> np.ndarray:
+    v = np.asarray(v, dtype=np.float32)
+    if compute == "bf16":
+        return rne_bf16(v)
+    if compute == "fp16":
+        return v.astype(np.float16).astype(np.float32)
+    if compute == "fp32":
+        return v
+    raise ValueError(compute)
+
+
+def woq_linear_any(x, qweight, scales, zps, bias, dtype: int, group_size: int, compute: str, io: str,
+                   fusion: int = FUSE_NONE, others: Sequence[np.ndarray] = ()) -> np.ndarray:
+    """The floating-point routes of qlinear_woq_affine for every weight dtype
+    (csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:75-165): compute in `compute` ("bf16", "fp16" or
+    "fp32"), activations / outputs / extra tensors of dtype `io`.
+
+    W = round((code - zp) * round(scale)), x rounded to the compute dtype, fp32 accumulation over
+    the whole K, + bias, rounded to `io`, post-op on `io` data (one rounding per operation).
+    For compute == io == "bf16" and INT4 / INT8 weights this is woq_linear_bf16."""
+    K = x.shape[1]
+    G = K if group_size <= 0 else group_size
+    q = weight_integers(qweight, dtype, K)
+    s_full = _expand_groups(_round_to(scales, compute), K, G)
+    if zps is None:
+        z_full = np.float32(8.0 if dtype == WOQ_DTYPE_INT4 else 0.0)
+    else:
+        z_full = _expand_groups(zps, K, G)
+    w = _round_to(((q - z_full) * s_full).astype(np.float32), compute)
+    acc = _round_to(x, compute) @ w.T
+    if bias is not None:
+        acc = acc + np.asarray(bias, dtype=np.float32)[None, :]
+    y = _round_to(acc, io)
+    r = lambda v: _round_to(v, io)  # noqa: E731
+    if fusion == FUSE_NONE:
+        return y
+    if fusion == FUSE_GELU_ERF:
+        y64 = y.astype(np.float64)
+        return r((0.5 * y64 * (1.0 + _erf(y64 / math.sqrt(2.0)))).astype(np.float32))
+    if fusion == FUSE_GELU_TANH:
+        y64 = y.astype(np.float64)
+        return r((0.5 * y64 * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (y64 + 0.044715 * y64**3)))).astype(np.float32))
+    if fusion == FUSE_RELU:
+        return np.maximum(y, np.float32(0))
+    if fusion == FUSE_SILU:
+        sig = r((1.0 / (1.0 + np.exp(-y.astype(np.float64)))).astype(np.float32))
+        return r(y * sig)
+    if fusion in (FUSE_ADD, FUSE_ADD_ADD):
+        for t in others[: 1 if fusion == FUSE_ADD else 2]:
+            y = r(y + np.asarray(t, dtype=np.float32).reshape(y.shape))
+        return y
+    if fusion == FUSE_MUL:
+        return r(y * np.asarray(others[0], dtype=np.float32).reshape(y.shape))
+    raise ValueError(f"unexpected fusion type {fusion:#x}")
 
 
 # ---------------------------------------------------------------------------------------
@@ -511,6 +609,106 @@ def woq_linear_int8(
         if zpa is not None:
             return y, int8_accumulators(qa, qw), qa, sa, zpa
         return y, int8_accumulators(qa, qw), qa, sa
+    return y
+
+
+# ---------------------------------------------------------------------------------------
+# a8 / a9 in general: every activation quantisation mode, INT4 or INT8 weights, K blocks
+# ---------------------------------------------------------------------------------------
+def int8_block_k(K: int, group_size: int) -> int:
+    """get_block_k for lowp INT8: min(group, 128), halved until it divides K
+    (csrc/cpu/aten/Linear.cpp:362-376)."""
+    kb = min(group_size, 128) if group_size > 0 else 128
+    while K % kb:
+        kb //= 2
+    return kb
+
+
+def dynamic_quant_blocks(x: np.ndarray, act_mode: int, block_k: int):
+    """Activation codes [M, K] and, per token and K block, scales [M, Kc] and zero points
+    [M, Kc] (None when symmetric) for all eight modes of the reference
+    (csrc/cpu/aten/utils/woq_defines.h:11-19, woq_dynamic_quant.h:1526-1750):
+      0 / 4  one range for the whole tensor          1 / 5  one per K block, shared by all tokens
+      2 / 6  one per token                            3 / 7  one per token and K block
+    (+4: symmetric int8 codes; else uint8 codes with a zero point).  Every mode is the per-token
+    rule of dynamic_quant_per_token applied to the elements that share a range."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    M, K = x.shape
+    Kc = (K + block_k - 1) // block_k
+    sym = act_mode >= 4
+    base = act_mode & 3
+    q = np.empty((M, K), dtype=np.int8 if sym else np.uint8)
+    sa = np.empty((M, Kc), dtype=np.float32)
+    zp = None if sym else np.empty((M, Kc), dtype=np.int32)
+    if base in (0, 2):
+        qq, s, z = dynamic_quant(x, act_mode)
+        q[:] = qq
+        sa[:] = s[:, None]
+        if zp is not None:
+            zp[:] = z[:, None]
+        return q, sa, zp
+    for c in range(Kc):
+        blk = x[:, c * block_k : (c + 1) * block_k]
+        if base == 1:   # all tokens share the block's range
+            qq, s, z = dynamic_quant_per_token(blk.reshape(1, -1), sym=sym)
+            q[:, c * block_k : (c + 1) * block_k] = qq.reshape(blk.shape)
+            sa[:, c] = s[0]
+            if zp is not None:
+                zp[:, c] = z[0]
+        else:
+            qq, s, z = dynamic_quant_per_token(blk, sym=sym)
+            q[:, c * block_k : (c + 1) * block_k] = qq
+            sa[:, c] = s
+            if zp is not None:
+                zp[:, c] = z
+    return q, sa, zp
+
+
+def woq_linear_int8_blocks(x, qweight, wdtype: int, scales, zps_w, bias, group_size: int, act_mode: int,
+                           fusion: int = FUSE_NONE, others: Sequence[np.ndarray] = (), return_blocks: bool = False):
+    """WoqLowpMode.INT8 for INT4 or INT8 weights with per-channel or per-group scales and any
+    activation quantisation mode.  Per K block (int8_block_k):
+        qC[m,n] = sum_k qa[m,k] * (qw[n,k] - zp_w[n,g])                      int32, exact
+        qC     -= comp[n] * zp_a[m,block],  comp[n] = sum_k (qw[n,k] - zp_w[n,g])   (asymmetric activations)
+        C[m,n] += (float(qC) * scale_a[m,block]) * scale_w[n,g]              fp32, blocks in k order
+    after the fp32 bias; then fp32 -> bf16 and the post-op
+    (csrc/cpu/aten/utils/woq.h:962-1126 for 4-bit weights, :2231-2354 for INT8 weights).
+    With return_blocks also the int32 block accumulators [Kc, M, N] (after the compensation)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    M, K = x.shape
+    G = K if group_size <= 0 else group_size
+    kb = int8_block_k(K, group_size)
+    qw = weight_integers(qweight, wdtype, K).astype(np.float64)
+    N = qw.shape[0]
+    if zps_w is None:
+        zw = np.full((N, (K + G - 1) // G), 8.0 if wdtype == WOQ_DTYPE_INT4 else 0.0)
+    else:
+        zw = np.asarray(zps_w, dtype=np.float64).reshape(N, -1)
+    sw = np.asarray(scales, dtype=np.float32).reshape(N, -1)
+    qa, sa, zpa = dynamic_quant_blocks(x, act_mode, kb)
+    qa64 = qa.astype(np.float64)
+    C = np.zeros((M, N), dtype=np.float32)
+    if bias is not None:
+        C += np.asarray(bias, dtype=np.float32)[None, :]
+    blocks = []
+    for c, k0 in enumerate(range(0, K, kb)):
+        g = k0 // G
+        wb = qw[:, k0 : k0 + kb] - zw[:, g][:, None]
+        qc = qa64[:, k0 : k0 + kb] @ wb.T
+        if zpa is not None:
+            qc = qc - zpa[:, c].astype(np.float64)[:, None] * wb.sum(axis=1)[None, :]
+        if return_blocks:
+            blocks.append(np.rint(qc).astype(np.int64).astype(np.int32))
+        qc = qc.astype(np.float32)
+        C = (C + ((qc * sa[:, c][:, None]).astype(np.float32) * sw[:, g][None, :]).astype(np.float32)).astype(np.float32)
+    y = rne_bf16(C)
+    if fusion == FUSE_SILU_MUL:
+        half = y.shape[1] // 2
+        y = rne_bf16(y[:, half:] * _silu_bf16(y[:, :half]))
+    else:
+        y = apply_post_op(y, fusion, others)
+    if return_blocks:
+        return y, np.stack(blocks), qa, sa, zpa
     return y
 
 

@@ -13,14 +13,15 @@ pieces that pin the WOQ linear path are plain PyTorch and are executed here as t
     (intel_extension_for_pytorch/quantization/_qconfig.py);
   * dequantize_awq and its helper from tests/cpu/test_ipex_llm_quantization.py, applied to
     the known-answer tensors tests/cpu/data/awq/*.pt;
-  * the activation fake-quantiser _fakequant_by_group_sym from
-    tests/cpu/test_quantization_default_recipe.py.
+  * the activation fake-quantisers _fakequant_by_group / _fakequant_by_group_sym from
+    tests/cpu/test_quantization_default_recipe.py (all eight activation quantisation modes).
 
 Outputs (inputs and the reference's results, nothing else):
   quantizer_cases.npz   seeded weights -> qweight / scales / zero points / dequantised
   awq_fixture.npz       AWQ checkpoint tensors, a slice of the activation, and the
                         reference-dequantised bf16 weight and reference output
   act_quant_cases.npz   seeded activations -> reference fake-quantised activations
+  act_quant_modes.npz   the same for every activation quantisation mode (0..7), K-block 128
 """
 import os
 import re
@@ -55,13 +56,13 @@ def _load_awq_helpers(ref):
     return ns
 
 
-def _load_fakequant(ref):
+def _load_fakequant(ref, asym=False):
     src = open(os.path.join(ref, "tests/cpu/test_quantization_default_recipe.py")).read()
-    a = src.index("    def _fakequant_by_group_sym(")
+    a = src.index("    def _fakequant_by_group(" if asym else "    def _fakequant_by_group_sym(")
     b = src.index("    def test_weight_only_quantization_act_quant_mode(")
     ns = {"torch": torch}
     exec(textwrap.dedent(src[a:b]), ns)
-    return ns["_fakequant_by_group_sym"]
+    return ns["_fakequant_by_group" if asym else "_fakequant_by_group_sym"]
 
 
 def bf16_bits(t: torch.Tensor) -> np.ndarray:
@@ -84,6 +85,8 @@ def main(ref):
         ("int4_pc_asym", 32, 200, W.INT4, -1, False, 0.02),
         ("int8_pc_sym", 64, 384, W.INT8, -1, True, 0.02),
         ("int8_g128_asym", 32, 256, W.INT8, 128, False, 0.02),
+        ("nf4_g64_sym", 24, 256, W.NF4, 64, True, 0.02),
+        ("nf4_pc_sym", 16, 200, W.NF4, -1, True, 0.05),
     ]
     for i, (name, N, K, dt, G, sym, std) in enumerate(specs):
         torch.manual_seed(100 + i)
@@ -146,6 +149,19 @@ def main(ref):
         acts[f"c{i}.x_bf16"] = bf16_bits(x)
         acts[f"c{i}.fq_f32"] = out.numpy()
     np.savez_compressed(os.path.join(here, "act_quant_cases.npz"), **acts)
+
+    # ---- every activation quantisation mode: 0 per tensor, 1 per K block, 2 per token, 3 per
+    # token and K block; +4 symmetric (csrc/cpu/aten/utils/woq_defines.h:11-19) ----------
+    fq_asym = _load_fakequant(ref, asym=True)
+    modes = {}
+    for i, (M, K) in enumerate([(4, 256), (9, 384), (2, 1024)]):
+        torch.manual_seed(300 + i)
+        x = (torch.randn(M, K) + 0.3).bfloat16()  # a range that is not centred on zero
+        modes[f"c{i}.x_bf16"] = bf16_bits(x)
+        for mode in range(8):
+            out = (fq_asym if mode < 4 else fq)(None, x.float(), mode, 128)
+            modes[f"c{i}.mode{mode}_f32"] = out.numpy()
+    np.savez_compressed(os.path.join(here, "act_quant_modes.npz"), **modes)
     print("golden fixtures written to", here)
 
 

@@ -58,8 +58,9 @@ def test_bad_arguments_are_rejected_without_a_gpu(built_lib):
     d = _capi.Desc(n=64, k=64, weight_dtype=_capi.DTYPE_INT4, group_size=0)
     rc = L.woq_b200_ctx_create(ctypes.byref(d), 16, 16, None, None, None, ctypes.byref(h))
     assert rc == 1 and b"group_size" in L.woq_b200_last_error()
-    d = _capi.Desc(n=64, k=64, weight_dtype=_capi.DTYPE_NF4, group_size=64,
-                   scale_dtype=_capi.T_F32)
+    # a valid reference configuration this build lacks: NF4 weights in a GPTQ checkpoint layout
+    d = _capi.Desc(n=64, k=64, weight_dtype=_capi.DTYPE_NF4, group_size=64, lowp_mode=_capi.LOWP_BF16,
+                   weight_format=_capi.FMT_GPTQ, scale_dtype=_capi.T_F32)
     rc = L.woq_b200_ctx_create(ctypes.byref(d), 16, 16, None, None, None, ctypes.byref(h))
     assert rc == 2
     assert L.woq_b200_ctx_destroy(None) == 1

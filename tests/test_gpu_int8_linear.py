@@ -163,12 +163,18 @@ def test_asymmetric_gate_up_silu_mul(capi):
     assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)
 
 
-def test_unsupported_modes_are_reported(capi):
+def test_other_int8_recipes_take_their_own_routes(capi):
+    """INT8 weights without INT8 compute run on the general kernel, an activation range per K block
+    on the K-block INT8 kernel (tests/test_gpu_generic.py, tests/test_gpu_int8_block.py); what no
+    kernel takes is refused with a status, never run as something else."""
     layer = make_layer(64, 128, seed=1)
     qw, s = torch.from_numpy(layer["qw"]).cuda(), torch.from_numpy(layer["s"]).cuda()
-    with pytest.raises(capi.WoqError) as e:
-        capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_BF16)
+    assert capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_BF16).route() == capi.ROUTE_GENERAL
+    assert capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
+                           act_quant_mode=7).route() == capi.ROUTE_INT8_BLOCK
+    assert capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
+                           act_quant_mode=6).route() == capi.ROUTE_INT8
+    with pytest.raises(capi.WoqError) as e:  # K block of 32: below what the integer kernel takes
+        capi.WoqContext(qw[:, :96].contiguous(), s, None, None, 64, 96, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
+                        act_quant_mode=7)
     assert e.value.code == 2
-    with pytest.raises(capi.WoqError) as e:
-        capi.WoqContext(qw, s, None, None, 64, 128, capi.DTYPE_INT8, -1, capi.LOWP_INT8, act_quant_mode=7)
-    assert e.value.code == 2  # the per-K-block modes are not built

@@ -331,33 +331,6 @@ def test_row_parallel_shards_sum_to_the_full_layer(ipex):
     parity(y, y_ref)
 
 
-def test_compute_dtypes_that_are_not_built_are_refused_not_narrowed(ipex):
-    """The reference routes lowp NONE by the activation dtype and has an fp16 kernel for lowp
-    FP16 (csrc/cpu/aten/kernels/WoqLinearKrnl.cpp:75-106).  Only the bf16 route exists here; the
-    others must fail with a clear message instead of running in bf16."""
-    q = ipex.quantization
-    mods = ipex.nn.modules
-    lin = make_linear(128, 256, False, seed=21)
-    # lowp NONE with bf16 activations IS the reference's bf16 kernel: it runs
-    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
-        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.NONE, group_size=128).global_qconfig
-    mod = mods.WeightOnlyQuantizedLinear.from_float(copy.deepcopy(lin))  # from_float empties its input
-    xb = torch.randn(4, 256, device="cuda").bfloat16()
-    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
-        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.BF16, group_size=128).global_qconfig
-    assert torch.equal(mod(xb), mods.WeightOnlyQuantizedLinear.from_float(copy.deepcopy(lin))(xb))
-    # ... with fp32 or fp16 activations it would be an fp32 / fp16 kernel: refused
-    with pytest.raises(RuntimeError, match="lowp_mode NONE"):
-        mod(xb.float())
-    with pytest.raises(RuntimeError, match="lowp_mode NONE"):
-        mod(xb.half())
-    # lowp FP16: refused when the context is made
-    lin.qconfig = q.get_weight_only_quant_qconfig_mapping(
-        weight_dtype=q.WoqWeightDtype.INT4, lowp_mode=q.WoqLowpMode.FP16, group_size=128).global_qconfig
-    with pytest.raises(RuntimeError, match="FP16"):
-        mods.WeightOnlyQuantizedLinear.from_float(copy.deepcopy(lin))
-
-
 def test_pickle_state_is_the_reference_twelve_tuple_and_load_from_ctx(ipex):
     q = ipex.quantization
     lin = make_linear(256, 512, True, seed=31)

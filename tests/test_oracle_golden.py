@@ -15,6 +15,8 @@ QUANT_CASES = [
     "int4_pc_asym",
     "int8_pc_sym",
     "int8_g128_asym",
+    "nf4_g64_sym",
+    "nf4_pc_sym",
 ]
 
 
@@ -164,3 +166,35 @@ def test_int8_activation_modes_of_the_oracle(act_mode):
     y = O.woq_linear_int8(x, qw, sw, None, act_mode=act_mode)
     ref = x @ (qw.view(np.int8).astype(np.float32) * sw.reshape(-1, 1)).T
     assert np.abs(y - ref).max() <= 0.03 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("mode", range(8))
+def test_every_activation_quant_mode_against_reference_fake_quant(golden_dir, mode):
+    """quantise -> dequantise of the oracle equals the reference test suite's fake-quantiser
+    (tests/cpu/test_quantization_default_recipe.py:836-958) for all eight modes, K block 128."""
+    f = np.load(os.path.join(golden_dir, "act_quant_modes.npz"))
+    for c in range(3):
+        x = O.from_bf16_bits(f[f"c{c}.x_bf16"])
+        q, sa, zp = O.dynamic_quant_blocks(x, mode, 128)
+        K = x.shape[1]
+        s_full = np.repeat(sa, 128, axis=1)[:, :K]
+        if zp is None:
+            dq = q.astype(np.float32) * s_full
+        else:
+            dq = ((q.astype(np.float32) - np.repeat(zp, 128, axis=1)[:, :K].astype(np.float32)) * s_full).astype(np.float32)
+        ref = f[f"c{c}.mode{mode}_f32"]
+        if mode in (0, 4):
+            # the fixture for the per-tensor modes comes from torch's MinMaxObserver, whose scale
+            # rule differs in the last bits ((max - min) / 255 with min, max clamped to include
+            # zero); the codes may differ by one step on a few elements
+            assert np.abs(dq - ref).max() <= 1.01 * sa.max()
+        elif mode >= 5:
+            np.testing.assert_array_equal(dq, ref)  # by value: the helper keeps the sign of a zero code
+        else:
+            # asymmetric: the kernel rounds x / scale + zero_point (one fp32 sum, then
+            # nearbyint, woq_dynamic_quant.h:1631-1638) where the test helper rounds x / scale and
+            # adds the zero point afterwards; the fp32 sum lands exactly on a half now and then,
+            # and the two roundings then differ by one code.  Everything else is identical.
+            diff = np.abs(dq - ref)
+            assert (diff > 0).mean() <= 0.01
+            assert diff.max() <= 1.01 * sa.max()
