@@ -910,12 +910,19 @@ def main():
                     help="DRAM bytes per launch from an ncu capture (default: TRAFFIC_RATIO x algorithmic bytes)")
     ap.add_argument("--configs", default=None, nargs="?", const="all",
                     help="time every benchmark configuration's linears (optionally a prefix: c1, c2, c3, c4, c5)")
+    ap.add_argument("--stack", default=None, nargs="?", const="all",
+                    help="the Llama-3-8B-architecture decode stack (bench_stack.py); optionally batch sizes, e.g. 1,8")
+    ap.add_argument("--new-tokens", type=int, default=128, help="--stack: greedy decode steps")
     args = ap.parse_args()
     if args.split is not None:
         from ipex_b200 import _capi
 
         _capi.set_option(_capi.OPT_DECODE_SPLIT, args.split)
-    if args.configs:
+    if args.stack:
+        import bench_stack
+
+        bench_stack.run_stack(args, peaks, ClockSampler)
+    elif args.configs:
         run_configs(args)
     elif args.single:
         run_single(args)

@@ -5,6 +5,7 @@ from . import _capi  # noqa: F401
 from . import quantization  # noqa: F401
 from . import nn  # noqa: F401
 from . import llm  # noqa: F401
+from . import utils  # noqa: F401
 from ._ops import load_ops  # noqa: F401
 
 __all__ = ["_capi", "quantization", "nn", "llm", "load_ops"]
