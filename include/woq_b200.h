@@ -115,9 +115,15 @@ extern "C" {
 
 /* kernel selection for INT4 weights.  AUTO, TENSOR_CORE and STREAM all multiply by the
  * bf16-rounded dequantised weights bf16((q - zp) * bf16(scale)) and differ only in summation
- * order.  STREAM_FAST applies scale and zero point after the per-block sum (what the
- * reference's small-M kernel does, csrc/cpu/aten/utils/woq.h:784-951): cheaper, within the
- * output tolerance, but not the same rounding as the tile dequantiser. */
+ * order.  STREAM_FAST applies scale and zero point after the sum over each 64-wide k-block
+ * (what the reference's small-M kernel does after each group,
+ * csrc/cpu/aten/utils/woq.h:784-951): about 10 % faster on large layers, exact on one-hot
+ * inputs, and for a single linear within the output tolerance (mean relative deviation
+ * 1.2e-3 .. 1.7e-3 from the per-weight form on every benchmark shape, bar 2e-3) - but not the
+ * same rounding as the tile dequantiser, and a product of two such linears (the gate/up
+ * epilogue, woq_linear_silu followed by woq_linear_mul) deviates by about 2.5e-3, over the
+ * bar; so it is never chosen automatically.  It expects |x| < 2^40 (larger activations
+ * overflow to infinity inside the kernel) and treats |x| < 2^-61 as zero. */
 #define WOQ_B200_HINT_AUTO 0        /* streaming kernel for M <= 16, tcgen05 kernel above      */
 #define WOQ_B200_HINT_TENSOR_CORE 1 /* tcgen05 kernel for every M                              */
 #define WOQ_B200_HINT_STREAM 2      /* register-dequant streaming kernel, 16 tokens a pass     */

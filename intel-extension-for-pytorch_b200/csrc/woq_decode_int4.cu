@@ -15,9 +15,12 @@
 //     Nibbles at bits 0..3 of a half-word are OR-ed into the mantissa of 128.0 (one lop3);
 //     nibbles at bits 4..7 are used in place: masked, the half-word read as bf16 is
 //     16 q * 2^-133 exactly, and the scale for those rows is pre-multiplied by 2^129.
-//     Fast variant (hint STREAM_FAST): no subtract or multiply per weight; the tensor core
-//     accumulates sum_k x * (128 + q) per k-block, an MMA with an all-ones A-fragment gives
-//     sum_k x, and scale and zero point are applied to the sums per k-block.
+//     Fast variant (hint STREAM_FAST): no subtract or multiply per weight.  The tensor core
+//     accumulates sum_k x * (128 + q) per k-block for the rows whose nibbles sit at bits 0..3
+//     and sum_k x * 16 q 2^-133 for the rows used in place (x enters multiplied by 2^64 so
+//     that these products stay normal fp32 numbers); an MMA with an all-ones A-fragment gives
+//     sum_k x, and scale and zero point are applied to the sums per k-block.  Five integer
+//     instructions per eight weights instead of thirteen integer and bf16 ones.
 //   * At the end of a segment the consumers drop their partial sums in shared memory and go
 //     on; the epilogue warp adds them.  A CTA that saw the whole K of the tile writes y
 //     (bias, rounding, fused post-op); otherwise the partial goes to the workspace and the
@@ -161,6 +164,11 @@ __device__ __forceinline__ uint32_t comm_wait_word(const uint2* w, uint32_t stam
 // Timeline probe, compiled in only with -DWOQ_B200_TIMELINE (a measuring build, never the
 // shipped library): CTA c of launch q writes global-timer stamps to p.stamps[q % 8][c][idx].
 #ifdef WOQ_B200_TIMELINE
+__device__ __forceinline__ uint32_t tl_smid() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
 __device__ __forceinline__ void decode_stamp(const DecodeParams& p, int idx) {
   if (p.stamps) p.stamps[(static_cast<size_t>(p.launch_seq & 7) * 1024 + blockIdx.x) * 8 + idx] = global_timer_ns();
 }
@@ -908,6 +916,9 @@ __global__ void __launch_bounds__(kThreads, 2)
   StageIter it(tile0, kb00, share, p.kb_per_tile, kStageKBlocks);
   int slot = 0;
   uint32_t phase = 0;
+#ifdef WOQ_B200_TIMELINE
+  long long tl_wait = 0, tl_begin = 0;
+#endif
   // per-row constants of the current group, rows g, g+8 of each row-tile
   uint32_t cz[8], cs[8];
   // per-lane offsets inside a stage.  A lane whose token does not exist reads the last real
@@ -922,7 +933,14 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int nkb = it.nkb();
     const int kb0 = it.kb;
     const uint8_t* st = stages + static_cast<size_t>(slot) * stage_bytes;
+#ifdef WOQ_B200_TIMELINE
+    const long long tl_c0 = clock64();
+#endif
     mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 2);
+#ifdef WOQ_B200_TIMELINE
+    tl_wait += clock64() - tl_c0;
+    if (tl_begin == 0) tl_begin = clock64();
+#endif
     if (warp == 0 && lane == 0 && kb0 == kb00) decode_stamp(p, 3);
 
     // one k-block (64 rows x 64 k) of the stage: index idx, constants reloaded if `prep`
@@ -951,8 +969,19 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           if constexpr (MODE == kScaleAfterSum) {
-            cs[i] = szw[i] & 0xffff0000u;  // scale as fp32 bits
-            cz[i] = szw[i] << 16;          // 128 + zp as fp32 bits
+            // x enters the MMAs multiplied by 2^64 (see below).  Row g (even i): the A operand
+            // is 128 + q, so sum = 2^64 sum_k x (128 + q): subtract (128 + zp) sum_k x, scale by
+            // s 2^-64.  Row g+8 (odd i): the A operand is the nibble in place, 16 q 2^-133 as a
+            // subnormal bf16, so sum = 2^-65 sum_k x q: subtract zp 2^-129 sum_k x, scale by s 2^65.
+            const float sf = __uint_as_float(szw[i] & 0xffff0000u);
+            const float zf = __uint_as_float(szw[i] << 16);  // 128 + zp
+            if (i & 1) {
+              cs[i] = __float_as_uint(sf * 36893488147419103232.f);                           // 2^65
+              cz[i] = __float_as_uint((zf - 128.f) * 1.4693679385278594e-39f);                // 2^-129
+            } else {
+              cs[i] = __float_as_uint(sf * 5.421010862427522e-20f);                           // 2^-64
+              cz[i] = __float_as_uint(zf);
+            }
           } else if (MODE == kExactInPlace && (i & 1)) {
             // row g+8 takes its nibbles from bits 4..7 / 20..23 without a shift: read as bf16
             // the masked half-word is 16 q * 2^-133 exactly (the encoding is linear below
@@ -994,6 +1023,12 @@ __global__ void __launch_bounds__(kThreads, 2)
           }
         }
       } else {
+        // Activations times 2^64 (exact unless |x| >= 2^63): the in-place rows multiply x by
+        // numbers near 2^-129, and the products must stay in fp32's normal range.
+#pragma unroll
+        for (int tb = 0; tb < TB; ++tb)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) xb[tb][i] = bf16x2_mul(xb[tb][i], 0x5f805f80u);
         float accg[4][TB][4];
         float sx[TB][4];
 #pragma unroll
@@ -1014,11 +1049,12 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
           for (int rt = 0; rt < 4; ++rt) {
             const uint32_t w = (rt == 0) ? wv[j].x : (rt == 1) ? wv[j].y : (rt == 2) ? wv[j].z : wv[j].w;
+            const uint32_t u = w >> 8;
             uint32_t a[4];
             a[0] = lop3_and_or(w, 0x000f000fu, kBf16Magic);
-            a[1] = lop3_and_or(w >> 4, 0x000f000fu, kBf16Magic);
-            a[2] = lop3_and_or(w >> 8, 0x000f000fu, kBf16Magic);
-            a[3] = lop3_and_or(w >> 12, 0x000f000fu, kBf16Magic);
+            a[1] = w & 0x00f000f0u;
+            a[2] = lop3_and_or(u, 0x000f000fu, kBf16Magic);
+            a[3] = u & 0x00f000f0u;
 #pragma unroll
             for (int tb = 0; tb < TB; ++tb)
               mma_bf16_16816(accg[rt][tb], a, xb[tb][2 * j], xb[tb][2 * j + 1]);
@@ -1062,6 +1098,11 @@ __global__ void __launch_bounds__(kThreads, 2)
       phase ^= 1;
     }
   }
+#ifdef WOQ_B200_TIMELINE
+  if (warp == 3 && lane == 0 && p.stamps)
+    p.stamps[(static_cast<size_t>(p.launch_seq & 7) * 1024 + blockIdx.x) * 8 + 6] =
+        (static_cast<long long>(tl_smid()) << 56) | ((tl_wait & 0xffffffll) << 32) | ((clock64() - tl_begin) & 0xffffffffll);
+#endif
   if (CLUSTER && csize > 1) {
     __syncwarp();
     cluster_sync_all();

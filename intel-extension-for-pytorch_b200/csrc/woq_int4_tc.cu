@@ -21,6 +21,13 @@
 //               either the fused post-op and store, or - when the CTA saw only part of K -
 //               a partial tile in the workspace that the last contributor sums in a fixed
 //               order.
+// Two rings.  The packed weights travel through a shared-memory ring of up to 32 slots that
+// the dequantising warps free as soon as they have the nibbles in registers; the dequantised
+// A groups (TMEM) and the activation tiles form a second, shorter ring freed by the MMAs'
+// commit.  The accumulator takes as many TMEM columns as there are token columns (rounded to
+// 32), the A groups all the others: 8 groups beside a 256-column accumulator, 14 beside a
+// 64-column one.  Weight bytes in flight per SM are bounded by shared memory (about 100 KB
+// and more for up to 128 tokens), not by TMEM.
 // Work split: the (tile, k-block) sequence is cut into equal contiguous shares, one per SM.
 #include <cstdlib>
 
@@ -36,19 +43,17 @@ constexpr int kWarpGroups = kDequantWarps / 4;
 constexpr int kTcThreads = (kDequantWarps + 4) * 32;
 constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1, kXProducerWarp = kDequantWarps + 2,
               kMmaWarp2 = kDequantWarps + 3;
-constexpr int kASlots = 8;           // 32 TMEM columns each (one k-block of bf16 A)
-constexpr int kDCol0 = 0;            // accumulator columns [0, 256)
-constexpr int kDCols = 256;
-constexpr int kMaxAcc = 8;           // independent accumulators for small token counts
-constexpr int kACol0 = 256;          // A slots in columns [256, 512)
-constexpr int kTmemCols = 512;
-constexpr int kMaxTcStages = 8;
+constexpr int kDCol0 = 0;            // accumulator columns [0, a_col0)
+constexpr int kTmemCols = 512;       // A groups (32 columns = one k-block of bf16 A) fill the rest
+constexpr int kMaxTcStages = 16;     // A-group / activation ring
+constexpr int kMaxWRing = 32;        // packed-weight ring
 constexpr int kTcHeaderBytes = 1024;
 
 struct TcHeader {
-  uint64_t w_full[kMaxTcStages];  // packed weights + scales of the stage have landed
+  uint64_t w_full[kMaxWRing];     // packed weights + scales of the weight-ring slot have landed
+  uint64_t w_free[kMaxWRing];     // the four dequantising warps have read the slot
   uint64_t full[kMaxTcStages];    // A group written (4 warps) and x tiles landed (1 + bytes)
-  uint64_t free_[kMaxTcStages];   // the stage's MMAs have completed: everything may be reused
+  uint64_t free_[kMaxTcStages];   // the stage's MMAs have completed: A group and x tiles may be reused
   uint64_t issued[2];             // MMA warp t has issued the MMAs of its latest stage
   uint64_t d_full, d_empty;
   uint32_t tmem_base;
@@ -149,9 +154,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 
   if (tid == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&hdr->w_full[s], 1);
       mbar_init(&hdr->full[s], 5);
       mbar_init(&hdr->free_[s], 1);
+    }
+    for (int s = 0; s < p.w_ring; ++s) {
+      mbar_init(&hdr->w_full[s], 1);
+      mbar_init(&hdr->w_free[s], 4);
     }
     mbar_init(&hdr->issued[0], 1);
     mbar_init(&hdr->issued[1], 1);
@@ -179,6 +187,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   int64_t b = b_begin;
   int slot = 0;
   uint32_t phase = 0;       // parity of the current use of `slot`
+  int wslot = 0;            // the same stage's slot in the weight ring
+  uint32_t wphase = 0;
   auto stage_len = [&]() {
     int nkb = p.kb_per_tile - kb0;
     if (nkb > p.kbs) nkb = p.kbs;
@@ -196,6 +206,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       slot = 0;
       phase ^= 1;
     }
+    if (++wslot == p.w_ring) {
+      wslot = 0;
+      wphase ^= 1;
+    }
   };
 
   if (warp == kProducerWarp) {
@@ -203,16 +217,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     if (lane == 0) {
       while (b < b_end) {
         const int nkb = stage_len();
-        uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
+        uint8_t* ws = w_stages + static_cast<size_t>(wslot) * w_stage_bytes;
         const int g0 = kb0 >> p.kbpg_shift;
         const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
-        mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 11);
-        mbar_arrive_expect_tx(&hdr->w_full[slot], nkb * kTcBlockBytes + ng * 512);
+        mbar_wait(&hdr->w_free[wslot], wphase ^ 1, abort_flag, p.status, 11);
+        mbar_arrive_expect_tx(&hdr->w_full[wslot], nkb * kTcBlockBytes + ng * 512);
         bulk_g2s(ws, p.wq + (static_cast<size_t>(tile) * p.kb_per_tile + kb0) * kTcBlockBytes,
-                 nkb * kTcBlockBytes, &hdr->w_full[slot]);
+                 nkb * kTcBlockBytes, &hdr->w_full[wslot]);
         bulk_g2s(ws + p.kbs * kTcBlockBytes,
                  p.sz + (static_cast<size_t>(tile) * p.groups + g0) * kTcTileN, ng * 512,
-                 &hdr->w_full[slot]);
+                 &hdr->w_full[wslot]);
         advance(nkb);
       }
     }
@@ -256,7 +270,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           if (mst > 0) mbar_wait(&hdr->issued[me ^ 1], ((mst - 1) >> 1) & 1, abort_flag, p.status, 14);
           tc_fence_after_sync();
           uint32_t accumulate = first_of_segment ? 0u : 1u;
-          uint32_t a_addr = tmem_base + kACol0 + slot * (p.kbs * 32);
+          uint32_t a_addr = tmem_base + p.a_col0 + slot * (p.kbs * 32);
           uint32_t b_lo = x_base_lo + slot * x_stage_lo;
           for (int j = 0; j < nkb; ++j) {
 #pragma unroll
@@ -363,11 +377,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     int stage_no = 0;
     while (b < b_end) {
       const int nkb = stage_len();
-      const uint8_t* ws = w_stages + static_cast<size_t>(slot) * w_stage_bytes;
+      const uint8_t* ws = w_stages + static_cast<size_t>(wslot) * w_stage_bytes;
       const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
       // the stages go round-robin to the four warpgroups; the others only keep count
       if ((stage_no & (kWarpGroups - 1)) == wg) {
-        mbar_wait(&hdr->w_full[slot], phase, abort_flag, p.status, 16);
+        mbar_wait(&hdr->w_full[wslot], wphase, abort_flag, p.status, 16);
         const int g0 = kb0 >> p.kbpg_shift;
         for (int j = 0; j < nkb; ++j) {
           const uint4* wp = reinterpret_cast<const uint4*>(ws + j * kTcBlockBytes);
@@ -384,11 +398,16 @@ __global__ void __launch_bounds__(kTcThreads, 1)
               r[jj * 4 + s] = bf16x2_mul(
                   bf16x2_sub(lop3_and_or(words[jj] >> (4 * s), 0x000f000fu, kBf16Magic), z2), s2);
           }
+          if (j == nkb - 1) {
+            // the values of the weight slot's last k-block have been used: the slot is free
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&hdr->w_free[wslot]);
+          }
           if (j == 0) {
             mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 17);
             tc_fence_after_sync();
           }
-          tmem_st_x32(lane_addr + kACol0 + slot * (p.kbs * 32) + j * 32, r);
+          tmem_st_x32(lane_addr + p.a_col0 + slot * (p.kbs * 32) + j * 32, r);
         }
         tc_wait_st();
         tc_fence_before_sync();
@@ -502,19 +521,37 @@ int tc_pick_grid(int tiles, int kb_per_tile, int num_sms) {
 }
 
 cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream) {
-  // k-blocks per stage: enough bytes in flight for small token counts, one x tile otherwise
+  // TMEM: the accumulator takes the token columns (rounded to 32), the A groups the rest.
+  p.a_col0 = (p.n_tok + 31) & ~31;
+  const int a_groups = (kTmemCols - p.a_col0) / 32;
+  // k-blocks per stage: two for small token counts (fewer barrier round trips per byte)
   p.kbs = p.n_tok <= 64 ? 2 : 1;
   const int x_stage = p.kbs * p.n_tok * 128;
   const int w_stage = p.kbs * kTcBlockBytes + (p.kbs + 1) * 512;
-  const int budget = 224 * 1024;
-  int stages = (budget - kTcHeaderBytes) / (x_stage + w_stage);
-  if (stages > kASlots / p.kbs) stages = kASlots / p.kbs;  // one A group in TMEM per slot
-  // A warpgroup works on every fourth stage.  With fewer than four pipeline slots it could
+  const int budget = 224 * 1024 - kTcHeaderBytes;
+  int stages, w_ring;
+  if (p.n_tok > 128) {
+    // a launch this wide is bound by the dequantising warps and the tensor core, not by bytes
+    // in flight: one ring length for both
+    stages = budget / (x_stage + w_stage);
+    if (stages > a_groups / p.kbs) stages = a_groups / p.kbs;
+    w_ring = stages;
+  } else {
+    // A-group ring as long as TMEM allows within half of the shared memory; the packed weights
+    // get what is left
+    stages = a_groups / p.kbs;
+    if (stages > kMaxTcStages) stages = kMaxTcStages;
+    while (stages > 4 && stages * x_stage > budget / 2) --stages;
+    w_ring = (budget - stages * x_stage) / w_stage;
+    if (w_ring > kMaxWRing) w_ring = kMaxWRing;
+  }
+  // A warpgroup works on every fourth stage.  With fewer than four slots in a ring it could
   // reach a slot two uses ahead of the producer or of the MMA warp, and a parity wait cannot
   // tell those apart.
-  if (stages < 4) return cudaErrorInvalidConfiguration;
+  if (stages < 4 || w_ring < 4) return cudaErrorInvalidConfiguration;
+  p.w_ring = w_ring;
   p.stages = stages;
-  const size_t smem = kTcHeaderBytes + static_cast<size_t>(stages) * (x_stage + w_stage);
+  const size_t smem = kTcHeaderBytes + static_cast<size_t>(stages) * x_stage + static_cast<size_t>(w_ring) * w_stage;
   cudaError_t e = cudaFuncSetAttribute(woq_int4_tc_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));

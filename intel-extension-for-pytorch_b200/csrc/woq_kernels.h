@@ -119,7 +119,8 @@ struct TcParams {
   int m0;              // first token row of this launch inside the x tensor map
   int n_tok;           // token columns of the MMA (multiple of 16, <= 256)
   int tiles, kb_per_tile, kbpg_shift, groups;
-  int kbs, stages;
+  int kbs, stages;     // k-blocks per stage; slots of the A-group / activation ring
+  int w_ring, a_col0;  // slots of the packed-weight ring; first TMEM column of the A groups
   int fusion, gate_up;
 };
 
