@@ -363,6 +363,51 @@ def e2e_through_ops(torch, quant, m, device, n_layers=4, steps=20):
             "api": "torch.ops.torch_ipex.{ipex_woq_linear, woq_linear_add, woq_linear_silu_mul}"}
 
 
+def fast_side_line(torch, capi, quant, device, m):
+    """One Llama-3-70B layer's four linears with both INT4 dequantisers of the streaming kernel:
+    the default (bf16 rounding per weight, the reference's tile dequantiser) and the hint
+    WOQ_B200_HINT_STREAM_FAST (scale and zero point applied after each k-block sum).  Timed as a
+    CUDA graph of the four launches in layer order (428 MB of weights per pass, more than L2);
+    the deviation is mean |y_fast - y_default| / mean |y_default| per shape."""
+    bf = dict(device=device, dtype=torch.bfloat16)
+    hbm_peak, _, _ = peaks()
+    sets = {}
+    xs, ys = {}, {}
+    g = torch.Generator(device=device).manual_seed(777)
+    for name, n, k, _ in layer_shapes(1):
+        w = torch.randn((n, k), device=device, generator=g) * 0.02
+        qw, s, z = quant.quantize_per_block(w, quant.WoqWeightDtype.INT4, GROUP)
+        del w
+        flags = capi.LAYOUT_STREAM_ONLY | (capi.LAYOUT_GATE_UP if name == "gate_up" else 0)
+        for hint in (capi.HINT_AUTO, capi.HINT_STREAM_FAST):
+            sets.setdefault(hint, {})[name] = capi.WoqContext(qw, s.half(), z, None, n, k, capi.DTYPE_INT4, GROUP,
+                                                              capi.LOWP_BF16, layout_flags=flags, kernel_hint=hint)
+        xs[name] = torch.randn((m, k), generator=g, **bf)
+        ys[name] = torch.empty((m, n // 2 if name == "gate_up" else n), **bf)
+        del qw, s, z
+    ws = capi.Workspace(max(c.workspace_bytes(m) for c in sets[capi.HINT_AUTO].values()), device)
+    out = {"m": m, "shapes": {}}
+    results = {}
+    for hint, key in ((capi.HINT_AUTO, "per_weight"), (capi.HINT_STREAM_FAST, "after_sum")):
+        def layer():
+            for name in ("qkv", "o_proj", "gate_up", "down_proj"):
+                sets[hint][name].linear(xs[name], capi.FUSE_SILU_MUL if name == "gate_up" else capi.FUSE_NONE,
+                                        out=ys[name], workspace=ws)
+        layer()
+        torch.cuda.synchronize()
+        results[key] = {name: ys[name].float().clone() for name in ys}
+        us = _time_graph(torch, layer, 4) * 4
+        wb = full_layer_weight_bytes()
+        out[key] = {"layer_us": round(us, 2), "weight_GBps": round(wb / us / 1e3, 1),
+                    "frac": round(wb / us / 1e3 / hbm_peak, 4)}
+    ws.status()
+    for name in ys:
+        a, b = results["after_sum"][name], results["per_weight"][name]
+        out["shapes"][name] = {"mean_rel_deviation": float((a - b).abs().mean() / b.abs().mean()),
+                               "max_abs_over_inf_norm": float((a - b).abs().max() / b.abs().max())}
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -638,6 +683,13 @@ def run_ours(args):
                    "frac": tflops / tf_peak if tf_peak else None}
         del pctx, px, py, pws
 
+    # ---- side line: the scale-after-sum dequantiser (WOQ_B200_HINT_STREAM_FAST) on one layer's
+    # four shapes beside the per-weight default, with the deviation between the two --------------
+    stream_fast = None
+    if p == 1 and m <= 8 and not args.no_fast:
+        stream_fast = fast_side_line(torch, capi, quant, device, m)
+        log(f"scale-after-sum side line: {stream_fast}")
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": p, "steps": args.steps,
@@ -650,7 +702,7 @@ def run_ours(args):
                                       if fused else "nccl"),
                        "l2": f"weights ({total_w / 1e9:.1f} GB per step over all ranks) exceed L2; no flush needed",
                        "cuda_graph": graph is not None},
-            "roofline": roofline, "prefill": prefill, "e2e": e2e, "e2e_ops": e2e_ops,
+            "roofline": roofline, "prefill": prefill, "stream_fast": stream_fast, "e2e": e2e, "e2e_ops": e2e_ops,
             "checked": check is not None, "check": check, "gpu_launches": launched_per_step * args.steps,
             "clocks": clocks,
         }
@@ -899,6 +951,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the check of the step's outputs before timing")
     ap.add_argument("--no-e2e-ops", action="store_true", help="skip the end-to-end leg through torch.ops")
+    ap.add_argument("--no-fast", action="store_true", help="skip the scale-after-sum side line")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (tensor-core kernel) side line")
     ap.add_argument("--single", default=None, help="NxK: run one linear shape only (profiler captures)")
     ap.add_argument("--int8", action="store_true", help="--single: INT8 weights with INT8 compute")
