@@ -424,6 +424,41 @@ at::Tensor mixtral_moe_woq(const at::Tensor& hidden_states, const at::Tensor& to
   return output;
 }
 
+// reference: csrc/cpu/aten/MoE.cpp:290-330.  topk_ids [tokens, top_k] names each token's experts; every
+// selected expert runs the per-expert routine above on its tokens.  The (token, slot) pairs of all
+// experts come from one stable sort on the device and one copy of the per-expert counts to the host.
+at::Tensor deepseek_moe_woq(const at::Tensor& hidden_states, const at::Tensor& topk_ids,
+                            const std::vector<c10::intrusive_ptr<WoqLinearOpContext>>& gate_ctx,
+                            const std::vector<c10::intrusive_ptr<WoqLinearOpContext>>& up_ctx,
+                            const std::vector<c10::intrusive_ptr<WoqLinearOpContext>>& down_ctx,
+                            const at::Tensor& routing_weights, bool is_distributed) {
+  const int64_t experts = static_cast<int64_t>(gate_ctx.size());
+  TORCH_CHECK(static_cast<int64_t>(up_ctx.size()) == experts && static_cast<int64_t>(down_ctx.size()) == experts,
+              "WOQ: deepseek_moe_woq takes one gate, up and down context per expert");
+  TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.size(0) == hidden_states.size(0),
+              "WOQ: topk_ids must be [tokens, top_k]");
+  at::Tensor output = at::zeros_like(hidden_states);
+  if (experts == 0 || topk_ids.numel() == 0) return output;
+  const int64_t top_k = topk_ids.size(1);
+  at::Tensor flat = topk_ids.to(hidden_states.device()).reshape({-1}).to(at::kLong);
+  at::Tensor order = at::argsort(flat, /*stable=*/true, /*dim=*/0, /*descending=*/false);
+  at::Tensor counts = at::bincount(flat, {}, experts).cpu();
+  TORCH_CHECK(counts.size(0) == experts, "WOQ: topk_ids names an expert beyond the contexts given");
+  const int64_t* cnt = counts.data_ptr<int64_t>();
+  int64_t off = 0;
+  for (int64_t e = 0; e < experts; ++e) {
+    if (cnt[e] == 0) continue;
+    at::Tensor pairs = order.narrow(0, off, cnt[e]);
+    off += cnt[e];
+    at::Tensor top_x = at::floor_divide(pairs, top_k);
+    at::Tensor idx = at::remainder(pairs, top_k);
+    output = mixtral_moe_woq(hidden_states, top_x, idx, gate_ctx[e]->get_data_handle(),
+                             up_ctx[e]->get_data_handle(), down_ctx[e]->get_data_handle(), routing_weights,
+                             output, is_distributed);
+  }
+  return output;
+}
+
 int64_t dtype_from_str(const std::string& s) {
   if (s == "int8") return WOQ_B200_DTYPE_INT8;
   if (s == "int4") return WOQ_B200_DTYPE_INT4;
@@ -618,6 +653,11 @@ TORCH_LIBRARY(torch_ipex, m) {
   m.def("woq_linear_mul(Tensor input, Tensor W_prepack, Tensor[] others) -> Tensor");
   m.def("mixtral_moe_woq(Tensor hidden_states, Tensor top_x, Tensor idx, Tensor gate_wei, Tensor up_wei, "
         "Tensor down_wei, Tensor routing_weights, Tensor output, bool is_distributed) -> Tensor");
+  m.def("deepseek_moe_woq(Tensor hidden_states, Tensor topk_ids, "
+        "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext[] gate_ctx, "
+        "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext[] up_ctx, "
+        "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext[] down_ctx, "
+        "Tensor routing_weights, bool is_distributed) -> Tensor");
   m.def("woq_check_status() -> ()", woq_check_status);
   m.def("woq_linear(Tensor input, Tensor qweight, str weight_dtype, int[] weight_shape, Tensor[] weight_scales, "
         "Tensor[]? weight_zeros, Tensor[]? bias, Tensor? g_idx, int group_size, int lowp_mode, "
@@ -636,6 +676,7 @@ TORCH_LIBRARY_IMPL(torch_ipex, CUDA, m) {
   m.impl("woq_linear_mul", woq_linear_mul);
   m.impl("woq_linear", woq_linear);
   m.impl("mixtral_moe_woq", mixtral_moe_woq);
+  m.impl("deepseek_moe_woq", deepseek_moe_woq);
 }
 
 TORCH_LIBRARY_IMPL(torch_ipex, AutocastCUDA, m) {

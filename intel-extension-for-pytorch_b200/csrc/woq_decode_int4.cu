@@ -1169,6 +1169,7 @@ void (*pick_kernel(int mode, bool comm, bool cluster))(const DecodeParams) {
 }  // namespace
 
 void decode_int4_set_split(int mode) { tuning().split = mode; }
+bool dependent_launch_enabled() { return tuning().pdl != 0; }
 
 namespace {
 

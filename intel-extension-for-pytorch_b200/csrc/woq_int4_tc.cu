@@ -176,6 +176,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
   __syncthreads();
   tc_fence_after_sync();
+  // Programmatic dependent launch, both ways: a following launch may begin while this grid
+  // runs, and this grid may have begun before the previous kernel in the stream ended.  The
+  // packed weights never change, so their producer starts at once; whoever touches x, y or the
+  // workspace waits for the previous kernel first (grid_dependency_wait).
+  grid_launch_dependents();
   const uint32_t tmem_base = hdr->tmem_base;
   volatile int* abort_flag = &hdr->abort_flag;
 
@@ -233,6 +238,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   } else if (warp == kXProducerWarp) {
     // activation tiles (TMA, 128-byte swizzle), one per k-block
     if (lane == 0) {
+      grid_dependency_wait();
       while (b < b_end) {
         const int nkb = stage_len();
         uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
@@ -419,6 +425,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (seg_end) {
         const bool whole = (seg_kb0 == 0 && kb0 + nkb == p.kb_per_tile);
         const int n_used = 1;
+        grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid from here on
         mbar_wait(&hdr->d_full, seg & 1, abort_flag, p.status, 18);
         tc_fence_after_sync();
         if (whole && p.fusion != FUSE_SILU_MUL) {
@@ -556,8 +563,17 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  woq_int4_tc_kernel<<<grid, kTcThreads, smem, stream>>>(p, xmap);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, woq_int4_tc_kernel, p, xmap);
 }
 
 }  // namespace woq

@@ -124,6 +124,8 @@ struct TcParams {
   int fusion, gate_up;
 };
 
+// launches opt into programmatic dependent launch unless WOQ_B200_PDL=0 was set before first use
+bool dependent_launch_enabled();
 int tc_pick_grid(int tiles, int kb_per_tile, int num_sms);
 size_t tc_partial_bytes(int grid, int n_tok);
 cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream);

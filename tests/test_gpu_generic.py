@@ -202,3 +202,26 @@ def test_nf4_module(ipex):
     x = make_acts(4, 256, seed=1)
     y = mod(to_io(x, "bf16"))
     check(y.float().cpu().numpy(), O.woq_linear_any(x, qw, s, None, b, O.WOQ_DTYPE_NF4, 64, "bf16", "bf16"), "bf16")
+
+
+@pytest.mark.parametrize("act_dtype", ["fp32", "bf16"])
+def test_default_recipe_runs_end_to_end(ipex, act_dtype):
+    """get_weight_only_quant_qconfig_mapping() with no arguments - INT8 weights per channel, lowp
+    NONE (compute in the activation's dtype) - and the default INT8-compute recipe (INT8 weights,
+    activation mode PER_BATCH_IC_BLOCK_SYM) both build and run through from_float
+    (reference: tests/cpu/test_quantization_default_recipe.py:318-419)."""
+    q = ipex.quantization
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(384, 192, bias=True)
+    x = torch.randn(5, 384)
+    y_fp = lin(x)
+    for qmap in (q.get_weight_only_quant_qconfig_mapping(),
+                 q.get_weight_only_quant_qconfig_mapping(lowp_mode=q.WoqLowpMode.INT8)):
+        mod = copy.deepcopy(lin)
+        mod.qconfig = qmap.global_qconfig
+        w = ipex.nn.modules.WeightOnlyQuantizedLinear.from_float(mod)
+        xin = x.to(TORCH[act_dtype]).cuda()
+        y = w(xin)
+        assert y.dtype == TORCH[act_dtype] and y.shape == (5, 192)
+        # 8-bit weights (and 8-bit activations in the second recipe): close to the float layer
+        assert torch.nn.functional.cosine_similarity(y.float().cpu().flatten(), y_fp.flatten(), dim=0) > 0.999

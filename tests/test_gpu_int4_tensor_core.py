@@ -128,3 +128,44 @@ def test_repeatable(capi):
     y0 = ctx.linear(x).clone()
     for _ in range(3):
         assert torch.equal(ctx.linear(x), y0)
+
+
+@pytest.mark.parametrize("m", [24, 200])
+def test_dependent_launches_back_to_back(capi, m):
+    """A chain in which every linear reads the previous one's output and all share one workspace,
+    launched without host synchronisation (the launches may overlap under programmatic dependent
+    launch) and as a CUDA graph: same bits as the chain with a synchronisation after every launch."""
+    dims = [(1024, 512), (768, 1024), (512, 768), (1024, 512)]
+    layers = [make_int4_layer(n, k, 128, seed=900 + i, std=0.05) for i, (n, k) in enumerate(dims)]
+    ctxs = [make_ctx(capi, layer) for layer in layers]
+    ws = capi.Workspace(max(c.workspace_bytes(m) for c in ctxs), "cuda")
+    x = bf16_tensor(make_acts(m, 512, seed=m), "cuda")
+    bufs = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for n, _ in dims]
+
+    def chain(sync):
+        h = x
+        for c, out in zip(ctxs, bufs):
+            c.linear(h, out=out, workspace=ws)
+            if sync:
+                torch.cuda.synchronize()
+            h = out
+        return h
+
+    want = chain(True).clone()
+    for _ in range(5):
+        got = chain(False)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        chain(False)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(3):
+                chain(False)
+        for _ in range(4):
+            graph.replay()
+        stream.synchronize()
+    assert torch.equal(bufs[-1], want)
+    ws.status()

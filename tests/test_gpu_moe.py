@@ -106,6 +106,43 @@ def test_mixtral_moe_woq_operator(env, tokens):
     parity(bf16_numpy(out), ref)
 
 
+@pytest.mark.parametrize("tokens", [3, 40])
+def test_deepseek_moe_woq_operator(env, tokens):
+    """The list-of-contexts form (csrc/cpu/aten/MoE.cpp:290-330): same result as the per-expert operator
+    called expert by expert, experts nobody chose are skipped."""
+    hidden, ffn = 512, 1024
+    experts, router = make_experts(hidden, ffn, seed=4200)
+    h = make_acts(tokens, hidden, seed=4200 + tokens)
+    idx, w = O.moe_route_top2(h, router)
+    ref = O.moe_layer(h, idx, w, experts, G)
+    hg = bf16_tensor(h, "cuda")
+    rw = bf16_tensor(w, "cuda")
+    sel = torch.from_numpy(idx.astype(np.int64)).cuda()
+
+    def ctx(q, s, z, n, k):
+        return torch.ops.ipex_prepack.weight_only_qlinear_prepack(
+            torch.from_numpy(q).cuda(), 2, [n, k], torch.from_numpy(s).cuda(), torch.from_numpy(z).cuda(),
+            None, None, None, G, 2, -1)
+
+    gate, up, down = [], [], []
+    for ex in experts:
+        q, s, z = ex["w13"]
+        gate.append(ctx(q[:ffn], s[:ffn], z[:ffn], ffn, hidden))
+        up.append(ctx(q[ffn:], s[ffn:], z[ffn:], ffn, hidden))
+        q, s, z = ex["w2"]
+        down.append(ctx(q, s, z, hidden, ffn))
+    out = torch.ops.torch_ipex.deepseek_moe_woq(hg, sel, gate, up, down, rw, False)
+    parity(bf16_numpy(out), ref)
+    # expert by expert through the per-expert operator: the same launches in the same order
+    out2 = torch.zeros_like(out)
+    expert_mask = torch.nn.functional.one_hot(sel, num_classes=E).permute(2, 1, 0)
+    for e in range(E):
+        j, top_x = torch.where(expert_mask[e])
+        out2 = torch.ops.torch_ipex.mixtral_moe_woq(hg, top_x, j, gate[e].get_data_handle(), up[e].get_data_handle(),
+                                                    down[e].get_data_handle(), rw, out2, False)
+    assert (out.float() - out2.float()).abs().max() <= 2.0 ** -7 * out2.float().abs().max()
+
+
 def test_config4_expert_shapes_one_token(env):
     """Full Mixtral-8x7B expert shapes (w13 28672x4096, w2 4096x14336), one token, two experts."""
     capi = env._capi

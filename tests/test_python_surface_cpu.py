@@ -90,3 +90,53 @@ def test_row_parallel_reduce_two_ranks_gloo(ipex):
         port = sock.getsockname()[1]
     mp.spawn(_tp_worker, args=(world, port, ret), nprocs=world, join=True)
     assert all(ret[r] for r in range(world))
+
+
+def test_checkpoint_tensor_conversions_on_cpu(ipex):
+    """The low-precision checkpoint loader's tensor conversions (no GPU needed): a GPTQ layer
+    with act-order comes out as plain nibbles with scales / zero points per output row, group
+    sizes are read off the tensors, and a block-scaled FP8 layer gets one scale per row and K block."""
+    import numpy as np
+
+    from ipex_b200.nn.modules.weight_only_quantization import WoqWeightFormat
+    from ipex_b200.utils.weight_only_quantization import _get_linear_parameters, _gptq_to_plain
+    from oracle import woq_oracle as O
+
+    n, k, g = 64, 256, 64
+    rng = np.random.default_rng(0)
+    q = rng.integers(0, 16, (n, k)).astype(np.uint32)
+    qT = q.T.reshape(k // 8, 8, n)
+    gq = np.zeros((k // 8, n), dtype=np.uint32)
+    for j in range(8):
+        gq |= qT[:, j, :] << (4 * j)
+    z = rng.integers(1, 16, (n, k // g))
+    zz = (z.T - 1) % 16
+    gz = np.zeros((k // g, n // 8), dtype=np.uint32)
+    for j in range(8):
+        gz |= zz[:, j::8].astype(np.uint32) << (4 * j)
+    s = (rng.random((k // g, n)) * 0.01 + 0.001).astype(np.float16)
+    tq, ts, tz = (torch.from_numpy(gq.view(np.int32)), torch.from_numpy(s), torch.from_numpy(gz.view(np.int32)))
+    # the oracle's reading of the same checkpoint words
+    np.testing.assert_array_equal(O.gptq_unpack_int32_rows(gq).T, q.astype(np.uint8))
+    plain, ps, pz = _gptq_to_plain(tq, ts.clone(), tz.clone())
+    np.testing.assert_array_equal(plain.numpy(), O.pack_nibbles(q.astype(np.uint8)))
+    np.testing.assert_array_equal(ps.float().numpy(), s.T.astype(np.float32))
+    np.testing.assert_array_equal(pz.float().numpy(), z.astype(np.float32))
+
+    g_idx = torch.from_numpy(rng.permutation(np.arange(k) // g).astype(np.int32))
+    sd = {"fc.qweight": tq, "fc.scales": ts, "fc.qzeros": tz, "fc.g_idx": g_idx}
+    w, sc, zp, b, group, gi, fmt = _get_linear_parameters("fc", sd, {"quant_method": "gptq"}, True)
+    assert group == g and gi is not None and fmt == WoqWeightFormat.PLAIN_FORMAT and w.dtype == torch.uint8
+    w, sc, zp, b, group, gi, fmt = _get_linear_parameters("fc", sd, {"quant_method": "gptq"}, False)
+    assert group == g and gi is None and fmt == WoqWeightFormat.GPTQ_FORMAT and w.dtype == torch.int32
+    natural = dict(sd, **{"fc.g_idx": torch.arange(k, dtype=torch.int32) // g})
+    assert _get_linear_parameters("fc", natural, {"quant_method": "gptq"}, True)[5] is None
+
+    w8 = torch.randn(200, 256).to(torch.float8_e4m3fn)
+    sinv = torch.rand(2, 2) + 0.5
+    w, sc, zp, b, group, gi, fmt = _get_linear_parameters(
+        "fc", {"fc.weight": w8, "fc.weight_scale_inv": sinv}, {"quant_method": "fp8", "weight_block_size": [128, 128]}, None)
+    assert w.dtype == torch.uint8 and sc.shape == (200, 2) and group == 128 and zp is None
+    assert torch.equal(sc[:128], sinv[0].expand(128, 2)) and torch.equal(sc[128:], sinv[1].expand(72, 2))
+    # a layer the checkpoint keeps in floating point
+    assert _get_linear_parameters("head", {"head.weight": torch.ones(4, 4)}, {"quant_method": "awq"}, None)[1] is None
