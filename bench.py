@@ -277,7 +277,11 @@ def verify_step(torch, dist, capi, L, p, rank, m, ws, hidden, resid, attn_slice,
     def compare(name, y, ref):
         mx, mr = _parity(torch, y, ref)
         worst[0], worst[1] = max(worst[0], mx), max(worst[1], mr)
-        if not (mx <= 1e-2 and mr <= 2e-3):
+        # The comparison arm sums the ranks' bf16 partials with NCCL in bf16, rounding after every
+        # addition (2.5e-3 mean relative at 8 ranks); the fused exchange adds them in fp32 and
+        # rounds once, like the yardstick.  The NCCL arm's row-parallel outputs get twice the bar.
+        bar = 4e-3 if (p > 1 and not fused and name in ("o_proj", "down_proj")) else 2e-3
+        if not (mx <= 1e-2 and mr <= bar):
             raise RuntimeError(f"bench check failed on rank {rank}: {name} max-abs/inf {mx:.3e}, mean-rel {mr:.3e}")
 
     qkv_ref = gather_ranks((hidden.float() @ deq(L["qkv"]).T).to(bf))
