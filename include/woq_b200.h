@@ -101,7 +101,7 @@ extern "C" {
  * (what the reference's Python loaders hand to weight_only_qlinear_prepack_int4). */
 #define WOQ_B200_LAYOUT_SCALES_NK 0x8
 /* woq_b200_ctx_create validates the zero points on the device.  Normally it waits for the
- * verdict (one stream synchronisation per context); with this flag the verdict travels to the
+ * outcome (one stream synchronisation per context); with this flag the outcome travels to the
  * host asynchronously and the first woq_b200_linear* call on the context reports it, so a
  * loader can create hundreds of contexts back to back.  The inputs must stay alive until the
  * stream has passed the create call either way.  Plain-format INT4 contexts only. */

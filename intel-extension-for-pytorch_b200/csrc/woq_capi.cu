@@ -82,7 +82,7 @@ struct woq_b200_ctx {
   int kc_per_tile;   // INT8: K / 128
   float* bias;       // fp32 [n] or null
   size_t wq_bytes, sz_bytes;
-  // Prepack verdict (bit 0: a zero point is not an integer in 0..127, bit 1: scales or zero
+  // Prepack check result (bit 0: a zero point is not an integer in 0..127, bit 1: scales or zero
   // points outside the range of the shift-free dequantiser).  With WOQ_B200_LAYOUT_DEFER_CHECK
   // the flag travels to pinned host memory asynchronously and is looked at by the first call
   // that needs it, so that loading many layers does not synchronise once per layer.
@@ -122,7 +122,7 @@ int check_ctx(const woq_b200_ctx* c) {
   return WOQ_B200_OK;
 }
 
-// Looks at a deferred prepack verdict once (see woq_b200_ctx::d_flag).
+// Looks at a deferred prepack check result once (see woq_b200_ctx::d_flag).
 int settle_prepack_flag(const woq_b200_ctx* cc) {
   woq_b200_ctx* c = const_cast<woq_b200_ctx*>(cc);
   if (c->flag_pending) {
@@ -684,7 +684,7 @@ int woq_b200_ctx_create(const woq_b200_desc* d, const void* qweight, const void*
   c->flag_pending = 1;
   c->plain_scales = 0;
   if (!(d->layout_flags & WOQ_B200_LAYOUT_DEFER_CHECK) || tmp_plain || tmp_zp) {
-    // look at the verdict now (the temporaries of a checkpoint format are freed below, which
+    // look at the result now (the temporaries of a checkpoint format are freed below, which
     // waits for the device anyway)
     if (int rc = settle_prepack_flag(c)) return cleanup(rc);
   }
