@@ -36,7 +36,7 @@ METRIC = "int4_woq_linear_weight_GBps_decode"
 # gate_up-sized launch (the device keeps 4 bytes of scale and zero point per row and group
 # against 3 algorithmic ones, and split-K partial tiles are written and read back); the
 # traffic of a launch grows in proportion to its bytes.
-TRAFFIC_RATIO = 1.041
+TRAFFIC_RATIO = 1.034
 FUSED_MAX_TOKENS = 8  # --collective auto: largest decode batch that takes the fused exchange
 UNIT = "GB/s"
 

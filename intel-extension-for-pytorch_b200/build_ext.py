@@ -52,7 +52,8 @@ def build(force=False):
         # libwoq_b200.so sits next to the final location, not there
         if not os.path.exists(built):
             raise
-    shutil.copyfile(built, OUT)
+    shutil.copyfile(built, OUT + ".new")
+    os.replace(OUT + ".new", OUT)  # never rewrite a library that a running process may have mapped
     open(STAMP, "w").write(digest)
     return OUT
 

@@ -60,12 +60,16 @@ def build(force=False, verbose=False):
     os.makedirs(OUT_DIR, exist_ok=True)
     extra = os.environ.get("WOQ_NVCC_EXTRA", "").split()
     cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else [])
-    cmd += [os.path.join(CSRC, s) for s in CUDA_SOURCES] + ["-o", LIB]
+    # link into a temporary name and rename: a process that has the old library mapped keeps its
+    # own copy instead of seeing the file change under it
+    tmp = LIB + ".new"
+    cmd += [os.path.join(CSRC, s) for s in CUDA_SOURCES] + ["-o", tmp]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building libwoq_b200.so")
+    os.replace(tmp, LIB)
     open(STAMP, "w").write(digest)
     return LIB
 
