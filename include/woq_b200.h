@@ -344,6 +344,30 @@ int woq_b200_moe_expert(const woq_b200_ctx* w13, const woq_b200_ctx* w2, const v
                         const int32_t* token_idx, const void* token_weight, int64_t tokens, void* out,
                         int64_t ld_out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* RMSNorm fused with the per-token activation quantiser of the INT8 path.  For every row of
+ * x (bf16 [m, k], k a multiple of 16):
+ *   y  = bf16(x * rsqrt(mean(x^2) + eps) * gamma)        fp32 arithmetic, one rounding; gamma bf16 [k]
+ *   qa = the int8 codes of y, sa its scale, zpa its zero point (asymmetric mode only), computed as
+ *        woq_b200_linear computes them for a context with the same act_quant_mode
+ *        (dynamic_quantize_per_block, csrc/cpu/aten/utils/woq_dynamic_quant.h:1526-1750)
+ * so that several linears which read the same normalised activations (q/k/v, gate/up) share one
+ * quantisation and y never makes a round trip through memory.  y may be null.
+ * act_quant_mode: WOQ_B200_ACT_PER_M or WOQ_B200_ACT_PER_M_SYM.  qa is [m, k] bytes (row stride k),
+ * sa [m] floats, zpa [m] int32.  This is a B200-side fusion: the reference runs the norm and the
+ * quantiser as separate steps (it has no fused form). */
+int woq_b200_rmsnorm_quant(const void* x, int64_t ldx, const void* gamma, float eps, int64_t m, int64_t k,
+                           int32_t act_quant_mode, void* y, int64_t ldy, void* qa, void* sa, void* zpa,
+                           void* stream);
+
+/* woq_b200_linear on activations that are already quantised (by woq_b200_rmsnorm_quant, or taken
+ * from woq_b200_int8_internals): codes qa [m, K], scales sa [m], zero points zpa [m] (null for the
+ * symmetric mode).  The context must be on the tcgen05 INT8 route (INT8 weights, lowp INT8) with a
+ * per-token act_quant_mode, and the codes must have been made in that mode.  Everything else
+ * (fusion, others, y, workspace of woq_b200_workspace_bytes(ctx, m) bytes) as in woq_b200_linear. */
+int woq_b200_linear_prequant(const woq_b200_ctx* ctx, const void* qa, const void* sa, const void* zpa, int64_t m,
+                             int32_t fusion, const void* const* others, int32_t n_others, void* y, int64_t ldy,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
 /* Parity hooks -------------------------------------------------------------------------
  * Dequantised weight [N, K] bf16 produced by the same device routine the tensor-core kernel
  * uses for its tiles (the reference's Dequantize<bfloat16>, csrc/cpu/aten/utils/woq.h:1501-1581). */

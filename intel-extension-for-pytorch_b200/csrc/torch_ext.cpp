@@ -394,6 +394,68 @@ at::Tensor woq_linear_mul(const at::Tensor& i, const at::Tensor& h, const std::v
   return run(from_handle(h), i, WOQ_B200_FUSE_MUL, {o[0]});
 }
 
+// B200-side fusion (the reference runs the norm and the activation quantiser as separate steps):
+// RMSNorm and the per-token INT8 quantiser in one kernel, so that the linears that read the same
+// normalised activations (q / k / v, gate / up) share one quantisation.  Returns (codes int8
+// [.., K], scales f32 [rows], zero points int32 [rows] - empty for the symmetric mode).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> woq_rmsnorm_quant(const at::Tensor& input, const at::Tensor& weight,
+                                                                 double eps, int64_t act_quant_mode) {
+  TORCH_CHECK(input.is_cuda() && input.scalar_type() == at::kBFloat16, "WOQ: rmsnorm_quant takes bf16 CUDA input");
+  const int64_t K = input.size(-1);
+  TORCH_CHECK(weight.numel() == K, "WOQ: the norm weight has ", weight.numel(), " elements, expected ", K);
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor x = input.reshape({-1, K});
+  if (x.stride(-1) != 1 || (x.stride(0) % 8) != 0 || (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15)) x = x.contiguous();
+  at::Tensor g = weight.to(input.device(), at::kBFloat16).contiguous();
+  const int64_t M = x.size(0);
+  auto sizes = input.sizes().vec();
+  at::Tensor qa = at::empty(sizes, x.options().dtype(at::kChar));
+  at::Tensor sa = at::empty({M}, x.options().dtype(at::kFloat));
+  const bool asym = act_quant_mode == WOQ_B200_ACT_PER_M;
+  at::Tensor zpa = at::empty({asym ? M : 0}, x.options().dtype(at::kInt));
+  auto stream = at::cuda::getCurrentCUDAStream(input.get_device());
+  WOQ_CHECK(woq_b200_rmsnorm_quant(x.data_ptr(), x.stride(0), g.data_ptr(), static_cast<float>(eps), M, K,
+                                   static_cast<int32_t>(act_quant_mode), nullptr, 0, qa.data_ptr(), sa.data_ptr(),
+                                   asym ? zpa.data_ptr() : nullptr, stream.stream()));
+  return std::make_tuple(qa, sa, zpa);
+}
+
+// The linear on activations quantised by woq_rmsnorm_quant; `fusion` as in the C ABI (0 none,
+// 0x100 silu*mul on a gate/up context, ...), `others` the extra operands of the binary post-ops.
+at::Tensor woq_linear_prequant(const at::Tensor& qa, const at::Tensor& sa, const at::Tensor& zpa,
+                               const at::Tensor& handle, int64_t fusion, const std::vector<at::Tensor>& others) {
+  WoqLinearOpContext* c = from_handle(handle);
+  TORCH_CHECK(qa.is_cuda() && qa.scalar_type() == at::kChar && qa.get_device() == c->device,
+              "WOQ: qa must be an int8 tensor on the weights' device");
+  const int64_t K = c->weight_shape[1], N = c->weight_shape[0];
+  TORCH_CHECK(qa.size(-1) == K, "WOQ: the last dimension of qa (", qa.size(-1), ") does not match in_features (", K, ")");
+  c10::cuda::CUDAGuard guard(c->device);
+  at::Tensor q2 = qa.reshape({-1, K}).contiguous();
+  const int64_t M = q2.size(0);
+  const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? N / 2 : N;
+  at::Tensor y = at::empty({M, n_out}, qa.options().dtype(at::kBFloat16));
+  std::vector<at::Tensor> oth;
+  std::vector<const void*> optr;
+  for (auto& o : others) {
+    at::Tensor t = o.reshape({-1, n_out});
+    TORCH_CHECK(t.size(0) == M, "WOQ: extra operand has ", t.size(0), " rows, expected ", M);
+    oth.push_back(t.to(at::kBFloat16).contiguous());
+    optr.push_back(oth.back().data_ptr());
+  }
+  auto stream = at::cuda::getCurrentCUDAStream(c->device);
+  if (M > 0) {
+    woq_b200_ctx* k = c->ctx_for(M);
+    at::Tensor& ws = workspace_for(c->device, stream.stream(), woq_b200_workspace_bytes(k, M));
+    WOQ_CHECK(woq_b200_linear_prequant(k, q2.data_ptr(), sa.data_ptr(), zpa.numel() ? zpa.data_ptr() : nullptr, M,
+                                       static_cast<int32_t>(fusion), optr.empty() ? nullptr : optr.data(),
+                                       static_cast<int32_t>(optr.size()), y.data_ptr(), y.stride(0), ws.data_ptr(),
+                                       ws.numel(), stream.stream()));
+  }
+  auto sizes = qa.sizes().vec();
+  sizes.back() = n_out;
+  return y.view(sizes);
+}
+
 // reference: csrc/cpu/aten/MoE.cpp:260-288 + kernels/MoEKrnl.cpp:254-285.  top_x = the tokens routed to
 // this expert, idx = which of their top-k slots; the three handles are the expert's w1 / w3 / w2.
 at::Tensor mixtral_moe_woq(const at::Tensor& hidden_states, const at::Tensor& top_x, const at::Tensor& idx,
@@ -658,6 +720,8 @@ TORCH_LIBRARY(torch_ipex, m) {
         "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext[] up_ctx, "
         "__torch__.torch.classes.ipex_prepack.WoqLinearOpContext[] down_ctx, "
         "Tensor routing_weights, bool is_distributed) -> Tensor");
+  m.def("woq_rmsnorm_quant(Tensor input, Tensor weight, float eps, int act_quant_mode) -> (Tensor, Tensor, Tensor)");
+  m.def("woq_linear_prequant(Tensor qa, Tensor sa, Tensor zpa, Tensor W_prepack, int fusion, Tensor[] others) -> Tensor");
   m.def("woq_check_status() -> ()", woq_check_status);
   m.def("woq_linear(Tensor input, Tensor qweight, str weight_dtype, int[] weight_shape, Tensor[] weight_scales, "
         "Tensor[]? weight_zeros, Tensor[]? bias, Tensor? g_idx, int group_size, int lowp_mode, "
@@ -677,6 +741,8 @@ TORCH_LIBRARY_IMPL(torch_ipex, CUDA, m) {
   m.impl("woq_linear", woq_linear);
   m.impl("mixtral_moe_woq", mixtral_moe_woq);
   m.impl("deepseek_moe_woq", deepseek_moe_woq);
+  m.impl("woq_rmsnorm_quant", woq_rmsnorm_quant);
+  m.impl("woq_linear_prequant", woq_linear_prequant);
 }
 
 TORCH_LIBRARY_IMPL(torch_ipex, AutocastCUDA, m) {

@@ -904,6 +904,49 @@ static int run_tc(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, 
   return WOQ_B200_OK;
 }
 
+// The tcgen05 int8 kernel, 256 tokens per launch, on activations that are already quantised:
+// codes qa [m, K], scales sa [m], zero points zpa [m] (null for the symmetric modes).
+static int run_int8_gemm(const woq_b200_ctx* c, const int8_t* qa, const float* sa, const int32_t* zpa, int64_t m,
+                         int32_t fusion, const void* o0, const void* o1, void* y, int64_t ldy, int32_t* acc_out,
+                         uint8_t* w8, size_t partial_off, cudaStream_t stream) {
+  const int64_t k = c->desc.k;
+  const int64_t mt = m < 256 ? m : 256;
+  const int n_tok = static_cast<int>((mt + 15) / 16 * 16);
+  CUtensorMap qamap;
+  if (int rc = make_kmajor_map(&qamap, qa, m, k, k, 1, n_tok)) return rc;
+  for (int64_t m0 = 0; m0 < m; m0 += 256) {
+    const int64_t mm = m - m0 < 256 ? m - m0 : 256;
+    woq::I8Params p{};
+    p.wq = reinterpret_cast<const int8_t*>(c->wq);
+    p.sw = c->scale_f32;
+    p.sa = sa + m0;
+    p.zpa = zpa ? zpa + m0 : nullptr;
+    p.comp = c->comp;
+    p.bias = c->bias;
+    p.y = y ? static_cast<__nv_bfloat16*>(y) + m0 * ldy : nullptr;
+    p.other0 = o0 ? static_cast<const __nv_bfloat16*>(o0) + m0 * ldy : nullptr;
+    p.other1 = o1 ? static_cast<const __nv_bfloat16*>(o1) + m0 * ldy : nullptr;
+    p.acc_out = acc_out ? acc_out + m0 * c->desc.n : nullptr;
+    p.status = reinterpret_cast<int*>(w8);
+    p.counters = reinterpret_cast<uint32_t*>(w8 + 256);
+    p.partials = w8 + partial_off;
+    p.ldy = ldy;
+    p.m = (int)mm;
+    p.n = (int)c->desc.n;
+    p.n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? (int)(c->desc.n / 2) : (int)c->desc.n;
+    p.m0 = (int)m0;
+    p.n_tok = n_tok;
+    p.tiles = c->tiles_tc;
+    p.kc_per_tile = c->kc_per_tile;
+    p.fusion = fusion;
+    p.gate_up = c->gate_up;
+    const int64_t total = static_cast<int64_t>(c->tiles_tc) * c->kc_per_tile;
+    const int grid = static_cast<int>(total < c->num_sms ? total : c->num_sms);
+    CUDA_TRY(woq::launch_int8_tc(p, qamap, grid, stream));
+  }
+  return WOQ_B200_OK;
+}
+
 // INT8 compute: quantise the activations per token, then the tcgen05 int8 kernel per 256 tokens
 static int run_int8(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx, int32_t fusion,
                     const void* o0, const void* o1, void* y, int64_t ldy, int8_t* qa_out, float* sa_out,
@@ -926,41 +969,7 @@ static int run_int8(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
   if (qa_out) CUDA_TRY(cudaMemcpyAsync(qa_out, qa, static_cast<size_t>(m) * k, cudaMemcpyDeviceToDevice, stream));
   if (sa_out) CUDA_TRY(cudaMemcpyAsync(sa_out, sa, static_cast<size_t>(m) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
   if (!y && !acc_out) return WOQ_B200_OK;
-  const int64_t mt = m < 256 ? m : 256;
-  const int n_tok = static_cast<int>((mt + 15) / 16 * 16);
-  CUtensorMap qamap;
-  if (int rc = make_kmajor_map(&qamap, qa, m, k, k, 1, n_tok)) return rc;
-  for (int64_t m0 = 0; m0 < m; m0 += 256) {
-    const int64_t mm = m - m0 < 256 ? m - m0 : 256;
-    woq::I8Params p{};
-    p.wq = reinterpret_cast<const int8_t*>(c->wq);
-    p.sw = c->scale_f32;
-    p.sa = sa + m0;
-    p.zpa = asym ? zpa + m0 : nullptr;
-    p.comp = c->comp;
-    p.bias = c->bias;
-    p.y = y ? static_cast<__nv_bfloat16*>(y) + m0 * ldy : nullptr;
-    p.other0 = o0 ? static_cast<const __nv_bfloat16*>(o0) + m0 * ldy : nullptr;
-    p.other1 = o1 ? static_cast<const __nv_bfloat16*>(o1) + m0 * ldy : nullptr;
-    p.acc_out = acc_out ? acc_out + m0 * c->desc.n : nullptr;
-    p.status = reinterpret_cast<int*>(w8);
-    p.counters = reinterpret_cast<uint32_t*>(w8 + 256);
-    p.partials = w8 + L.partial_off;
-    p.ldy = ldy;
-    p.m = (int)mm;
-    p.n = (int)c->desc.n;
-    p.n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? (int)(c->desc.n / 2) : (int)c->desc.n;
-    p.m0 = (int)m0;
-    p.n_tok = n_tok;
-    p.tiles = c->tiles_tc;
-    p.kc_per_tile = c->kc_per_tile;
-    p.fusion = fusion;
-    p.gate_up = c->gate_up;
-    const int64_t total = static_cast<int64_t>(c->tiles_tc) * c->kc_per_tile;
-    const int grid = static_cast<int>(total < c->num_sms ? total : c->num_sms);
-    CUDA_TRY(woq::launch_int8_tc(p, qamap, grid, stream));
-  }
-  return WOQ_B200_OK;
+  return run_int8_gemm(c, qa, sa, asym ? zpa : nullptr, m, fusion, o0, o1, y, ldy, acc_out, w8, L.partial_off, stream);
 }
 
 static bool use_tc_path(const woq_b200_ctx* c, int64_t m) {
@@ -1103,6 +1112,78 @@ int woq_b200_linear(const woq_b200_ctx* c, const void* x, int64_t m, int64_t ldx
       return rc;
   }
   return WOQ_B200_OK;
+}
+
+// ---- RMSNorm fused with the activation quantiser, and the linear on quantised activations ---
+int woq_b200_rmsnorm_quant(const void* x, int64_t ldx, const void* gamma, float eps, int64_t m, int64_t k,
+                           int32_t act_quant_mode, void* y, int64_t ldy, void* qa, void* sa, void* zpa,
+                           void* stream_) {
+  if (m == 0) return WOQ_B200_OK;
+  if (!x || !gamma || !qa || !sa) return fail(WOQ_B200_ERR_INVALID_ARG, "x, gamma, qa and sa must be non-null");
+  if (m < 0 || k <= 0 || (k % 16) != 0)
+    return fail(WOQ_B200_ERR_INVALID_ARG, "woq_b200_rmsnorm_quant needs M >= 0 and K a positive multiple of 16");
+  if (act_quant_mode != WOQ_B200_ACT_PER_M && act_quant_mode != WOQ_B200_ACT_PER_M_SYM)
+    return fail(WOQ_B200_ERR_UNSUPPORTED,
+                "woq_b200_rmsnorm_quant quantises per token (WOQ_B200_ACT_PER_M or _PER_M_SYM), got mode %d",
+                act_quant_mode);
+  const int asym = act_quant_mode == WOQ_B200_ACT_PER_M;
+  if (asym && !zpa) return fail(WOQ_B200_ERR_INVALID_ARG, "the asymmetric mode writes zero points: zpa is null");
+  if (ldx < k || (ldx % 8) != 0 || !aligned16(x) || !aligned16(gamma) || !aligned16(qa))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "x, gamma and qa must be 16-byte aligned, ldx >= K and ldx %% 8 == 0");
+  if (y && (ldy < k || (ldy % 8) != 0 || !aligned16(y)))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "y must be 16-byte aligned with ldy >= K and ldy %% 8 == 0");
+  CUDA_TRY(woq::launch_rmsnorm_quant(static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(gamma),
+                                     eps, (int)m, (int)k, asym, static_cast<__nv_bfloat16*>(y), ldy,
+                                     static_cast<int8_t*>(qa), static_cast<float*>(sa), static_cast<int32_t*>(zpa),
+                                     static_cast<cudaStream_t>(stream_)));
+  return WOQ_B200_OK;
+}
+
+int woq_b200_linear_prequant(const woq_b200_ctx* c, const void* qa, const void* sa, const void* zpa, int64_t m,
+                             int32_t fusion, const void* const* others, int32_t n_others, void* y, int64_t ldy,
+                             void* workspace, size_t workspace_bytes, void* stream_) {
+  if (int rc = check_ctx(c)) return rc;
+  if (m == 0) return WOQ_B200_OK;
+  if (!c->is_int8 || c->is_i8block || c->is_generic)
+    return fail(WOQ_B200_ERR_UNSUPPORTED,
+                "woq_b200_linear_prequant takes contexts on the tcgen05 INT8 route (INT8 weights, lowp INT8, "
+                "one activation scale per token)");
+  const int mode = c->desc.act_quant_mode;
+  if (mode != WOQ_B200_ACT_PER_M && mode != WOQ_B200_ACT_PER_M_SYM)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "the context quantises activations in mode %d, not per token", mode);
+  const bool asym = mode == WOQ_B200_ACT_PER_M;
+  if (!qa || !sa || !y || !workspace || m < 0 || (asym && !zpa))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "qa, sa, y and workspace must be non-null (zpa too for the asymmetric mode)");
+  if (!asym && zpa) return fail(WOQ_B200_ERR_INVALID_ARG, "the context's mode is symmetric: zpa must be null");
+  if (!aligned16(qa)) return fail(WOQ_B200_ERR_INVALID_ARG, "qa must be 16-byte aligned");
+  if (int rc = check_current_device(c)) return rc;
+  int need = 0;
+  switch (fusion) {
+    case WOQ_B200_FUSE_NONE: case WOQ_B200_FUSE_GELU_ERF: case WOQ_B200_FUSE_GELU_TANH:
+    case WOQ_B200_FUSE_RELU: case WOQ_B200_FUSE_SILU: need = 0; break;
+    case WOQ_B200_FUSE_ADD: case WOQ_B200_FUSE_MUL: need = 1; break;
+    case WOQ_B200_FUSE_ADD_ADD: need = 2; break;
+    case WOQ_B200_FUSE_SILU_MUL:
+      if (!c->gate_up)
+        return fail(WOQ_B200_ERR_INVALID_ARG, "silu_mul needs a context created with the gate/up layout");
+      break;
+    default: return fail(WOQ_B200_ERR_INVALID_ARG, "unexpected fusion type %#x", fusion);
+  }
+  if (n_others != need || (need > 0 && !others))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "fusion %#x takes %d extra tensors, got %d", fusion, need, n_others);
+  const void* o0 = need > 0 ? others[0] : nullptr;
+  const void* o1 = need > 1 ? others[1] : nullptr;
+  if ((need > 0 && !o0) || (need > 1 && !o1)) return fail(WOQ_B200_ERR_INVALID_ARG, "null extra tensor");
+  const int64_t n_out = fusion == WOQ_B200_FUSE_SILU_MUL ? c->desc.n / 2 : c->desc.n;
+  if (ldy < n_out) return fail(WOQ_B200_ERR_INVALID_ARG, "ldy smaller than the output width");
+  const Int8Workspace L = int8_ws_layout(c, m);
+  if (workspace_bytes < L.total)
+    return fail(WOQ_B200_ERR_WORKSPACE, "workspace has %zu bytes, need %zu", workspace_bytes, L.total);
+  if (c->tiles_tc > kMaxCounterTiles)
+    return fail(WOQ_B200_ERR_UNSUPPORTED, "N too large for the workspace header");
+  return run_int8_gemm(c, static_cast<const int8_t*>(qa), static_cast<const float*>(sa),
+                       static_cast<const int32_t*>(zpa), m, fusion, o0, o1, y, ldy, nullptr,
+                       static_cast<uint8_t*>(workspace), L.partial_off, static_cast<cudaStream_t>(stream_));
 }
 
 // ---- tensor-parallel exchange (one node, CUDA IPC) ---------------------------------------

@@ -184,6 +184,97 @@ __global__ void __launch_bounds__(256) quant_act_kernel(const __nv_bfloat16* x, 
   }
 }
 
+// RMSNorm fused with the per-token quantiser: one CTA per token row.
+//   y = bf16(x * rsqrt(mean(x^2) + eps) * gamma)   (fp32 arithmetic, one rounding)
+// and then exactly what quant_act_kernel does on y, without y making a round trip through
+// memory (it is written only when the caller wants it).  Three passes over the row, which
+// stays in L1 after the first.
+template <bool ASYM>
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __nv_bfloat16* x, int64_t ldx,
+                                                            const __nv_bfloat16* gamma, float eps, int k,
+                                                            __nv_bfloat16* y, int64_t ldy, int8_t* qa, float* sa,
+                                                            int32_t* zpa) {
+  __shared__ float red[16];
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const __nv_bfloat16* xr = x + static_cast<int64_t>(m) * ldx;
+  // pass 1: sum of squares
+  float ss = 0.f;
+  for (int i = tid * 8; i < k; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  ss = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) ss += red[i];
+  __syncthreads();
+  const float inv = rsqrtf(__fdiv_rn(ss, static_cast<float>(k)) + eps);
+  auto normed = [&](uint32_t xw, uint32_t gw, float& a, float& b) {
+    a = bf16_round(__uint_as_float(xw << 16) * inv * __uint_as_float(gw << 16));
+    b = bf16_round(__uint_as_float(xw & 0xffff0000u) * inv * __uint_as_float(gw & 0xffff0000u));
+  };
+  // pass 2: range of the normalised row (and y itself, if wanted)
+  float lo = INFINITY, hi = -INFINITY;
+  for (int i = tid * 8; i < k; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint4 g = *reinterpret_cast<const uint4*>(gamma + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a, b;
+      normed(w[j], gw[j], a, b);
+      lo = fminf(lo, fminf(a, b));
+      hi = fmaxf(hi, fmaxf(a, b));
+      out[j] = (__float_as_uint(a) >> 16) | (__float_as_uint(b) & 0xffff0000u);
+    }
+    if (y) *reinterpret_cast<uint4*>(y + static_cast<int64_t>(m) * ldy + i) = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+  block_min_max(lo, hi, red);
+  float scale, zp = 0.f;
+  if (ASYM) {
+    scale = __fdiv_rn(hi - lo, 255.0f);
+    const float z = -rintf(__fdiv_rn(lo, scale));
+    zp = z;
+    if (tid == 0) zpa[m] = scale > 0.f ? static_cast<int32_t>(z) : 0;
+  } else {
+    scale = __fdiv_rn(fmaxf(fabsf(hi), fabsf(lo)), 127.0f);
+  }
+  if (tid == 0) sa[m] = scale;
+  const float q_lo = ASYM ? 0.f : -128.f, q_hi = ASYM ? 255.f : 127.f;
+  int8_t* qr = qa + static_cast<int64_t>(m) * k;
+  // pass 3: codes
+  for (int i = tid * 8; i < k; i += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+    const uint4 g = *reinterpret_cast<const uint4*>(gamma + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint32_t out[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a, b;
+      normed(w[j], gw[j], a, b);
+      float ql = 0.f, qh = 0.f;
+      if (scale > 0.f) {
+        ql = fminf(fmaxf(rintf(__fdiv_rn(a, scale) + zp), q_lo), q_hi);
+        qh = fminf(fmaxf(rintf(__fdiv_rn(b, scale) + zp), q_lo), q_hi);
+      }
+      const uint32_t c = (static_cast<uint32_t>(static_cast<int>(ql)) & 0xffu) |
+                         ((static_cast<uint32_t>(static_cast<int>(qh)) & 0xffu) << 8);
+      out[j >> 1] |= c << ((j & 1) * 16);
+    }
+    *reinterpret_cast<uint2*>(qr + i) = make_uint2(out[0], out[1]);
+  }
+}
+
 // compensation[n] = sum over k of the weight codes of row n (plain [n][k] int8): what an
 // activation zero point contributes to every accumulator of that row.  One warp per row.
 __global__ void __launch_bounds__(256) weight_row_sum_kernel(const int8_t* w, int n, int k, int32_t* comp) {
@@ -648,6 +739,17 @@ cudaError_t launch_quant_act(const __nv_bfloat16* x, int64_t ldx, int m, int k, 
     quant_act_kernel<true><<<m, 256, 0, stream>>>(x, ldx, k, qa, sa, zpa, r, m);
   else
     quant_act_kernel<false><<<m, 256, 0, stream>>>(x, ldx, k, qa, sa, zpa, r, m);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_quant(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* gamma, float eps, int m,
+                                 int k, int asym, __nv_bfloat16* y, int64_t ldy, int8_t* qa, float* sa, int32_t* zpa,
+                                 cudaStream_t stream) {
+  if (asym)
+    rmsnorm_quant_kernel<true><<<m, 256, 0, stream>>>(x, ldx, gamma, eps, k, y, ldy, qa, sa, zpa);
+  else
+    rmsnorm_quant_kernel<false><<<m, 256, 0, stream>>>(x, ldx, gamma, eps, k, y, ldy, qa, sa, zpa);
   count_launch();
   return cudaGetLastError();
 }

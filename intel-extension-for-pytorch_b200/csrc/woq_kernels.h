@@ -164,6 +164,9 @@ cudaError_t launch_pad_scale(const void* src, float* dst, int n, int n_pad, int 
                              cudaStream_t stream);
 cudaError_t launch_quant_act(const __nv_bfloat16* x, int64_t ldx, int m, int k, int asym, int per_tensor,
                              int8_t* qa, float* sa, int32_t* zpa, float* range, cudaStream_t stream);
+cudaError_t launch_rmsnorm_quant(const __nv_bfloat16* x, int64_t ldx, const __nv_bfloat16* gamma, float eps, int m,
+                                 int k, int asym, __nv_bfloat16* y, int64_t ldy, int8_t* qa, float* sa, int32_t* zpa,
+                                 cudaStream_t stream);
 cudaError_t launch_weight_row_sum(const int8_t* plain, int n, int k, int32_t* comp, cudaStream_t stream);
 size_t int8_partial_bytes(int grid, int n_tok);
 cudaError_t launch_int8_tc(I8Params p, const CUtensorMap& qamap, int grid, cudaStream_t stream);

@@ -52,6 +52,8 @@ EXPORTS = [
     "woq_b200_moe_expert",
     "woq_b200_dump_dequant",
     "woq_b200_int8_internals",
+    "woq_b200_rmsnorm_quant",
+    "woq_b200_linear_prequant",
     "woq_b200_int8_block_internals",
     "woq_b200_int8_block_size",
     "woq_b200_ctx_route",
@@ -132,6 +134,8 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_moe_expert.argtypes = [vp, vp, vp, i64, vp, vp, i64, vp, i64, vp, sz, vp]
     L.woq_b200_dump_dequant.argtypes = [vp, vp, vp]
     L.woq_b200_int8_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, sz, vp]
+    L.woq_b200_rmsnorm_quant.argtypes = [vp, i64, vp, ctypes.c_float, i64, i64, i32, vp, i64, vp, vp, vp, vp]
+    L.woq_b200_linear_prequant.argtypes = [vp, vp, vp, vp, i64, i32, ctypes.POINTER(vp), i32, vp, i64, vp, sz, vp]
     L.woq_b200_int8_block_internals.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, vp, sz, vp]
     L.woq_b200_int8_block_size.argtypes = [vp]
     L.woq_b200_ctx_route.argtypes = [vp]
@@ -546,6 +550,23 @@ class WoqContext:
             )
         return qa, sa, acc
 
+    def linear_prequant(self, qa, sa, zpa=None, fusion: int = FUSE_NONE, others=(), out=None, workspace=None):
+        """woq_b200_linear_prequant: the linear on activations quantised beforehand (rmsnorm_quant)."""
+        m = qa.shape[0]
+        n_out = self.n // 2 if fusion == FUSE_SILU_MUL else self.n
+        y = out if out is not None else torch.empty((m, n_out), dtype=torch.bfloat16, device=self.device)
+        ws = workspace if workspace is not None else self.workspace(m)
+        oth = _others(others, m, n_out, y)
+        arr = (ctypes.c_void_p * max(len(oth), 1))(*[o.data_ptr() for o in oth])
+        with torch.cuda.device(self.device):
+            _check(
+                lib().woq_b200_linear_prequant(
+                    self._h, qa.data_ptr(), sa.data_ptr(), None if zpa is None else zpa.data_ptr(), m, fusion,
+                    arr, len(oth), y.data_ptr(), y.stride(0), ws.buf.data_ptr(), ws.nbytes, _stream(),
+                )
+            )
+        return y
+
     def int8_zero_points(self, m: int) -> torch.Tensor:
         """Activation zero points the latest INT8 call with m tokens left in this context's workspace."""
         zp = torch.empty((m,), dtype=torch.int32, device=self.device)
@@ -553,6 +574,30 @@ class WoqContext:
         with torch.cuda.device(self.device):
             _check(lib().woq_b200_int8_zero_points(self._h, m, zp.data_ptr(), ws.buf.data_ptr(), ws.nbytes, _stream()))
         return zp
+
+
+def rmsnorm_quant(x: torch.Tensor, gamma: torch.Tensor, eps: float, act_quant_mode: int = 6, want_y: bool = False):
+    """woq_b200_rmsnorm_quant on torch tensors: x bf16 [m, k], gamma bf16 [k].  Returns
+    (qa int8 [m, k], sa f32 [m], zpa int32 [m] or None, y bf16 [m, k] or None)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    m, k = x2.shape
+    dev = x.device
+    qa = torch.empty((m, k), dtype=torch.int8, device=dev)
+    sa = torch.empty((m,), dtype=torch.float32, device=dev)
+    zpa = torch.empty((m,), dtype=torch.int32, device=dev) if act_quant_mode == ACT_PER_M else None
+    y = torch.empty((m, k), dtype=torch.bfloat16, device=dev) if want_y else None
+    g = gamma.to(device=dev, dtype=torch.bfloat16).contiguous()
+    with torch.cuda.device(dev):
+        _check(
+            lib().woq_b200_rmsnorm_quant(
+                x2.data_ptr(), x2.stride(0), g.data_ptr(), float(eps), m, k, act_quant_mode,
+                None if y is None else y.data_ptr(), k, qa.data_ptr(), sa.data_ptr(),
+                None if zpa is None else zpa.data_ptr(), _stream(),
+            )
+        )
+    return qa, sa, zpa, y
 
 
 def moe_expert(w13: "WoqContext", w2: "WoqContext", hidden, token_idx, token_weight, out, workspace=None):

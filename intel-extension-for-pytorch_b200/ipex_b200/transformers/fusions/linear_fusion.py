@@ -73,10 +73,14 @@ class _IPEXlinearFusedGateUp(nn.Module):
     """One kernel for a stacked gate/up weight: y = silu(gate(x)) * up(x).  Not in the reference;
     numerically the same composition as _IPEXlinearSiluMul."""
 
-    def __init__(self, op_context, out_features):
+    is_gate_up = True
+
+    def __init__(self, op_context, out_features, lowp_mode=-1, act_quant_mode=-1):
         super().__init__()
         self._op_context = op_context
         self.out_features = out_features
+        self._lowp_mode = int(lowp_mode)
+        self._act_quant_mode = int(act_quant_mode)
 
     @classmethod
     def from_quantized(cls, qweight, dtype, shape, scales, zero_points, group_size, lowp_mode, act_quant_mode=-1):
@@ -86,7 +90,7 @@ class _IPEXlinearFusedGateUp(nn.Module):
         ctx = torch.ops.ipex_prepack.weight_only_qlinear_prepack_gate_up(
             qweight, int(dtype), list(shape), scales, zero_points, None, group_size, int(lowp_mode),
             int(act_quant_mode))
-        return cls(ctx, shape[0] // 2)
+        return cls(ctx, shape[0] // 2, lowp_mode, act_quant_mode)
 
     def forward(self, x):
         return torch.ops.torch_ipex.woq_linear_silu_mul(x, self._op_context.get_data_handle())

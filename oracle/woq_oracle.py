@@ -492,6 +492,17 @@ def linear_from_dequantised(x, w, bias=None, fusion: int = FUSE_NONE, others: Se
     return apply_post_op(y, fusion, others)
 
 
+def rmsnorm_bf16(x: np.ndarray, gamma: np.ndarray, eps: float) -> np.ndarray:
+    """y = bf16(x * rsqrt(mean(x^2) + eps) * gamma), fp32 arithmetic and one rounding: what stands in
+    front of the q/k/v and gate/up linears of a Llama-style block (stock torch rms_norm in the
+    reference's model rewrites; the reference has no fused norm + quantiser, this restates the
+    unfused pair for the B200 side's fusion).  x [M, K] and gamma [K] hold bf16 values."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    ms = (x * x).sum(axis=1, dtype=np.float32) / np.float32(x.shape[1])
+    inv = (np.float32(1.0) / np.sqrt(ms + np.float32(eps))).astype(np.float32)
+    return rne_bf16((x * inv[:, None]).astype(np.float32) * np.asarray(gamma, dtype=np.float32)[None, :])
+
+
 # ---------------------------------------------------------------------------------------
 # a8. Dynamic per-token activation quantisation (WoqLowpMode.INT8)
 # ---------------------------------------------------------------------------------------

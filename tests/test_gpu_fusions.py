@@ -362,3 +362,30 @@ def test_checkpoint_and_config_must_agree(ipex):
                                                    {"fc1.weight": torch.zeros(64, 64)}, {"quant_method": "gptq"})
     with pytest.raises(AssertionError, match="not supported"):
         _convert_woq_with_low_precision_checkpoint(TwoLinears(64, 64, False), qmap(ipex), {}, {"quant_method": "rtn"})
+
+
+def test_rmsnorm_quant_module_shares_one_quantisation(ipex):
+    """_IPEXRmsNormQuantLinears(norm, [q, k, v]) == the three INT8-compute linears on
+    rms_norm(x), each quantising for itself."""
+    from ipex_b200.transformers.fusions.norm_quant import _IPEXRmsNormQuantLinears
+
+    q = ipex.quantization
+    qm = q.get_weight_only_quant_qconfig_mapping(weight_dtype=q.WoqWeightDtype.INT8, lowp_mode=q.WoqLowpMode.INT8,
+                                                 act_quant_mode=q.WoqActQuantMode.PER_BATCH_SYM)
+    mods = [woq(ipex, make_linear(n, 1024, False, 70 + i), qm) for i, n in enumerate((1024, 256, 256))]
+    norm = nn.RMSNorm(1024, eps=1e-5)
+    with torch.no_grad():
+        norm.weight.copy_(torch.rand(1024) + 0.5)
+    norm = norm.cuda().bfloat16()
+    fused = _IPEXRmsNormQuantLinears(norm, mods)
+    x = (torch.randn(3, 5, 1024, device="cuda") * 2).bfloat16()
+    outs = fused(x)
+    assert len(outs) == 3 and outs[0].shape == (3, 5, 1024) and outs[1].shape == (3, 5, 256)
+    # reference: the library's own normalised rows, then every linear quantising for itself
+    _, _, _, y = ipex._capi.rmsnorm_quant(x, norm.weight, 1e-5, 6, want_y=True)
+    for got, mod in zip(outs, mods):
+        assert torch.equal(got, mod(y.view(3, 5, 1024)))
+    # and close to torch's own rms_norm feeding the same linears
+    y_t = torch.nn.functional.rms_norm(x.float(), (1024,), norm.weight.float(), 1e-5).bfloat16()
+    a, b = outs[0].float(), mods[0](y_t).float()
+    assert (a - b).abs().max() <= 0.02 * b.abs().max()

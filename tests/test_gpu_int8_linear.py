@@ -178,3 +178,69 @@ def test_other_int8_recipes_take_their_own_routes(capi):
         capi.WoqContext(qw[:, :96].contiguous(), s, None, None, 64, 96, capi.DTYPE_INT8, -1, capi.LOWP_INT8,
                         act_quant_mode=7)
     assert e.value.code == 2
+
+
+# --------------------------------------------------------------------------------------------
+# RMSNorm fused with the per-token quantiser; linears on quantised activations
+
+
+@pytest.mark.parametrize("mode_name", ["PER_M_SYM", "PER_M"])
+@pytest.mark.parametrize("m", [1, 7, 300])
+def test_rmsnorm_quant_feeds_the_int8_linear(capi, mode_name, m):
+    """woq_b200_rmsnorm_quant + woq_b200_linear_prequant against the unfused pair: the
+    normalised row is the oracle's rmsnorm (bf16, a last-bit difference allowed where the fp32
+    mean differs by summation order), its codes / scales / zero points are bit for bit those of
+    the library's own quantiser run on that row, and the linear on the shared codes equals the
+    linear that quantises for itself."""
+    mode = getattr(capi, "ACT_" + mode_name)
+    n, k = 384, 1024
+    rng = np.random.default_rng(40 + m)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    qw, s, _ = O.quantize_per_channel(w, O.WOQ_DTYPE_INT8, True)
+    ctx = capi.WoqContext(torch.from_numpy(qw).cuda(), torch.from_numpy(s).cuda(), None, None, n, k,
+                          capi.DTYPE_INT8, -1, capi.LOWP_INT8, act_quant_mode=mode)
+    x = O.rne_bf16((rng.standard_normal((m, k)) * 3.0 + 0.5).astype(np.float32))
+    gamma = O.rne_bf16((rng.random(k) + 0.5).astype(np.float32))
+    eps = 1e-5
+    xg, gg = bf16_tensor(x, "cuda"), bf16_tensor(gamma, "cuda")
+    qa, sa, zpa, y = capi.rmsnorm_quant(xg, gg, eps, mode, want_y=True)
+    y_ref = O.rmsnorm_bf16(x, gamma, eps)
+    y_np = bf16_numpy(y)
+    differ = y_np != y_ref
+    assert differ.mean() < 2e-3, differ.mean()
+    np.testing.assert_allclose(y_np, y_ref, rtol=2.0 ** -7, atol=0)
+    # the library's own quantiser on the same normalised rows
+    qa2, sa2, _ = ctx.int8_internals(y)
+    assert torch.equal(qa, qa2) and torch.equal(sa, sa2)
+    if mode == capi.ACT_PER_M:
+        assert torch.equal(zpa, ctx.int8_zero_points(m))
+    else:
+        assert zpa is None
+    # the linear on the shared codes equals the linear that quantises for itself
+    want = ctx.linear(y)
+    got = ctx.linear_prequant(qa, sa, zpa)
+    assert torch.equal(got, want)
+    resid = bf16_tensor(rng.standard_normal((m, n)).astype(np.float32), "cuda")
+    assert torch.equal(ctx.linear_prequant(qa, sa, zpa, capi.FUSE_ADD, [resid]), ctx.linear(y, capi.FUSE_ADD, [resid]))
+    # and the whole thing against the oracle
+    ref = O.woq_linear_int8(y_np, qw, s, None, act_mode=mode)
+    mx, mr = O.parity_metrics(bf16_numpy(got), ref)
+    assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)
+
+
+def test_rmsnorm_quant_rejects_what_it_cannot_do(capi):
+    x = torch.zeros((2, 64), dtype=torch.bfloat16, device="cuda")
+    g = torch.ones((64,), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(capi.WoqError, match="per token"):
+        capi.rmsnorm_quant(x, g, 1e-5, capi.ACT_PER_TENSOR_SYM)
+    with pytest.raises(capi.WoqError, match="multiple of 16"):
+        capi.rmsnorm_quant(x[:, :40].contiguous(), g[:40].contiguous(), 1e-5, capi.ACT_PER_M_SYM)
+    # a context that quantises per K block cannot take per-token codes
+    w = (np.random.default_rng(0).standard_normal((64, 128)) * 0.02).astype(np.float32)
+    qw, s, _ = O.quantize_per_channel(w, O.WOQ_DTYPE_INT8, True)
+    blk = capi.WoqContext(torch.from_numpy(qw).cuda(), torch.from_numpy(s).cuda(), None, None, 64, 128,
+                          capi.DTYPE_INT8, -1, capi.LOWP_INT8, act_quant_mode=capi.ACT_PER_M_K_BLOCK_SYM)
+    qa = torch.zeros((2, 128), dtype=torch.int8, device="cuda")
+    sa = torch.ones((2,), dtype=torch.float32, device="cuda")
+    with pytest.raises(capi.WoqError, match="tcgen05 INT8 route"):
+        blk.linear_prequant(qa, sa)
