@@ -271,6 +271,205 @@ __global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_kernel(const I8Blo
   p.y[o] = __float2bfloat16_rn(r);
 }
 
+// Many tokens: a CTA owns 64 rows x 64 tokens and walks the whole K.  Warp w keeps the weights of
+// its 16 rows of a k-step in registers and runs them against eight 8-token column blocks (the
+// four warps read the same activation codes, so three of the four reads hit L1); every warp sees
+// every K block, so there is nothing to add across warps.  Against the 16 x 8 kernel above this
+// reads the weights 8 times and the activation codes 4 times less often.
+constexpr int kWideTokBlocks = 8;
+constexpr int kWideTok = 8 * kWideTokBlocks;
+constexpr int kWideChunk = 32;             // K blocks whose per-token figures are staged at a time
+constexpr int kWideStride = kWideTok + 2;  // even (64-bit loads stay aligned), not a multiple of 32
+
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <bool W4, bool ASYM>
+__global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_wide_kernel(const I8BlockParams p) {
+  // Two stages of one 64-wide k-step each: the CTA's 64 weight rows (64 B each, 32 B for 4-bit
+  // weights) and the codes of its 64 tokens (64 B each), copied with 16-byte cp.async by all
+  // threads (four consecutive threads cover one row's chunk) and read back as MMA fragments.
+  // Rows are 64 B apart in shared memory: the two rows a quarter-warp reads together with one
+  // 128-bit load are 128 contiguous bytes, so the fragment loads have no bank conflicts.
+  constexpr int kWRow = W4 ? 32 : 64;
+  __shared__ __align__(16) uint8_t s_w[2][64 * kWRow];
+  __shared__ __align__(16) uint8_t s_a[2][kWideTok * 64];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row_lo = blockIdx.x * 64 + warp * 16 + g, row_hi = row_lo + 8;
+  const int tok0 = blockIdx.y * kWideTok;
+  const int r0 = row_lo < p.n ? row_lo : 0, r1 = row_hi < p.n ? row_hi : 0;
+  const size_t row_bytes = W4 ? p.k / 2 : p.k;
+  // column block nt: this lane feeds the codes of token tok0 + 8 nt + g and owns the accumulator
+  // columns of tokens tok0 + 8 nt + 2t, + 1; rows and tokens outside the problem read row / token 0
+  // this thread's 16-byte pieces of a stage: piece c -> (row or token c / 4 (c / 2 for 4-bit
+  // weights), 16-byte part c % 4 (c % 2))
+  constexpr int kWParts = kWRow / 16, kWPieces = 64 * kWParts / (kI8Warps * 32);
+  const uint8_t* src_w[kWPieces > 0 ? kWPieces : 1];
+  int dst_w[kWPieces > 0 ? kWPieces : 1];
+#pragma unroll
+  for (int j = 0; j < kWPieces; ++j) {
+    const int cidx = threadIdx.x + j * kI8Warps * 32, r = cidx / kWParts, part = cidx % kWParts;
+    const int gr = blockIdx.x * 64 + r;
+    src_w[j] = p.w + static_cast<size_t>(gr < p.n ? gr : 0) * row_bytes + part * 16;
+    dst_w[j] = r * kWRow + part * 16;
+  }
+  const uint8_t* src_a[2];
+  int dst_a[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int cidx = threadIdx.x + j * kI8Warps * 32, tk = cidx / 4, part = cidx % 4;
+    const int gt = tok0 + tk;
+    src_a[j] = p.qa + static_cast<size_t>(gt < p.m ? gt : 0) * p.k + part * 16;
+    dst_a[j] = tk * 64 + part * 16;
+  }
+  const int steps = p.k / 64;  // k-steps over the whole K (a K block is kb / 64 of them)
+  auto issue = [&](int step, int stage) {
+    const int koff = step * 64;
+#pragma unroll
+    for (int j = 0; j < kWPieces; ++j) cp_async16(&s_w[stage][dst_w[j]], src_w[j] + (W4 ? koff / 2 : koff));
+#pragma unroll
+    for (int j = 0; j < 2; ++j) cp_async16(&s_a[stage][dst_a[j]], src_a[j] + koff);
+    cp_async_commit();
+  };
+  issue(0, 0);
+  // C starts from the fp32 bias and takes the K blocks in order, as the reference does
+  const float b_lo = p.bias ? p.bias[r0] : 0.f, b_hi = p.bias ? p.bias[r1] : 0.f;
+  float c[kWideTokBlocks][4];
+#pragma unroll
+  for (int nt = 0; nt < kWideTokBlocks; ++nt) {
+    c[nt][0] = c[nt][1] = b_lo;
+    c[nt][2] = c[nt][3] = b_hi;
+  }
+
+  // scales, code sums and zero points of the CTA's 64 tokens for 32 K blocks at a time,
+  // transposed to [block][token]: the drain of a block reads them with two or three shared loads
+  // per column block instead of four to six global ones
+  __shared__ __align__(8) float s_sa[kWideChunk][kWideStride];
+  __shared__ __align__(8) int s_sq[kWideChunk][kWideStride];
+  __shared__ __align__(8) int s_zp[ASYM ? kWideChunk : 1][kWideStride];
+  for (int blk = 0; blk < p.kc; ++blk) {
+    if ((blk % kWideChunk) == 0) {
+      __syncthreads();  // everyone is done with the previous chunk
+      for (int i = threadIdx.x; i < kWideTok * kWideChunk; i += kI8Warps * 32) {
+        const int tok = i / kWideChunk, b = i % kWideChunk;
+        const int gt = tok0 + tok < p.m ? tok0 + tok : 0;
+        if (blk + b < p.kc) {
+          const size_t src = static_cast<size_t>(gt) * p.kc + blk + b;
+          s_sa[b][tok] = p.sa[src];
+          s_sq[b][tok] = p.sumqa[src];
+          if (ASYM) s_zp[b][tok] = p.zpa[src];
+        }
+      }
+      __syncthreads();
+    }
+    const int bl = blk % kWideChunk;
+    int acc[kWideTokBlocks][4];
+#pragma unroll
+    for (int nt = 0; nt < kWideTokBlocks; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
+    const int k0 = blk * p.kb;
+    for (int kk = 0; kk < p.kb; kk += 64) {
+      const int step = (k0 + kk) / 64, stage = step & 1;
+      // the next k-step goes into the other buffer (everyone left it at the end of the previous
+      // iteration) while this one is used
+      if (step + 1 < steps) {
+        issue(step + 1, stage ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      uint32_t a[8];  // A fragments of the two k32 MMAs: rows g and g + 8 of this warp's 16
+      const int wr = warp * 16 + g;
+      if (W4) {
+        const uint2 u = *reinterpret_cast<const uint2*>(&s_w[stage][wr * kWRow + 8 * t]);
+        const uint2 v = *reinterpret_cast<const uint2*>(&s_w[stage][(wr + 8) * kWRow + 8 * t]);
+        a[0] = u.x & 0x0f0f0f0fu; a[1] = v.x & 0x0f0f0f0fu; a[2] = (u.x >> 4) & 0x0f0f0f0fu; a[3] = (v.x >> 4) & 0x0f0f0f0fu;
+        a[4] = u.y & 0x0f0f0f0fu; a[5] = v.y & 0x0f0f0f0fu; a[6] = (u.y >> 4) & 0x0f0f0f0fu; a[7] = (v.y >> 4) & 0x0f0f0f0fu;
+      } else {
+        const uint4 u = *reinterpret_cast<const uint4*>(&s_w[stage][wr * kWRow + 16 * t]);
+        const uint4 v = *reinterpret_cast<const uint4*>(&s_w[stage][(wr + 8) * kWRow + 16 * t]);
+        a[0] = u.x; a[1] = v.x; a[2] = u.y; a[3] = v.y;
+        a[4] = u.z; a[5] = v.z; a[6] = u.w; a[7] = v.w;
+      }
+#pragma unroll
+      for (int nt = 0; nt < kWideTokBlocks; ++nt) {
+        const uint4 bv = *reinterpret_cast<const uint4*>(&s_a[stage][(8 * nt + g) * 64 + 16 * t]);
+        mma_i8<W4, ASYM>(acc[nt], a[0], a[1], a[2], a[3], bv.x, bv.y);
+        mma_i8<W4, ASYM>(acc[nt], a[4], a[5], a[6], a[7], bv.z, bv.w);
+      }
+      __syncthreads();  // the buffer may be overwritten by the copy issued in the next iteration
+    }
+    // the block's part of C, as in the 16 x 8 kernel
+    const int grp = p.group >= p.k ? 0 : k0 / p.group;
+    const float s0 = p.sw[static_cast<size_t>(r0) * p.groups + grp], s1 = p.sw[static_cast<size_t>(r1) * p.groups + grp];
+    const int z0 = static_cast<int>(p.zpw ? p.zpw[static_cast<size_t>(r0) * p.groups + grp] : p.default_zp);
+    const int z1 = static_cast<int>(p.zpw ? p.zpw[static_cast<size_t>(r1) * p.groups + grp] : p.default_zp);
+    int c0 = 0, c1 = 0;
+    if (ASYM) {
+      c0 = p.comp[static_cast<size_t>(r0) * p.kc + blk];
+      c1 = p.comp[static_cast<size_t>(r1) * p.kc + blk];
+    }
+#pragma unroll
+    for (int nt = 0; nt < kWideTokBlocks; ++nt) {
+      // tokens 8 nt + 2t and + 1 of the CTA (a token outside the problem holds token 0's figures)
+      const int2 sq = *reinterpret_cast<const int2*>(&s_sq[bl][8 * nt + 2 * t]);
+      const float2 sav = *reinterpret_cast<const float2*>(&s_sa[bl][8 * nt + 2 * t]);
+      const int sqa = sq.x, sqb = sq.y;
+      int v[4] = {acc[nt][0] - z0 * sqa, acc[nt][1] - z0 * sqb, acc[nt][2] - z1 * sqa, acc[nt][3] - z1 * sqb};
+      if (ASYM) {
+        const int2 zz = *reinterpret_cast<const int2*>(&s_zp[bl][8 * nt + 2 * t]);
+        const int za = zz.x, zb = zz.y;
+        v[0] -= c0 * za;
+        v[1] -= c0 * zb;
+        v[2] -= c1 * za;
+        v[3] -= c1 * zb;
+      }
+      if (p.acc_out) {
+        const int tc0 = tok0 + 8 * nt + 2 * t, tc1 = tc0 + 1;
+        int32_t* ao = p.acc_out + static_cast<size_t>(blk) * p.m * p.n;
+        if (row_lo < p.n && tc0 < p.m) ao[static_cast<size_t>(tc0) * p.n + row_lo] = v[0];
+        if (row_lo < p.n && tc1 < p.m) ao[static_cast<size_t>(tc1) * p.n + row_lo] = v[1];
+        if (row_hi < p.n && tc0 < p.m) ao[static_cast<size_t>(tc0) * p.n + row_hi] = v[2];
+        if (row_hi < p.n && tc1 < p.m) ao[static_cast<size_t>(tc1) * p.n + row_hi] = v[3];
+      }
+      const float sa_a = sav.x, sa_b = sav.y;
+      c[nt][0] += (static_cast<float>(v[0]) * sa_a) * s0;
+      c[nt][1] += (static_cast<float>(v[1]) * sa_b) * s0;
+      c[nt][2] += (static_cast<float>(v[2]) * sa_a) * s1;
+      c[nt][3] += (static_cast<float>(v[3]) * sa_b) * s1;
+    }
+  }
+  if (!p.y) return;
+#pragma unroll
+  for (int nt = 0; nt < kWideTokBlocks; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = (i & 2) ? row_hi : row_lo;
+      const int tok = tok0 + 8 * nt + 2 * t + (i & 1);
+      if (row >= p.n || tok >= p.m) continue;
+      float r = bf16_round(c[nt][i]);
+      const size_t o = static_cast<size_t>(tok) * p.ldy + row;
+      if (p.fusion == FUSE_ADD || p.fusion == FUSE_ADD_ADD) {
+        r = bf16_round(r + __bfloat162float(p.other0[o]));
+        if (p.fusion == FUSE_ADD_ADD) r = bf16_round(r + __bfloat162float(p.other1[o]));
+      } else if (p.fusion == FUSE_MUL) {
+        r = bf16_round(r * __bfloat162float(p.other0[o]));
+      } else {
+        r = unary_post_op(r, p.fusion);
+      }
+      p.y[o] = __float2bfloat16_rn(r);
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_act_block_quant(const __nv_bfloat16* x, int64_t ldx, int m, int k, int kb, int act_mode,
@@ -304,6 +503,23 @@ cudaError_t launch_weight_block_sum(const uint8_t* w, const float* zpw, int n, i
 }
 
 cudaError_t launch_i8_block(const I8BlockParams& p, cudaStream_t stream) {
+  if (p.m > 16) {
+    // 64 rows x 64 tokens per CTA
+    const dim3 wgrid(static_cast<unsigned>((p.n + 63) / 64), static_cast<unsigned>((p.m + kWideTok - 1) / kWideTok));
+    if (wgrid.y > 65535) return cudaErrorInvalidConfiguration;
+    if (p.w4) {
+      if (p.asym)
+        woq_i8_block_wide_kernel<true, true><<<wgrid, kI8Warps * 32, 0, stream>>>(p);
+      else
+        woq_i8_block_wide_kernel<true, false><<<wgrid, kI8Warps * 32, 0, stream>>>(p);
+    } else {
+      if (p.asym)
+        woq_i8_block_wide_kernel<false, true><<<wgrid, kI8Warps * 32, 0, stream>>>(p);
+      else
+        woq_i8_block_wide_kernel<false, false><<<wgrid, kI8Warps * 32, 0, stream>>>(p);
+    }
+    return cudaGetLastError();
+  }
   const dim3 grid(static_cast<unsigned>((p.n + 15) / 16), static_cast<unsigned>((p.m + 7) / 8));
   if (grid.y > 65535) return cudaErrorInvalidConfiguration;
   if (p.w4) {

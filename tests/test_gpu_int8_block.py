@@ -62,7 +62,7 @@ def test_internals_bit_exact_and_outputs(ipex, kind, n, k, g, mode):
     bias = (rng.standard_normal(n) * 0.1).astype(np.float32) if mode % 2 else None
     ctx = make_ctx(capi, qw, s, z, dt, n, k, g, mode, bias)
     assert ctx.route() == capi.ROUTE_INT8_BLOCK
-    for m in (1, 5, 8, 19):
+    for m in (1, 5, 8, 19, 70):  # up to 16 tokens the 16 x 8 kernel, above it the 64 x 64 one
         x = O.rne_bf16(make_acts(m, k, seed=m + mode) + (0.0 if mode >= 4 else 0.31))
         if m > 2:
             x[1, : O.int8_block_k(k, g)] = 0.0  # a block of zeros: scale 0, codes 0
@@ -85,13 +85,14 @@ def test_internals_bit_exact_and_outputs(ipex, kind, n, k, g, mode):
                                              (O.FUSE_ADD_ADD, 2), (O.FUSE_MUL, 1)])
 def test_post_ops(ipex, fusion, n_others):
     capi = ipex._capi
-    n, k, g, m = 160, 512, 128, 11
+    n, k, g = 160, 512, 128
     qw, s, z, dt = make_layer("int4", n, k, g, seed=fusion)
     ctx = make_ctx(capi, qw, s, z, dt, n, k, g, 7)
-    x = make_acts(m, k, seed=fusion + 1)
-    others = [make_acts(m, n, seed=30 + i) for i in range(n_others)]
-    y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda"), fusion, [bf16_tensor(o, "cuda") for o in others]))
-    parity(y, O.woq_linear_int8_blocks(x, qw, dt, s, z, None, g, 7, fusion, others))
+    for m in (11, 90):  # both kernels of the route
+        x = make_acts(m, k, seed=fusion + 1)
+        others = [make_acts(m, n, seed=30 + i) for i in range(n_others)]
+        y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda"), fusion, [bf16_tensor(o, "cuda") for o in others]))
+        parity(y, O.woq_linear_int8_blocks(x, qw, dt, s, z, None, g, 7, fusion, others))
 
 
 def test_llama_sized_layer_decode_and_prefill_tokens(ipex):
@@ -102,7 +103,7 @@ def test_llama_sized_layer_decode_and_prefill_tokens(ipex):
     qw, s, z, dt = make_layer("int4", n, k, g, seed=1)
     ctx = make_ctx(capi, qw, s, z, dt, n, k, g, 7)
     rows = np.arange(0, n, 13)
-    for m in (1, 8, 64):
+    for m in (1, 8, 64, 300):
         x = make_acts(m, k, seed=m)
         y = bf16_numpy(ctx.linear(bf16_tensor(x, "cuda")))[:, rows]
         ctx.workspace(m).status()
