@@ -278,7 +278,8 @@ __global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_kernel(const I8Blo
 // reads the weights 8 times and the activation codes 4 times less often.
 constexpr int kWideTokBlocks = 8;
 constexpr int kWideTok = 8 * kWideTokBlocks;
-constexpr int kWideChunk = 32;             // K blocks whose per-token figures are staged at a time
+constexpr int kWideChunk = 16;             // K blocks whose per-token figures are staged at a time
+constexpr int kWideStages = 4;             // k-steps in flight (cp.async ring)
 constexpr int kWideStride = kWideTok + 2;  // even (64-bit loads stay aligned), not a multiple of 32
 
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
@@ -292,14 +293,14 @@ __device__ __forceinline__ void cp_async_wait() {
 
 template <bool W4, bool ASYM>
 __global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_wide_kernel(const I8BlockParams p) {
-  // Two stages of one 64-wide k-step each: the CTA's 64 weight rows (64 B each, 32 B for 4-bit
+  // A ring of four stages of one 64-wide k-step each: the CTA's 64 weight rows (64 B each, 32 B for 4-bit
   // weights) and the codes of its 64 tokens (64 B each), copied with 16-byte cp.async by all
   // threads (four consecutive threads cover one row's chunk) and read back as MMA fragments.
   // Rows are 64 B apart in shared memory: the two rows a quarter-warp reads together with one
   // 128-bit load are 128 contiguous bytes, so the fragment loads have no bank conflicts.
   constexpr int kWRow = W4 ? 32 : 64;
-  __shared__ __align__(16) uint8_t s_w[2][64 * kWRow];
-  __shared__ __align__(16) uint8_t s_a[2][kWideTok * 64];
+  __shared__ __align__(16) uint8_t s_w[kWideStages][64 * kWRow];
+  __shared__ __align__(16) uint8_t s_a[kWideStages][kWideTok * 64];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int row_lo = blockIdx.x * 64 + warp * 16 + g, row_hi = row_lo + 8;
@@ -330,15 +331,20 @@ __global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_wide_kernel(const 
     dst_a[j] = tk * 64 + part * 16;
   }
   const int steps = p.k / 64;  // k-steps over the whole K (a K block is kb / 64 of them)
-  auto issue = [&](int step, int stage) {
-    const int koff = step * 64;
+  // one commit group per k-step, empty beyond the last, so that "all but the newest
+  // kWideStages - 2 groups have landed" always means "this iteration's step has landed"
+  auto issue = [&](int step) {
+    if (step < steps) {
+      const int koff = step * 64, stage = step % kWideStages;
 #pragma unroll
-    for (int j = 0; j < kWPieces; ++j) cp_async16(&s_w[stage][dst_w[j]], src_w[j] + (W4 ? koff / 2 : koff));
+      for (int j = 0; j < kWPieces; ++j) cp_async16(&s_w[stage][dst_w[j]], src_w[j] + (W4 ? koff / 2 : koff));
 #pragma unroll
-    for (int j = 0; j < 2; ++j) cp_async16(&s_a[stage][dst_a[j]], src_a[j] + koff);
+      for (int j = 0; j < 2; ++j) cp_async16(&s_a[stage][dst_a[j]], src_a[j] + koff);
+    }
     cp_async_commit();
   };
-  issue(0, 0);
+#pragma unroll
+  for (int st = 0; st < kWideStages - 1; ++st) issue(st);
   // C starts from the fp32 bias and takes the K blocks in order, as the reference does
   const float b_lo = p.bias ? p.bias[r0] : 0.f, b_hi = p.bias ? p.bias[r1] : 0.f;
   float c[kWideTokBlocks][4];
@@ -377,16 +383,10 @@ __global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_wide_kernel(const 
       for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
     const int k0 = blk * p.kb;
     for (int kk = 0; kk < p.kb; kk += 64) {
-      const int step = (k0 + kk) / 64, stage = step & 1;
-      // the next k-step goes into the other buffer (everyone left it at the end of the previous
-      // iteration) while this one is used
-      if (step + 1 < steps) {
-        issue(step + 1, stage ^ 1);
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
-      __syncthreads();
+      const int step = (k0 + kk) / 64, stage = step % kWideStages;
+      cp_async_wait<kWideStages - 2>();  // this step's copies of this thread have landed
+      __syncthreads();                   // ... everyone's have, and everyone has left the previous step's buffer
+      issue(step + kWideStages - 1);     // which is the buffer this copy goes to
       uint32_t a[8];  // A fragments of the two k32 MMAs: rows g and g + 8 of this warp's 16
       const int wr = warp * 16 + g;
       if (W4) {
@@ -406,7 +406,6 @@ __global__ void __launch_bounds__(kI8Warps * 32) woq_i8_block_wide_kernel(const 
         mma_i8<W4, ASYM>(acc[nt], a[0], a[1], a[2], a[3], bv.x, bv.y);
         mma_i8<W4, ASYM>(acc[nt], a[4], a[5], a[6], a[7], bv.z, bv.w);
       }
-      __syncthreads();  // the buffer may be overwritten by the copy issued in the next iteration
     }
     // the block's part of C, as in the 16 x 8 kernel
     const int grp = p.group >= p.k ? 0 : k0 / p.group;
