@@ -39,7 +39,7 @@ def make_experts(hidden, ffn, seed):
 
 def parity(y, y_ref):
     mx, mr = O.parity_metrics(y, y_ref)
-    assert mx <= O.MAX_ABS_TOL and mr <= 2 * O.MEAN_REL_TOL, (mx, mr)  # three chained roundings
+    assert mx <= O.MAX_ABS_TOL and mr <= O.MEAN_REL_TOL, (mx, mr)  # measured: at most 3e-6
 
 
 @pytest.mark.parametrize("tokens", [1, 16, 256])
