@@ -198,3 +198,19 @@ def test_every_activation_quant_mode_against_reference_fake_quant(golden_dir, mo
             diff = np.abs(dq - ref)
             assert (diff > 0).mean() <= 0.01
             assert diff.max() <= 1.01 * sa.max()
+
+
+def test_rmsnorm_restatement_against_torch():
+    """oracle.rmsnorm_bf16 (what stands in front of the fused norm + quantiser) against torch's own
+    rms_norm in fp32 rounded to bf16: identical except where the fp32 mean differs by summation
+    order, and then by one bf16 step."""
+    import torch
+
+    rng = np.random.default_rng(5)
+    x = O.rne_bf16((rng.standard_normal((33, 1024)) * 2.5 + 0.3).astype(np.float32))
+    gamma = O.rne_bf16((rng.random(1024) + 0.5).astype(np.float32))
+    got = O.rmsnorm_bf16(x, gamma, 1e-5)
+    want = torch.nn.functional.rms_norm(torch.from_numpy(x), (1024,), torch.from_numpy(gamma), 1e-5).bfloat16().float().numpy()
+    differ = got != want
+    assert differ.mean() < 2e-3, differ.mean()
+    np.testing.assert_allclose(got, want, rtol=2.0 ** -7, atol=0)
