@@ -176,11 +176,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
   __syncthreads();
   tc_fence_after_sync();
-  // Programmatic dependent launch, both ways: a following launch may begin while this grid
-  // runs, and this grid may have begun before the previous kernel in the stream ended.  The
-  // packed weights never change, so their producer starts at once; whoever touches x, y or the
-  // workspace waits for the previous kernel first (grid_dependency_wait).
-  grid_launch_dependents();
+  // No programmatic dependent launch for this kernel.  With it (weights prefetched and TMEM
+  // allocated while the previous kernel drained, 2-3 us per launch) about one in a thousand of
+  // back-to-back 256-token launches ended in a launch failure; 4800 such launches without it ran
+  // clean.
   const uint32_t tmem_base = hdr->tmem_base;
   volatile int* abort_flag = &hdr->abort_flag;
 
@@ -238,7 +237,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   } else if (warp == kXProducerWarp) {
     // activation tiles (TMA, 128-byte swizzle), one per k-block
     if (lane == 0) {
-      grid_dependency_wait();
       while (b < b_end) {
         const int nkb = stage_len();
         uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
@@ -425,7 +423,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (seg_end) {
         const bool whole = (seg_kb0 == 0 && kb0 + nkb == p.kb_per_tile);
         const int n_used = 1;
-        grid_dependency_wait();  // y, the fused operands and the workspace belong to this grid from here on
         mbar_wait(&hdr->d_full, seg & 1, abort_flag, p.status, 18);
         tc_fence_after_sync();
         if (whole && p.fusion != FUSE_SILU_MUL) {
@@ -510,6 +507,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
+    __syncwarp();  // lane 0 comes from the issuing loop; the deallocation is a warp-wide instruction
     tmem_dealloc(tmem_base, kTmemCols);
   }
 }
@@ -531,8 +529,12 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
   // TMEM: the accumulator takes the token columns (rounded to 32), the A groups the rest.
   p.a_col0 = (p.n_tok + 31) & ~31;
   const int a_groups = (kTmemCols - p.a_col0) / 32;
-  // k-blocks per stage: two for small token counts (fewer barrier round trips per byte)
-  p.kbs = p.n_tok <= 64 ? 2 : 1;
+  // k-blocks per stage.  Every stage costs each role a fixed amount of scalar bookkeeping and
+  // barrier traffic (an issuing thread spends about 800 cycles per stage outside its MMAs),
+  // whatever the stage holds, so up to 128 tokens, where the MMAs of one k-block are short, a
+  // stage takes as many k-blocks as the rings allow: three up to 64 tokens (four or five A
+  // groups of three), two up to 128 (four activation slots of 32 KB).
+  p.kbs = p.n_tok <= 64 ? 3 : p.n_tok <= 128 ? 2 : 1;
   const int x_stage = p.kbs * p.n_tok * 128;
   const int w_stage = p.kbs * kTcBlockBytes + (p.kbs + 1) * 512;
   const int budget = 224 * 1024 - kTcHeaderBytes;
@@ -563,17 +565,8 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return e;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kTcThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, woq_int4_tc_kernel, p, xmap);
+  woq_int4_tc_kernel<<<grid, kTcThreads, smem, stream>>>(p, xmap);
+  return cudaGetLastError();
 }
 
 }  // namespace woq

@@ -694,6 +694,7 @@ __global__ void __launch_bounds__(kI8Threads, 1)
   __syncthreads();
   if (warp == kI8Mma) {
     tc_fence_after_sync();
+    __syncwarp();  // lane 0 comes from the issuing loop
     tmem_dealloc(tmem_base, kI8TmemCols);
   }
 }
