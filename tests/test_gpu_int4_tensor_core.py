@@ -130,11 +130,32 @@ def test_repeatable(capi):
         assert torch.equal(ctx.linear(x), y0)
 
 
+def test_many_full_width_launches_in_a_row(capi):
+    """Several hundred 256-token launches on two weight copies with nothing between them: every
+    one completes (the status word stays clear) and gives the bits of the first."""
+    layers = [make_int4_layer(8192, 4096, 128, seed=70 + i) for i in range(2)]
+    ctxs = [make_ctx(capi, layer) for layer in layers]
+    x = bf16_tensor(make_acts(256, 4096, seed=3), "cuda")
+    ws = capi.Workspace(ctxs[0].workspace_bytes(256), "cuda")
+    outs = [torch.empty((256, 8192), dtype=torch.bfloat16, device="cuda") for _ in ctxs]
+    want = []
+    for c, out in zip(ctxs, outs):
+        c.linear(x, out=out, workspace=ws)
+        want.append(out.clone())
+    for _ in range(200):
+        for c, out in zip(ctxs, outs):
+            c.linear(x, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    ws.status()
+    for out, w in zip(outs, want):
+        assert torch.equal(out, w)
+
+
 @pytest.mark.parametrize("m", [24, 200])
-def test_dependent_launches_back_to_back(capi, m):
+def test_launches_back_to_back(capi, m):
     """A chain in which every linear reads the previous one's output and all share one workspace,
-    launched without host synchronisation (the launches may overlap under programmatic dependent
-    launch) and as a CUDA graph: same bits as the chain with a synchronisation after every launch."""
+    launched without host synchronisation and as a CUDA graph: same bits as the chain with a
+    synchronisation after every launch."""
     dims = [(1024, 512), (768, 1024), (512, 768), (1024, 512)]
     layers = [make_int4_layer(n, k, 128, seed=900 + i, std=0.05) for i, (n, k) in enumerate(dims)]
     ctxs = [make_ctx(capi, layer) for layer in layers]
