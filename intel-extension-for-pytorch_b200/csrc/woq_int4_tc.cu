@@ -554,9 +554,18 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
     w_ring = (budget - stages * x_stage) / w_stage;
     if (w_ring > kMaxWRing) w_ring = kMaxWRing;
   }
-  // A warpgroup works on every fourth stage.  With fewer than four slots in a ring it could
-  // reach a slot two uses ahead of the producer or of the MMA warp, and a parity wait cannot
-  // tell those apart.
+  // A parity wait cannot tell a barrier that is one completion short from one that is three
+  // short, so whoever waits for use u of a slot must know that use u - 1 has completed.
+  //  - A group / activation ring: a warpgroup works on every fourth stage and reaches stage s only
+  //    after stage s - 4, whose wait covered the MMAs of stage s - 4 - stages; the MMAs complete in
+  //    order, so with at least four slots the previous use (stage s - stages) has completed.
+  //  - packed-weight ring: nothing orders the landing of one stage's weights against a warpgroup
+  //    that works on other stages, so its length is a multiple of four: every slot then belongs to
+  //    one warpgroup, which has itself waited for the slot's previous use.  (A ring of six beside
+  //    four warpgroups let a warpgroup find, about once in a thousand 256-token launches, a slot
+  //    whose previous load had not landed yet: it read the use before that, released the slot
+  //    early, and the launch ended in a time-out or a launch failure.)
+  w_ring &= ~3;
   if (stages < 4 || w_ring < 4) return cudaErrorInvalidConfiguration;
   p.w_ring = w_ring;
   p.stages = stages;
