@@ -6,14 +6,14 @@
 // tokens] accumulated in fp32 in TMEM over the whole K of its share.
 //
 //   warp 16     producer: bulk copies of packed nibbles + group scales;
-//   warp 18     producer: TMA tile loads of x (128-byte swizzled K-major rows) - all copies
+//   warp 17     producer: TMA tile loads of x (128-byte swizzled K-major rows) - all copies
 //               complete on mbarriers;
 //   warps 0-15  dequantise: thread = output row.  Two 128-bit shared loads give the row's 64
 //               nibbles of a k-block; each becomes bf16((q - zp) * bf16(scale)) exactly (the
 //               reference's tile dequantiser) and the 32 packed registers go straight to
 //               TMEM with one tcgen05.st - the dequantised tile never touches shared memory.
 //               Consecutive stages go round-robin to the four warpgroups;
-//   warps 17,19 one thread each issues tcgen05.mma (A from TMEM, B from shared memory) for
+//   warps 18,19 one thread each issues tcgen05.mma (A from TMEM, B from shared memory) for
 //               alternate stages: per stage one wait (the A group is written and the x
 //               tiles have landed) and one tcgen05.commit that frees the stage's buffers and
 //               its A group together;
@@ -21,6 +21,11 @@
 //               either the fused post-op and store, or - when the CTA saw only part of K -
 //               a partial tile in the workspace that the last contributor sums in a fixed
 //               order.
+// Scalar bookkeeping is what the single-thread roles and the stage hand-overs are made of, and a
+// lone thread gets through only one dependent instruction every 10-15 cycles beside sixteen busy
+// warps.  So every role keeps its own few 32-bit counters (k-blocks left in the tile and in the
+// CTA's share, ring slot and parity), and a dequantising warpgroup steps from one of its stages
+// straight to the next one, four stages on, instead of walking the stages between.
 // Two rings.  The packed weights travel through a shared-memory ring of up to 32 slots that
 // the dequantising warps free as soon as they have the nibbles in registers; the dequantised
 // A groups (TMEM) and the activation tiles form a second, shorter ring freed by the MMAs'
@@ -29,8 +34,6 @@
 // 64-column one.  Weight bytes in flight per SM are bounded by shared memory (about 100 KB
 // and more for up to 128 tokens), not by TMEM.
 // Work split: the (tile, k-block) sequence is cut into equal contiguous shares, one per SM.
-#include <cstdlib>
-
 #include "woq_kernels.h"
 #include "woq_tc_common.cuh"
 
@@ -40,9 +43,9 @@ namespace {
 
 constexpr int kDequantWarps = 16;
 constexpr int kWarpGroups = kDequantWarps / 4;
-constexpr int kTcThreads = (kDequantWarps + 4) * 32;
-constexpr int kProducerWarp = kDequantWarps, kMmaWarp = kDequantWarps + 1, kXProducerWarp = kDequantWarps + 2,
-              kMmaWarp2 = kDequantWarps + 3;
+constexpr int kIssuers = 2;  // threads that issue MMAs, each in a warp of its own
+constexpr int kTcThreads = (kDequantWarps + 2 + kIssuers) * 32;
+constexpr int kProducerWarp = kDequantWarps, kXProducerWarp = kDequantWarps + 1, kMmaWarp = kDequantWarps + 2;
 constexpr int kDCol0 = 0;            // accumulator columns [0, a_col0)
 constexpr int kTmemCols = 512;       // A groups (32 columns = one k-block of bf16 A) fill the rest
 constexpr int kMaxTcStages = 16;     // A-group / activation ring
@@ -54,7 +57,7 @@ struct TcHeader {
   uint64_t w_free[kMaxWRing];     // the four dequantising warps have read the slot
   uint64_t full[kMaxTcStages];    // A group written (4 warps) and x tiles landed (1 + bytes)
   uint64_t free_[kMaxTcStages];   // the stage's MMAs have completed: A group and x tiles may be reused
-  uint64_t issued[2];             // MMA warp t has issued the MMAs of its latest stage
+  uint64_t issued[kIssuers];      // MMA thread t has issued the MMAs of its latest stage
   uint64_t d_full, d_empty;
   uint32_t tmem_base;
   int abort_flag;
@@ -161,9 +164,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       mbar_init(&hdr->w_full[s], 1);
       mbar_init(&hdr->w_free[s], 4);
     }
-    mbar_init(&hdr->issued[0], 1);
-    mbar_init(&hdr->issued[1], 1);
-    mbar_init(&hdr->d_full, 2);
+    for (int t = 0; t < kIssuers; ++t) mbar_init(&hdr->issued[t], 1);
+    mbar_init(&hdr->d_full, kIssuers);
     mbar_init(&hdr->d_empty, kDequantWarps);
     hdr->abort_flag = 0;
     hdr->is_last = 0;
@@ -176,127 +178,147 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
   __syncthreads();
   tc_fence_after_sync();
-  // No programmatic dependent launch for this kernel.  With it (weights prefetched and TMEM
-  // allocated while the previous kernel drained, 2-3 us per launch) about one in a thousand of
-  // back-to-back 256-token launches ended in a launch failure; 4800 such launches without it ran
-  // clean.
+  // No programmatic dependent launch for this kernel (measured: 2-3 us per launch from the weights
+  // prefetched and TMEM allocated while the previous kernel drained; not kept).
   const uint32_t tmem_base = hdr->tmem_base;
   volatile int* abort_flag = &hdr->abort_flag;
 
-  // every role walks the same sequence of stages; a stage is up to `kbs` k-blocks of one tile.
-  // Stage `it` uses pipeline slot it % stages: its shared-memory buffers and the A group (kbs *
-  // 32 TMEM columns) of the same index.
-  int tile = static_cast<int>(b_begin / p.kb_per_tile);
-  int kb0 = static_cast<int>(b_begin % p.kb_per_tile);
-  int64_t b = b_begin;
-  int slot = 0;
-  uint32_t phase = 0;       // parity of the current use of `slot`
-  int wslot = 0;            // the same stage's slot in the weight ring
-  uint32_t wphase = 0;
-  auto stage_len = [&]() {
-    int nkb = p.kb_per_tile - kb0;
-    if (nkb > p.kbs) nkb = p.kbs;
-    if (nkb > b_end - b) nkb = static_cast<int>(b_end - b);
-    return nkb;
-  };
-  auto advance = [&](int nkb) {
-    b += nkb;
-    kb0 += nkb;
-    if (kb0 == p.kb_per_tile) {
-      kb0 = 0;
-      ++tile;
-    }
-    if (++slot == p.stages) {
-      slot = 0;
-      phase ^= 1;
-    }
-    if (++wslot == p.w_ring) {
-      wslot = 0;
-      wphase ^= 1;
-    }
-  };
+  // Every role walks the same sequence of stages; a stage is up to `kbs` k-blocks of one tile and
+  // never crosses a tile end or the end of the CTA's share.  Stage number s uses slot s % stages
+  // of the A-group / activation ring (shared-memory tiles and kbs * 32 TMEM columns) and slot
+  // s % w_ring of the packed-weight ring.
+  const int kbpt = p.kb_per_tile, kbs = p.kbs, n_stages = p.stages, n_wring = p.w_ring;
+  const int tile0 = static_cast<int>(b_begin / kbpt);
+  const int kb00 = static_cast<int>(b_begin % kbpt);
+  const int rem0 = static_cast<int>(b_end - b_begin);
 
   if (warp == kProducerWarp) {
     // packed weights and their group scales
     if (lane == 0) {
-      while (b < b_end) {
-        const int nkb = stage_len();
+      int tile = tile0, kb0 = kb00, rem = rem0, wslot = 0;
+      uint32_t wphase = 0;
+      while (rem > 0) {
+        int nkb = kbpt - kb0;
+        if (nkb > kbs) nkb = kbs;
+        if (nkb > rem) nkb = rem;
         uint8_t* ws = w_stages + static_cast<size_t>(wslot) * w_stage_bytes;
         const int g0 = kb0 >> p.kbpg_shift;
         const int ng = ((kb0 + nkb - 1) >> p.kbpg_shift) - g0 + 1;
         mbar_wait(&hdr->w_free[wslot], wphase ^ 1, abort_flag, p.status, 11);
         mbar_arrive_expect_tx(&hdr->w_full[wslot], nkb * kTcBlockBytes + ng * 512);
-        bulk_g2s(ws, p.wq + (static_cast<size_t>(tile) * p.kb_per_tile + kb0) * kTcBlockBytes,
+        bulk_g2s(ws, p.wq + (static_cast<size_t>(tile) * kbpt + kb0) * kTcBlockBytes,
                  nkb * kTcBlockBytes, &hdr->w_full[wslot]);
-        bulk_g2s(ws + p.kbs * kTcBlockBytes,
+        bulk_g2s(ws + kbs * kTcBlockBytes,
                  p.sz + (static_cast<size_t>(tile) * p.groups + g0) * kTcTileN, ng * 512,
                  &hdr->w_full[wslot]);
-        advance(nkb);
+        kb0 += nkb;
+        rem -= nkb;
+        if (kb0 == kbpt) {
+          kb0 = 0;
+          ++tile;
+        }
+        if (++wslot == n_wring) {
+          wslot = 0;
+          wphase ^= 1;
+        }
       }
     }
   } else if (warp == kXProducerWarp) {
     // activation tiles (TMA, 128-byte swizzle), one per k-block
     if (lane == 0) {
-      while (b < b_end) {
-        const int nkb = stage_len();
+      int kb0 = kb00, rem = rem0, slot = 0;
+      uint32_t phase = 0;
+      while (rem > 0) {
+        int nkb = kbpt - kb0;
+        if (nkb > kbs) nkb = kbs;
+        if (nkb > rem) nkb = rem;
         uint8_t* xs = x_stages + static_cast<size_t>(slot) * x_stage_bytes;
         mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 12);
         mbar_arrive_expect_tx(&hdr->full[slot], nkb * p.n_tok * 128);
         for (int j = 0; j < nkb; ++j)
           tma_load_2d(xs + j * p.n_tok * 128, &xmap, (kb0 + j) * kBlockK, p.m0, &hdr->full[slot]);
-        advance(nkb);
+        kb0 += nkb;
+        rem -= nkb;
+        if (kb0 == kbpt) kb0 = 0;
+        if (++slot == n_stages) {
+          slot = 0;
+          phase ^= 1;
+        }
       }
     }
-  } else if (warp == kMmaWarp || warp == kMmaWarp2) {
+  } else if (warp >= kMmaWarp) {
     if (lane == 0) {
-      // Two threads issue the MMAs, one the even stages and one the odd ones.  Issuing an MMA
-      // blocks the thread while the tensor core is busy, and the waits and commits around a
-      // stage cost about as much again; with two threads one of them has always finished its
-      // wait when the other has issued its last MMA.  A token (`issued`) keeps the stages in
-      // order, so the MMA that starts a tile's accumulator runs before any that adds to it.
-      const int me = warp == kMmaWarp ? 0 : 1;
+      // The issuing threads take the stages in turn.  Issuing an MMA blocks the thread while the
+      // tensor core is busy, and the waits, the commit and the bookkeeping around a stage cost
+      // about as much again; with two threads one of them has finished its wait when the other
+      // has issued its last MMA (one thread alone: 5-25 % slower at every token count).  A token
+      // (`issued`) keeps the stages in order, so the MMA that starts a tile's accumulator runs
+      // before any that adds to it.
+      const int me = warp - kMmaWarp;
+      const int before_me = (me + kIssuers - 1) % kIssuers;
+      int turn = 0;  // whose stage the current one is
+      int mst = 0;   // stage number within this CTA
       const uint32_t idesc = umma_idesc(p.n_tok, /*bf16*/ 1, /*bf16*/ 1, /*f32*/ 1);
       const uint64_t desc_hi = umma_desc_k128(0) & 0xffffffff00000000ull;
       const uint32_t x_base_lo = (smem_u32(x_stages) & 0x3FFFFu) >> 4;
       const uint32_t x_stage_lo = static_cast<uint32_t>(x_stage_bytes) >> 4;
       const uint32_t x_blk_lo = static_cast<uint32_t>(p.n_tok * 128) >> 4;
       const uint32_t d_addr = tmem_base + kDCol0;
+      const uint32_t a_base = tmem_base + p.a_col0;
+      const uint32_t a_stage = static_cast<uint32_t>(kbs * 32);
       uint32_t seg = 0;
       bool first_of_segment = true;
-      int mst = 0;  // stage number within this CTA
-      while (b < b_end) {
-        const int nkb = stage_len();
-        const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
-        if ((mst & 1) == me) {
+      int kb0 = kb00, rem = rem0, slot = 0;
+      uint32_t phase = 0;
+      uint32_t a_addr = a_base, b_lo = x_base_lo;  // of the current slot
+      while (rem > 0) {
+        int nkb = kbpt - kb0;
+        if (nkb > kbs) nkb = kbs;
+        if (nkb > rem) nkb = rem;
+        if (turn == me) {
           mbar_wait(&hdr->full[slot], phase, abort_flag, p.status, 13);
           if (first_of_segment) mbar_wait(&hdr->d_empty, (seg & 1) ^ 1, abort_flag, p.status, 15);
-          // the previous stage's MMAs have been issued (by the other thread)
-          if (mst > 0) mbar_wait(&hdr->issued[me ^ 1], ((mst - 1) >> 1) & 1, abort_flag, p.status, 14);
+          // the previous stage's MMAs have been issued (by the thread before this one)
+          if (mst > 0) mbar_wait(&hdr->issued[before_me], ((mst - 1) / kIssuers) & 1, abort_flag, p.status, 14);
           tc_fence_after_sync();
           uint32_t accumulate = first_of_segment ? 0u : 1u;
-          uint32_t a_addr = tmem_base + p.a_col0 + slot * (p.kbs * 32);
-          uint32_t b_lo = x_base_lo + slot * x_stage_lo;
+          uint32_t a = a_addr, bl = b_lo;
           for (int j = 0; j < nkb; ++j) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_f16_ts(d_addr, a_addr + ks * 8, desc_hi | (b_lo + ks * 2), idesc, accumulate);
+              umma_f16_ts(d_addr, a + ks * 8, desc_hi | (bl + ks * 2), idesc, accumulate);
               accumulate = 1;
             }
-            a_addr += 32;
-            b_lo += x_blk_lo;
+            a += 32;
+            bl += x_blk_lo;
           }
           mbar_arrive(&hdr->issued[me]);
           tc_commit(&hdr->free_[slot]);
         }
+        kb0 += nkb;
+        rem -= nkb;
         first_of_segment = false;
-        if (seg_end) {
-          // both threads: everything this thread issued for the segment is tracked
+        if (kb0 == kbpt || rem == 0) {
+          // Segment end, every issuing thread: what this thread issued for the segment is
+          // tracked.  A thread that does not own the segment's last stage first waits until that
+          // stage has been issued: otherwise it could run on through a following short segment
+          // and arrive on d_full a second time before the owner's arrival for this one.
+          if (turn != me) mbar_wait(&hdr->issued[turn], (mst / kIssuers) & 1, abort_flag, p.status, 14);
           tc_commit(&hdr->d_full);
           ++seg;
           first_of_segment = true;
+          if (kb0 == kbpt) kb0 = 0;
         }
         ++mst;
-        advance(nkb);
+        if (++turn == kIssuers) turn = 0;
+        a_addr += a_stage;
+        b_lo += x_stage_lo;
+        if (++slot == n_stages) {
+          slot = 0;
+          phase ^= 1;
+          a_addr = a_base;
+          b_lo = x_base_lo;
+        }
       }
     }
   } else {
@@ -317,7 +339,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         for (int e = 0; e < 8; ++e) v[e] += __uint_as_float(t[e]);
       }
     };
-    int seg = 0, seg_kb0 = kb0;
+    int seg = 0;
     bool first_segment = true;
     // a first segment that is partial is reduced at the very end if this CTA turns out to be
     // the last contributor; `pend_old` (thread 0) is the arrival count the atomic returned
@@ -378,20 +400,31 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       }
     };
 
-    int stage_no = 0;
-    while (b < b_end) {
-      const int nkb = stage_len();
-      const uint8_t* ws = w_stages + static_cast<size_t>(wslot) * w_stage_bytes;
-      const bool seg_end = (kb0 + nkb == p.kb_per_tile) || (b + nkb == b_end);
-      // the stages go round-robin to the four warpgroups; the others only keep count
-      if ((stage_no & (kWarpGroups - 1)) == wg) {
+    // Segment by segment (a segment = the CTA's k-blocks of one tile).  The segment's stages
+    // have the global numbers st .. st + ns - 1; this warpgroup takes those equal to wg modulo
+    // four and keeps the ring positions of its next stage (both rings have at least four
+    // slots, so a step of four wraps at most once).
+    int tile = tile0, seg_kb0 = kb00, rem = rem0;
+    int st = 0, own = wg;
+    int slot = wg, wslot = wg;
+    uint32_t phase = 0, wphase = 0;
+    while (rem > 0) {
+      int seg_len = kbpt - seg_kb0;
+      if (seg_len > rem) seg_len = rem;
+      const int ns = (seg_len + kbs - 1) / kbs;
+      const int seg_kb1 = seg_kb0 + seg_len;
+      for (; own < st + ns; own += kWarpGroups) {
+        const int kb0 = seg_kb0 + (own - st) * kbs;
+        int nkb = seg_kb1 - kb0;
+        if (nkb > kbs) nkb = kbs;
+        const uint8_t* ws = w_stages + static_cast<size_t>(wslot) * w_stage_bytes;
         mbar_wait(&hdr->w_full[wslot], wphase, abort_flag, p.status, 16);
         const int g0 = kb0 >> p.kbpg_shift;
         for (int j = 0; j < nkb; ++j) {
           const uint4* wp = reinterpret_cast<const uint4*>(ws + j * kTcBlockBytes);
           const uint4 v0 = wp[row], v1 = wp[kTcTileN + row];
           const uint32_t szw = reinterpret_cast<const uint32_t*>(
-              ws + p.kbs * kTcBlockBytes)[(((kb0 + j) >> p.kbpg_shift) - g0) * kTcTileN + row];
+              ws + kbs * kTcBlockBytes)[(((kb0 + j) >> p.kbpg_shift) - g0) * kTcTileN + row];
           const uint32_t z2 = __byte_perm(szw, 0, 0x1010), s2 = __byte_perm(szw, 0, 0x3232);
           const uint32_t words[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
           uint32_t r[32];
@@ -411,20 +444,35 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             mbar_wait(&hdr->free_[slot], phase ^ 1, abort_flag, p.status, 17);
             tc_fence_after_sync();
           }
-          tmem_st_x32(lane_addr + p.a_col0 + slot * (p.kbs * 32) + j * 32, r);
+          // the lanes may leave a wait loop or the one-lane arrive above apart; the TMEM store is
+          // a warp-wide instruction
+          __syncwarp();
+          tmem_st_x32(lane_addr + p.a_col0 + slot * (kbs * 32) + j * 32, r);
         }
         tc_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&hdr->full[slot]);
+        slot += kWarpGroups;
+        if (slot >= n_stages) {
+          slot -= n_stages;
+          phase ^= 1;
+        }
+        wslot += kWarpGroups;
+        if (wslot >= n_wring) {
+          wslot -= n_wring;
+          wphase ^= 1;
+        }
       }
-      ++stage_no;
+      st += ns;
 
-      if (seg_end) {
-        const bool whole = (seg_kb0 == 0 && kb0 + nkb == p.kb_per_tile);
+      {
+        const bool whole = (seg_kb0 == 0 && seg_len == kbpt);
+        const bool more = rem > seg_len;  // this CTA goes on to another tile
         const int n_used = 1;
         mbar_wait(&hdr->d_full, seg & 1, abort_flag, p.status, 18);
         tc_fence_after_sync();
+        __syncwarp();  // the TMEM loads below are warp-wide instructions
         if (whole && p.fusion != FUSE_SILU_MUL) {
           for (int ch = wg; ch < n_chunks; ch += kWarpGroups) {
             float v[8];
@@ -450,7 +498,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           __syncwarp();
           if (lane == 0) mbar_arrive(&hdr->d_empty);
           named_bar_sync(1, kDequantWarps * 32);
-          const bool defer = !whole && first_segment && (b + nkb < b_end);
+          const bool defer = !whole && first_segment && more;
           if (defer) {
             // more tiles follow: count the arrival now, look at the answer when all work is done
             if (tid == 0) {
@@ -483,8 +531,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         ++seg;
         first_segment = false;
       }
-      advance(nkb);
-      if (seg_end) seg_kb0 = kb0;
+      rem -= seg_len;
+      seg_kb0 = seg_kb1;
+      if (seg_kb0 == kbpt) {
+        seg_kb0 = 0;
+        ++tile;
+      }
     }
     if (pend_tile >= 0) {
       if (tid == 0) {
@@ -507,7 +559,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after_sync();
-    __syncwarp();  // lane 0 comes from the issuing loop; the deallocation is a warp-wide instruction
+    __syncwarp();  // lane 0 comes from the issuing loop
     tmem_dealloc(tmem_base, kTmemCols);
   }
 }
@@ -530,10 +582,9 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
   p.a_col0 = (p.n_tok + 31) & ~31;
   const int a_groups = (kTmemCols - p.a_col0) / 32;
   // k-blocks per stage.  Every stage costs each role a fixed amount of scalar bookkeeping and
-  // barrier traffic (an issuing thread spends about 800 cycles per stage outside its MMAs),
-  // whatever the stage holds, so up to 128 tokens, where the MMAs of one k-block are short, a
-  // stage takes as many k-blocks as the rings allow: three up to 64 tokens (four or five A
-  // groups of three), two up to 128 (four activation slots of 32 KB).
+  // barrier traffic, whatever the stage holds, so up to 128 tokens, where the MMAs of one k-block
+  // are short, a stage takes as many k-blocks as the rings allow: three up to 64 tokens (four or
+  // five A groups of three), two up to 128 (four activation slots of 32 KB).
   p.kbs = p.n_tok <= 64 ? 3 : p.n_tok <= 128 ? 2 : 1;
   const int x_stage = p.kbs * p.n_tok * 128;
   const int w_stage = p.kbs * kTcBlockBytes + (p.kbs + 1) * 512;
