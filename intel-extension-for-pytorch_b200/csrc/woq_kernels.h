@@ -120,11 +120,12 @@ struct TcParams {
   int n_tok;           // token columns of the MMA (multiple of 16, <= 256)
   int tiles, kb_per_tile, kbpg_shift, groups;
   int kbs, stages;     // k-blocks per stage; slots of the A-group / activation ring
-  int w_ring, a_col0;  // slots of the packed-weight ring; first TMEM column of the A groups
+  int w_ring, a_col0;  // slots of the packed-weight ring (a multiple of four); first TMEM column of the A groups
   int fusion, gate_up;
 };
 
-// launches opt into programmatic dependent launch unless WOQ_B200_PDL=0 was set before first use
+// the M <= 16 kernel's launches opt into programmatic dependent launch unless WOQ_B200_PDL=0 was
+// set before first use (the tcgen05 kernels launch plainly)
 bool dependent_launch_enabled();
 int tc_pick_grid(int tiles, int kb_per_tile, int num_sms);
 size_t tc_partial_bytes(int grid, int n_tok);
