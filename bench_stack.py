@@ -211,6 +211,8 @@ def run_stack(args, peaks, clock_sampler):
             prefill()
             e1.record()
             torch.cuda.synchronize()
+            # a kernel that gave up a bounded wait still ends; its status word says so
+            torch.ops.torch_ipex.woq_check_status()
         prefill_ms = e0.elapsed_time(e1)
         first = tok.clone()
 
@@ -256,6 +258,7 @@ def run_stack(args, peaks, clock_sampler):
         e1.record()
         torch.cuda.synchronize()
         decode_ms = e0.elapsed_time(e1) / new_tokens
+        torch.ops.torch_ipex.woq_check_status()
         distinct = int(out_tokens.unique().numel())
 
         # ---- the WOQ linears of one token step alone -------------------------------------
