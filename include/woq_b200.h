@@ -409,6 +409,14 @@ int woq_b200_int8_zero_points(const woq_b200_ctx* ctx, int64_t m, int32_t* zp, c
  * shared-memory budget per thread block in bytes. */
 int woq_b200_decode_plan(const woq_b200_ctx* ctx, int64_t m, int32_t* out);
 
+/* The pipeline shape of one launch of the tcgen05 INT4 kernel with n_tok token columns (16..256,
+ * a multiple of 16; woq_b200_linear rounds the tokens of a launch up to that).  No reference
+ * counterpart; a diagnostic that needs no GPU: out[0] k-blocks per stage, out[1] slots of the
+ * A-group / activation ring (at least 4), out[2] slots of the packed-weight ring (a multiple of 4),
+ * out[3] first TMEM column of the A groups (out[3] + 32 * out[0] * out[1] <= 512), out[4] dynamic
+ * shared memory in bytes. */
+int woq_b200_tc_plan(int32_t n_tok, int32_t* out);
+
 /* Reads the status word of a workspace (synchronises the stream).  WOQ_B200_OK, or
  * WOQ_B200_ERR_DEVICE_WAIT when a bounded wait inside a kernel gave up; the word is cleared. */
 int woq_b200_workspace_status(void* workspace, void* stream);

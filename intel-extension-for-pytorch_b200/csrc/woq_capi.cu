@@ -1550,6 +1550,21 @@ int woq_b200_decode_plan(const woq_b200_ctx* c, int64_t m, int32_t* out) {
   return WOQ_B200_OK;
 }
 
+int woq_b200_tc_plan(int32_t n_tok, int32_t* out) {
+  if (!out || n_tok < 16 || n_tok > 256 || (n_tok & 15))
+    return fail(WOQ_B200_ERR_INVALID_ARG, "tensor-core plan: token columns 16..256, a multiple of 16");
+  woq::TcParams p{};
+  p.n_tok = n_tok;
+  const size_t smem = woq::tc_plan(p);
+  if (smem == 0) return fail(WOQ_B200_ERR_UNSUPPORTED, "no pipeline shape for %d token columns", (int)n_tok);
+  out[0] = p.kbs;
+  out[1] = p.stages;
+  out[2] = p.w_ring;
+  out[3] = p.a_col0;
+  out[4] = static_cast<int32_t>(smem);
+  return WOQ_B200_OK;
+}
+
 int woq_b200_workspace_status(void* workspace, void* stream_) {
   if (!workspace) return fail(WOQ_B200_ERR_INVALID_ARG, "workspace is null");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);

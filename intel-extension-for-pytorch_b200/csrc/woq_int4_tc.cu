@@ -577,7 +577,10 @@ int tc_pick_grid(int tiles, int kb_per_tile, int num_sms) {
   return static_cast<int>(grid < 1 ? 1 : grid);
 }
 
-cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream) {
+// Pipeline shape of a launch with `n_tok` token columns (a multiple of 16, at most 256): fills
+// a_col0, kbs, stages and w_ring of `p` and returns the dynamic shared memory in bytes, or 0 when
+// no valid shape exists.
+size_t tc_plan(TcParams& p) {
   // TMEM: the accumulator takes the token columns (rounded to 32), the A groups the rest.
   p.a_col0 = (p.n_tok + 31) & ~31;
   const int a_groups = (kTmemCols - p.a_col0) / 32;
@@ -617,10 +620,15 @@ cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaSt
   //    whose previous load had not landed yet: it read the use before that, released the slot
   //    early, and the launch ended in a time-out or a launch failure.)
   w_ring &= ~3;
-  if (stages < 4 || w_ring < 4) return cudaErrorInvalidConfiguration;
+  if (stages < 4 || w_ring < 4) return 0;
   p.w_ring = w_ring;
   p.stages = stages;
-  const size_t smem = kTcHeaderBytes + static_cast<size_t>(stages) * x_stage + static_cast<size_t>(w_ring) * w_stage;
+  return kTcHeaderBytes + static_cast<size_t>(stages) * x_stage + static_cast<size_t>(w_ring) * w_stage;
+}
+
+cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream) {
+  const size_t smem = tc_plan(p);
+  if (smem == 0) return cudaErrorInvalidConfiguration;
   cudaError_t e = cudaFuncSetAttribute(woq_int4_tc_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem));

@@ -129,6 +129,7 @@ struct TcParams {
 bool dependent_launch_enabled();
 int tc_pick_grid(int tiles, int kb_per_tile, int num_sms);
 size_t tc_partial_bytes(int grid, int n_tok);
+size_t tc_plan(TcParams& p);  // fills a_col0, kbs, stages, w_ring from n_tok; returns the dynamic shared memory (0: none)
 cudaError_t launch_int4_tc(TcParams p, const CUtensorMap& xmap, int grid, cudaStream_t stream);
 
 __host__ __device__ inline int tc_tile_row_to_n(int n_total, int gate_up, int tile, int row) {

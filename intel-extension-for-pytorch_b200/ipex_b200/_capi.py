@@ -60,6 +60,7 @@ EXPORTS = [
     "woq_b200_int8_zero_points",
     "woq_b200_workspace_status",
     "woq_b200_decode_plan",
+    "woq_b200_tc_plan",
     "woq_b200_comm_create",
     "woq_b200_comm_export",
     "woq_b200_comm_connect",
@@ -142,6 +143,7 @@ def lib() -> ctypes.CDLL:
     L.woq_b200_int8_zero_points.argtypes = [vp, i64, vp, vp, sz, vp]
     L.woq_b200_workspace_status.argtypes = [vp, vp]
     L.woq_b200_decode_plan.argtypes = [vp, i64, ctypes.POINTER(i32)]
+    L.woq_b200_tc_plan.argtypes = [i32, ctypes.POINTER(i32)]
     L.woq_b200_comm_create.argtypes = [i32, i32, i64, sz, ctypes.POINTER(vp)]
     L.woq_b200_comm_export.argtypes = [vp, vp]
     L.woq_b200_comm_connect.argtypes = [vp, vp]
@@ -177,6 +179,13 @@ def _others(others, m: int, n_out: int, out: torch.Tensor):
             raise ValueError("extra operands must have the output's row stride "
                              f"({out.stride(0)}), got {o.stride(0)}")
     return oth
+
+
+def tc_plan(n_tok: int) -> dict:
+    """Pipeline shape of a tcgen05 INT4 launch with n_tok token columns (woq_b200_tc_plan; no GPU needed)."""
+    out = (ctypes.c_int32 * 5)()
+    _check(lib().woq_b200_tc_plan(n_tok, out))
+    return {"kbs": out[0], "stages": out[1], "w_ring": out[2], "a_col0": out[3], "smem_bytes": out[4]}
 
 
 def static_scratch_status():

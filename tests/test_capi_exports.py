@@ -67,3 +67,32 @@ def test_bad_arguments_are_rejected_without_a_gpu(built_lib):
     assert L.woq_b200_linear(None, None, 1, 64, 0, None, 0, None, 64, None, 0, None) == 1
     fake = (ctypes.c_uint64 * 64)()
     assert L.woq_b200_ctx_destroy(ctypes.cast(fake, ctypes.c_void_p)) == 5
+
+
+def test_tensor_core_pipeline_shapes_keep_the_ring_rules(built_lib):
+    """woq_b200_tc_plan for every token-column count a launch can have: at least four slots in the
+    A-group / activation ring (a warpgroup works on every fourth stage), a packed-weight ring whose
+    length is a multiple of four (every slot belongs to one warpgroup, which has itself waited for
+    the slot's previous use - a parity wait cannot tell one missing completion from three), the A
+    groups inside the 512 TMEM columns, the tiles 1024-byte aligned, shared memory within a CTA's
+    227 KB."""
+    from ipex_b200 import _capi
+
+    for n_tok in range(16, 257, 16):
+        p = _capi.tc_plan(n_tok)
+        assert p["kbs"] == (3 if n_tok <= 64 else 2 if n_tok <= 128 else 1), (n_tok, p)
+        assert p["stages"] >= 4, (n_tok, p)
+        assert p["w_ring"] >= 4 and p["w_ring"] % 4 == 0 and p["w_ring"] <= 32, (n_tok, p)
+        assert p["a_col0"] >= n_tok and p["a_col0"] % 32 == 0, (n_tok, p)
+        assert p["a_col0"] + 32 * p["kbs"] * p["stages"] <= 512, (n_tok, p)
+        x_stage = p["kbs"] * n_tok * 128
+        w_stage = p["kbs"] * 4096 + (p["kbs"] + 1) * 512
+        assert x_stage % 1024 == 0 and w_stage % 16 == 0
+        assert p["smem_bytes"] == 1024 + p["stages"] * x_stage + p["w_ring"] * w_stage, (n_tok, p)
+        assert p["smem_bytes"] <= 227 * 1024, (n_tok, p)
+    assert _capi.tc_plan(256) == {"kbs": 1, "stages": 6, "w_ring": 4, "a_col0": 256, "smem_bytes": 1024 + 6 * 32768 + 4 * 5120}
+    assert _capi.tc_plan(128)["stages"] == 4 and _capi.tc_plan(128)["w_ring"] == 8
+    L = _capi.lib()
+    out = (ctypes.c_int32 * 5)()
+    for bad in (0, 8, 24, 272):
+        assert L.woq_b200_tc_plan(bad, out) == 1
